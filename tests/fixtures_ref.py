@@ -1,0 +1,127 @@
+"""Structured fixtures of the reference's own device qualification tests, rebuilt
+from the constants those tests state (they are data, not code).  Each builder
+names the reference test it follows; sizes are parameters so that the same
+patterns can be used on small planes."""
+import numpy as np
+
+from oracle import tuisko_oracle as O
+
+# qual/src/fp8_projection_oracle.rs:6-8
+WEIGHT_CODES = np.array([0x38, 0xB0, 0x30, 0x28], dtype=np.uint8)
+WEIGHT_VALUES = np.array([1.0, -0.5, 0.5, 0.25], dtype=np.float32)
+SCALE_VALUES = np.array([1.0, 0.5, 0.25, 2.0], dtype=np.float32)
+# qual/src/fp8_qkv.rs:23-30
+FP8_INPUT_PATTERN = np.array([0.875, -0.875, 0.5, -0.5, 0.25, -0.25, 0.125, -0.125, 0.0625,
+                              -0.0625, 0.03125, -0.03125, 0.0, 0.5, -0.25, 0.125], dtype=np.float32)
+FP8_TOKEN_FACTORS = np.array([1.0, 0.5, 0.25, 0.125, -1.0, -0.5, -0.25, -0.125, 0.75, -0.75,
+                              0.375, -0.375, 0.1875, -0.1875, 0.09375, -0.09375], dtype=np.float32)
+# qual/src/residual_norm.rs:12-19
+NORM_INPUT_PATTERN = np.array([0.875, -0.75, 0.625, -0.5, 0.375, -0.25, 0.125, -0.0625, -0.875,
+                               0.75, -0.625, 0.5, -0.375, 0.25, -0.125, 0.0625], dtype=np.float32)
+NORM_BRANCH_PATTERN = np.array([0.25, -0.125, 0.0625, -0.03125, -0.25, 0.125, -0.0625, 0.03125],
+                               dtype=np.float32)
+NORM_WEIGHT_PATTERN = np.array([-0.25, -0.125, -0.0625, 0.0, 0.0625, 0.125, 0.1875, 0.25],
+                               dtype=np.float32)
+# qual/src/nvfp4_swiglu.rs:16-23,196-199
+NVFP4_WEIGHT_SCALE_DIVISOR = 0.125
+NVFP4_INPUT_PATTERN = np.array([0.5, -0.5, 0.25, -0.25, 0.125, -0.125, 0.0, 0.5, -0.5, 0.25, -0.25,
+                                0.125, -0.125, 0.0, 0.5, -0.5], dtype=np.float32)
+NVFP4_TOKEN_FACTORS = np.array([1.0, 0.5, 0.25, 0.125, 1.0, 0.5, 0.25, 0.125], dtype=np.float32)
+NVFP4_BASE = np.array([0xF7, 0xD5, 0xB3, 0x70, 0x5F, 0x3D, 0x0B, 0xF7], dtype=np.uint8)
+NVFP4_SPARSE = np.array([0x01, 0, 0, 0, 0, 0, 0, 0], dtype=np.uint8)
+NVFP4_SCALE_CODES = np.array([0x38, 0x01, 0x40, 0x01], dtype=np.uint8)
+
+
+def fp8_input(rows: int, hidden: int) -> np.ndarray:
+    """qual/src/fp8_qkv.rs:169-177 (make_input): BF16 bits [rows, hidden]."""
+    idx = np.arange(rows * hidden)
+    vals = FP8_INPUT_PATTERN[idx & 15] * FP8_TOKEN_FACTORS[(idx // hidden) % 16]
+    return O.f32_to_bf16(vals).reshape(rows, hidden)
+
+
+def fp8_weights(out_rows: int, hidden: int):
+    """qual/src/fp8_qkv.rs:179-195 (make_weights): constant code per row, BF16 row scales."""
+    rows = np.arange(out_rows)
+    codes = np.repeat(WEIGHT_CODES[rows & 3][:, None], hidden, axis=1).astype(np.uint8)
+    scales = O.f32_to_bf16(SCALE_VALUES[rows & 3])
+    return np.ascontiguousarray(codes), scales
+
+
+def fp8_expected(represented_sum: float, scale: np.float32, out_rows: int) -> np.ndarray:
+    """qual/src/fp8_qkv.rs:281-285 closed form, f64 [out_rows]."""
+    rows = np.arange(out_rows)
+    return (represented_sum * WEIGHT_VALUES[rows & 3].astype(np.float64) * np.float64(scale)
+            * SCALE_VALUES[rows & 3].astype(np.float64))
+
+
+def norm_fixture(rows: int, hidden: int):
+    """qual/src/residual_norm.rs:80-94: (input, branch, weight) BF16 bit planes."""
+    idx = np.arange(rows * hidden)
+    tok = idx // hidden
+    x = NORM_INPUT_PATTERN[(idx + tok) & 15] * (np.float32(1.0) - tok.astype(np.float32) * np.float32(0.03125))
+    b = NORM_BRANCH_PATTERN[(idx * 3 + tok) & 7]
+    w = NORM_WEIGHT_PATTERN[np.arange(hidden) & 7]
+    return (O.f32_to_bf16(x).reshape(rows, hidden), O.f32_to_bf16(b).reshape(rows, hidden),
+            O.f32_to_bf16(w))
+
+
+def nvfp4_input(rows: int, k: int) -> np.ndarray:
+    """qual/src/nvfp4_swiglu.rs:173-180 (make_fixture input)."""
+    idx = np.arange(rows * k)
+    vals = NVFP4_INPUT_PATTERN[idx & 15] * NVFP4_TOKEN_FACTORS[(idx // k) % 8]
+    return O.f32_to_bf16(vals).reshape(rows, k)
+
+
+def nvfp4_exceptional_group(row, groups):
+    """qual/src/nvfp4_swiglu.rs:355-357."""
+    return (row * 17 + row // 128 * 13) % groups
+
+
+def nvfp4_weights(rows_w: int, k: int, gate_up_split: int | None):
+    """qual/src/nvfp4_swiglu.rs:196-234 (gate_up_split = OUTPUT_ROWS) and
+    qual/src/nvfp4_down.rs:196-230 (gate_up_split = None).  Returns (codes [rows_w,k/2],
+    swizzled scale plane)."""
+    groups = k // 16
+    negative = NVFP4_BASE ^ 0x88
+    codes = np.zeros((rows_w, groups, 8), dtype=np.uint8)
+    scales = np.zeros(rows_w * groups, dtype=np.uint8)
+    offs = O.nvfp4_scale_offsets(rows_w, groups)
+    for row in range(rows_w):
+        base_is_base = (row & 1) == 0
+        if gate_up_split is None:
+            base = NVFP4_BASE if base_is_base else negative
+        elif row < gate_up_split and row & 1:
+            base = NVFP4_SPARSE
+        elif row >= gate_up_split and row & 1:
+            base = negative
+        else:
+            base = NVFP4_BASE
+        exceptional = NVFP4_SPARSE if base_is_base else NVFP4_BASE
+        eg = nvfp4_exceptional_group(row, groups)
+        codes[row, :, :] = base
+        codes[row, eg, :] = exceptional
+        sc = np.full(groups, NVFP4_SCALE_CODES[row & 3], dtype=np.uint8)
+        sc[eg] = NVFP4_SCALE_CODES[(row + 1) & 3]
+        scales[offs[row]] = sc
+    return codes.reshape(rows_w, k // 2), scales
+
+
+def nvfp4_closed_form_dot(x_bits: np.ndarray, token: int, row: int, codes, scales, k: int) -> float:
+    """qual/src/nvfp4_swiglu.rs:317-353 (dot_oracle + group_dot): the fixture's closed form."""
+    groups = k // 16
+    eg = nvfp4_exceptional_group(row, groups)
+    og = (eg + 1) % groups
+    xf = O.bf16_to_f32(x_bits[token]).astype(np.float64)
+    tab = O.e4m3_decode_table().astype(np.float64)
+
+    def group_dot(g):
+        s = 0.0
+        for c in range(16):
+            packed = int(codes[row, g * 8 + c // 2])
+            code = (packed >> 4) if (c & 1) else (packed & 15)
+            s += xf[g * 16 + c] * O.e2m1_decode(code)
+        return s
+
+    so = tab[scales[O.nvfp4_scale_offset(row, og, groups)]]
+    se = tab[scales[O.nvfp4_scale_offset(row, eg, groups)]]
+    return ((groups - 1) * group_dot(og) * so + group_dot(eg) * se) / NVFP4_WEIGHT_SCALE_DIVISOR
