@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized projection hot path on B200.
+
+Workload (all N): the FP8 LM head with fused greedy argmax of the third benchmark
+configuration -- K = 5120, vocabulary 248320, M decode tokens (default 1), E4M3 weights
+~N(0, 0.02) with one BF16 scale per row, BF16 hidden ~N(0, 1), fp32 logits + int32 argmax
+out -- the largest single-GPU configuration of the path and the one that shards: the
+vocabulary is split contiguously over the N ranks, every rank streams its shard once per
+step and the per-shard (max, index) pairs are gathered with NCCL and merged.
+
+One step = quantise the hidden rows + stream the weight shard through the tcgen05
+projection kernel + argmax finalize (+ all-gather + merge when N > 1).
+
+  value   whole-job algorithmic GB/s with the hidden rows resident in HBM
+  e2e     the same through the public operator call with HOST buffers: pinned-host ->
+          device copy of the hidden rows and device -> host read of the argmax pairs
+          inside the timed region, one stream synchronisation per step
+  roofline  the projection kernel alone against the measured HBM copy bandwidth
+
+`--impl reference` times the CPU restatement of the reference's qualification oracle for
+the same workload on the host cores (the reference is Rust + cuda-oxide for sm_120 and can
+neither be built nor run here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN = 5120
+VOCAB = 248320
+SEED = 20260425
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(rows: int, out_rows: int, k: int, out_bytes: int) -> int:
+    """weights + row scales + activation codes + activation scales + outputs."""
+    return out_rows * k + 2 * out_rows + rows * k + 4 * rows + out_bytes * rows * out_rows
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Polls nvidia-smi for SM clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        for p in self.samples:
+            try:
+                sm.append(float(p[0]))
+                mx = max(mx, float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------- CPU arm
+
+def cpu_lm_head(rows: int, steps: int, warmup: int, budget_s: float, sample_rows: int = 0):
+    """Times the oracle's LM-head formula (quantise + f64 FP8 dot + greedy pick) on a
+    bounded sample of vocabulary rows sized so that all steps take about `budget_s` seconds;
+    returns (GB/s, seconds/step, threads, note)."""
+    import numpy as np
+
+    from oracle import tuisko_oracle as O
+    from tuiskollm_b200 import synth
+
+    O.lib()
+    x = synth.normal_bf16(SEED, 2, (rows, HIDDEN))
+
+    def make_step(wc, ws):
+        def step():
+            codes, scales = O.quantize_e4m3(x)
+            logits = O.fp8_projection(codes, scales, wc, ws)
+            bits = O.f32_to_bf16(logits.astype(np.float32))
+            return [O.greedy_index(bits[t]) for t in range(rows)]
+        return step
+
+    if sample_rows <= 0:
+        probe_rows = 2048
+        probe = make_step(*synth.fp8_weights(SEED, 1, probe_rows, HIDDEN))
+        probe()
+        t0 = time.perf_counter()
+        probe()
+        rate = probe_rows / max(time.perf_counter() - t0, 1e-6)  # vocabulary rows per second
+        sample_rows = int(rate * budget_s / max(1, steps + warmup))
+        sample_rows = max(1024, min(32768, sample_rows // 128 * 128))  # bounded host memory
+    step = make_step(*synth.fp8_weights(SEED, 1, sample_rows, HIDDEN))
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    nbytes = algorithmic_bytes(rows, sample_rows, HIDDEN, 4)
+    note = (f"{sample_rows} of {VOCAB} vocabulary rows x {HIDDEN}, M={rows}: per-token E4M3 "
+            f"quantise, f64 dot of decoded codes, greedy pick; OpenMP over rows")
+    return nbytes / dt / 1e9, dt, O.num_threads(), note, sample_rows
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    gbs, dt, threads, note, sample = cpu_lm_head(args.rows, max(1, args.steps), args.warmup,
+                                                 budget_s=90.0, sample_rows=args.cpu_sample_rows)
+    line = {
+        "impl": "reference", "metric": "fp8_lm_head_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3",
+        "data": "synthetic",
+        "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={VOCAB} M={args.rows}",
+                   "rows": args.rows, "sampled_vocab_rows": sample},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": note},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------- GPU arm
+
+def time_region(torch, fn, steps, sync_each=False):
+    """CUDA-event time (ms) of `steps` calls of fn on the current stream."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        fn()
+        if sync_each:
+            torch.cuda.current_stream().synchronize()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop)
+
+
+def extra_rows(torch, tk, ctx, peak_gbs):
+    """Other configurations of the path on one GPU: decode projections with the weight plane
+    rotated over several copies so that every launch streams from HBM, not from L2."""
+    import numpy as np
+
+    from tuiskollm_b200 import synth
+
+    out = []
+    dev = "cuda"
+    for name, n_rows in (("fp8_qkv", synth.QKV_ROWS), ("fp8_gdn_input", synth.GDN_ROWS),
+                         ("fp8_qkv_refN", synth.QKV_ROWS_REF),
+                         ("fp8_gdn_input_refN", synth.GDN_ROWS_REF)):
+        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)
+        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, dev) for c in range(copies)]
+        for m in (1, 8, 32):
+            if name.endswith("refN") and m != 1:
+                continue
+            x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), dev)
+            codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+            scales = torch.empty((m,), dtype=torch.float32, device=dev)
+            outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device=dev)
+            op = tk.GdnInputProjectionOp(ctx, n_rows)
+            op.launch(None, m, x, codes, scales, planes[0][0], planes[0][1], outp)
+            state = {"i": 0}
+
+            def proj():
+                w, s = planes[state["i"] % copies]
+                state["i"] += 1
+                op.launch(None, m, None, codes, scales, w, s, outp)
+
+            for _ in range(copies * 2):
+                proj()
+            iters = copies * 12
+            ms = time_region(torch, proj, iters) / iters
+            b = algorithmic_bytes(m, n_rows, HIDDEN, 2)
+            out.append({"op": name, "M": m, "N": n_rows, "us": ms * 1e3, "GB/s": b / ms / 1e6,
+                        "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs,
+                        "frac_of_8TBs": b / ms / 1e6 / 8000.0, "weight_copies": copies})
+        del planes
+    # fused residual + RMSNorm + quantise
+    normop = tk.ResidualNormOp(ctx)
+    for m in (1, 256, 512):
+        copies = 1 if m == 1 else max(2, int(2 * 126e6 / (m * HIDDEN * 11)) + 1)
+        xs = [synth.torch_normal_bf16(SEED, 90 + c, (m, HIDDEN), dev) for c in range(copies)]
+        bs = [synth.torch_normal_bf16(SEED, 190 + c, (m, HIDDEN), dev) for c in range(copies)]
+        w = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)
+        res = [torch.empty_like(xs[0]) for _ in range(copies)]
+        nrm = [torch.empty_like(xs[0]) for _ in range(copies)]
+        codes = [torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev) for _ in range(copies)]
+        scales = torch.empty((m,), dtype=torch.float32, device=dev)
+        state = {"i": 0}
+
+        def norm():
+            i = state["i"] % copies
+            state["i"] += 1
+            normop.launch_quantize(None, m, xs[i], bs[i], w, res[i], nrm[i], codes[i], scales)
+
+        for _ in range(8):
+            norm()
+        iters = 200
+        ms = time_region(torch, norm, iters) / iters
+        b = 10 * m * HIDDEN + m * HIDDEN + 4 * m
+        out.append({"op": "residual_rmsnorm_quant_e4m3", "M": m, "us": ms * 1e3,
+                    "GB/s": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs})
+    return out
+
+
+def run_native(args):
+    import numpy as np
+    import torch
+
+    import tuiskollm_b200 as tk
+    from tuiskollm_b200 import synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    m = args.rows
+    assert VOCAB % world == 0
+    shard = VOCAB // world
+    offset = rank * shard
+    ctx = tk.Context(device=local, max_rows=max(2048, m))
+    dev = "cuda"
+    # every rank draws the same hidden rows; weights are drawn per shard (stream = rank)
+    wc, ws = synth.torch_fp8_weights(SEED, 1000 + rank, shard, HIDDEN, dev)
+    x_host = torch.from_numpy(synth.normal_bf16(SEED, 2, (m, HIDDEN)).view(np.int16)).pin_memory()
+    x = x_host.to(dev)
+    codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+    scales = torch.empty((m,), dtype=torch.float32, device=dev)
+    logits = torch.empty((m, shard), dtype=torch.float32, device=dev)
+    scratch = torch.zeros((m,), dtype=torch.int64, device=dev)
+    pairs = torch.zeros((m, 2), dtype=torch.int32, device=dev)
+    gathered = torch.zeros((world, m, 2), dtype=torch.int32, device=dev)
+    merged = torch.zeros((m, 2), dtype=torch.int32, device=dev)
+    merged_host = torch.zeros((m, 2), dtype=torch.int32).pin_memory()
+    op = tk.LmHeadOp(ctx, shard, offset)
+
+    def step():
+        op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, pairs)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), pairs.view(-1))
+            op.merge(None, m, world, gathered, merged)
+
+    def step_e2e():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        merged_host.copy_(merged if world > 1 else pairs, non_blocking=True)
+
+    def projection_only():
+        op.launch(None, m, None, codes, scales, wc, ws, None, logits, scratch, pairs)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launch_count
+    ms = time_region(torch, step, args.steps)
+    launches = ctx.launch_count - launches0
+    barrier()
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    ms_e2e = time_region(torch, step_e2e, args.steps, sync_each=True)
+    barrier()
+    for _ in range(3):
+        projection_only()
+    ms_proj = time_region(torch, projection_only, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([ms, ms_e2e, ms_proj], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e, ms_proj = [float(v) for v in times.tolist()]
+
+    # sanity: the selected token is the arg-max of the logits this step wrote
+    step()
+    torch.cuda.synchronize()
+    final = (merged if world > 1 else pairs).cpu().numpy()
+    mine = pairs.cpu().numpy()
+    rounded = logits.to(torch.bfloat16).float()
+    for t in range(m):
+        first = int(torch.nonzero(rounded[t] == rounded[t].max())[0, 0]) + offset
+        assert int(mine[t, 1]) == first, "device argmax disagrees with its own logits"
+    status = ctx.device_status()
+    assert status == 0, f"device status word {status:#x}"
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        total_bytes = algorithmic_bytes(m, VOCAB, HIDDEN, 4) + (world - 1) * (m * HIDDEN + 4 * m)
+        per_step = ms / args.steps
+        value = total_bytes / per_step / 1e6
+        e2e_value = total_bytes / (ms_e2e / args.steps) / 1e6
+        shard_bytes = algorithmic_bytes(m, shard, HIDDEN, 4)
+        proj_ms = ms_proj / args.steps
+        achieved = shard_bytes / proj_ms / 1e6
+        line = {
+            "metric": "fp8_lm_head_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3",
+            "data": "synthetic",
+            "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={VOCAB} M={m}",
+                       "rows": m, "vocab_shard_rows": shard, "parallelism": f"vocab-shard x{world}",
+                       "l2": "weight shard (%.0f MB) larger than L2, streamed once per step"
+                             % (shard * HIDDEN / 1e6),
+                       "tokens_per_s": m / (per_step * 1e-3), "us_per_step": per_step * 1e3},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
+                    "d2h_bytes_per_step": m * 8, "us_per_step": ms_e2e / args.steps * 1e3},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "fp8_projection_kernel<16> (+ argmax finalize, < 2 us)",
+                         "us_per_launch": proj_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
+            "clocks": clocks,
+            "selected_tokens": final[:, 1].tolist()[:8],
+        }
+        if world == 1 and not args.no_cpu:
+            gbs, dt, threads, note, _ = cpu_lm_head(m, 3, 1, budget_s=15.0,
+                                                    sample_rows=args.cpu_sample_rows)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": note, "seconds_per_sample": dt}
+        if world == 1 and not args.no_extra:
+            line["extra"] = extra_rows(torch, tk, ctx, peak)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--rows", type=int, default=1, help="decode tokens M (1, 4 or 32 in the config)")
+    ap.add_argument("--cpu-sample-rows", type=int, default=0,
+                    help="vocabulary rows per CPU step (0 = sized from a probe)")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_native(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,172 @@
+/*
+ * tuisko-kernels-sm100: C ABI of the B200 (sm_100a) quantized projection operators.
+ *
+ * Each entry point stands in for one prepared-operator method of the reference's
+ * sm_120 / sm_89 kernel crates (file:line cited per function, paths relative to the
+ * blaind/tuiskollm tree) and keeps its pointer planes, layouts and scale conventions:
+ *
+ *   - BF16 planes are uint16_t bit patterns, row-major, token-major outputs [rows, N];
+ *   - FP8 weights are E4M3FN codes [N, K] row-major (K contiguous) with ONE BF16 scale
+ *     per output row; activations are quantised per token to E4M3FN with one fp32
+ *     scale = amax/448 (1 when amax == 0);
+ *   - NVFP4 weights are E2M1 codes [N, K/2] (low nibble = even column), E4M3 block
+ *     scales per 16 columns stored in 128-row x 4-group tiles
+ *     (tuisko-model/src/materialize.rs:410-422) and one fp32 global divisor;
+ *   - the RMSNorm weight is stored zero-centred and applied as (1 + w).
+ *
+ * Conventions shared by every launch function:
+ *   - the caller owns every buffer; launches allocate nothing, synchronise nothing and
+ *     are stream-ordered on `stream` (a CUstream / cudaStream_t), so they can be
+ *     recorded into a CUDA graph;
+ *   - rows beyond `rows` of any output plane are never written;
+ *   - pointers must be 16-byte aligned (the reference's arenas align to 256 bytes);
+ *     FP8/NVFP4 code planes read through TMA must be 128-byte aligned;
+ *   - the return value is a tk100_status; tk100_last_error() describes the failure.
+ *     Nothing aborts or throws across this boundary.
+ *
+ * The library has no CPU fallback: without a CUDA device tk100_create fails.
+ */
+#ifndef TUISKO_SM100_H_
+#define TUISKO_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TK100_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define TK100_API __attribute__((visibility("default")))
+#else
+#define TK100_API
+#endif
+
+/* Mirrors tuisko-gpu/src/error.rs:8-43 (GpuErrorCode) one to one. */
+typedef enum tk100_status {
+  TK100_OK = 0,
+  TK100_ERR_DRIVER = 1,  /* gpu.driver  */
+  TK100_ERR_ARENA = 2,   /* gpu.arena   */
+  TK100_ERR_GRAPH = 3,   /* gpu.graph   */
+  TK100_ERR_CONTEXT = 4, /* gpu.context */
+  TK100_ERR_LAUNCH = 5,  /* gpu.launch  */
+  TK100_ERR_MODULE = 6   /* gpu.module  */
+} tk100_status;
+
+/* Bits of the device status word returned by tk100_device_status(). */
+#define TK100_DEVICE_WAIT_TIMEOUT 1u    /* a bounded in-kernel wait gave up */
+#define TK100_DEVICE_NONFINITE_LOGIT 2u /* LM head produced NaN/Inf (sampling.rs:233-242) */
+#define TK100_DEVICE_NONFINITE_INPUT 4u /* quantiser met NaN/Inf */
+#define TK100_DEVICE_BAD_ARGUMENT 8u
+
+typedef struct tk100_ctx tk100_ctx;
+typedef void* tk100_stream; /* CUstream / cudaStream_t */
+
+/* Model geometry, the run-time counterpart of the reference's `Arch` constants
+ * (tuisko-model/src/lib.rs:29-137).  Zero fields take the Qwen3.8-27B values. */
+typedef struct tk100_config {
+  uint32_t abi_version;     /* TK100_ABI_VERSION */
+  int32_t device;           /* CUDA device ordinal; must be current-able by the caller */
+  uint32_t hidden;          /* 5120 */
+  uint32_t intermediate;    /* 17408 */
+  float rms_norm_epsilon;   /* 1e-6 */
+  uint32_t max_rows;        /* largest `rows` any launch will pass (default 2048) */
+  uint64_t workspace_bytes; /* split-K scratch allocated once by tk100_create (default 64 MiB) */
+} tk100_config;
+
+/* (max, index) of one token row, index in global vocabulary numbering; -1 = no row. */
+typedef struct tk100_argmax_pair {
+  float value;
+  int32_t index;
+} tk100_argmax_pair;
+
+/* Replaces `*Op::new(&Arc<CudaContext>)` (tuisko-kernels-sm120/src/residual_norm.rs:396-416,
+ * src/fp8/projection.rs:525-545, :629, :720; tuisko-kernels-sm89/src/nvfp4/swiglu.rs:495):
+ * validates the geometry, prepares every kernel route and allocates the only memory the
+ * library ever owns (split-K scratch, tile tickets, the status word).  No launches. */
+TK100_API tk100_status tk100_create(const tk100_config* config, tk100_ctx** out);
+TK100_API void tk100_destroy(tk100_ctx* ctx);
+/* Message of the last failure on this context (or of tk100_create when ctx is NULL). */
+TK100_API const char* tk100_last_error(const tk100_ctx* ctx);
+/* Reads and clears the device status word; synchronises `stream`. */
+TK100_API tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* word);
+/* Number of kernels this context has launched (for launch accounting). */
+TK100_API uint64_t tk100_launch_count(const tk100_ctx* ctx);
+
+/* ResidualNormOp::launch_plain (tuisko-kernels-sm120/src/residual_norm.rs:425-456). */
+TK100_API tk100_status tk100_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
+                            const uint16_t* weight, uint16_t* output);
+
+/* ResidualNormOp::launch_residual (tuisko-kernels-sm120/src/residual_norm.rs:467-507).
+ * residual_input and branch may alias each other; residual_output may be residual_input. */
+TK100_API tk100_status tk100_residual_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                     const uint16_t* residual_input, const uint16_t* branch,
+                                     const uint16_t* weight, uint16_t* residual_output,
+                                     uint16_t* normalized_output);
+
+/* The fused producer: launch_residual / launch_plain (branch == NULL, residual_output
+ * ignored) plus the per-token E4M3 quantiser that the reference launches separately
+ * (tuisko-kernels-sm120/src/fp8/projection.rs:71-88, device/fp8_projection.rs:54-126),
+ * in ONE kernel.  activation_codes [rows, hidden] u8, activation_scales [rows] f32. */
+TK100_API tk100_status tk100_residual_rms_norm_quantize(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                              const uint16_t* residual_input,
+                                              const uint16_t* branch, const uint16_t* weight,
+                                              uint16_t* residual_output,
+                                              uint16_t* normalized_output,
+                                              uint8_t* activation_codes,
+                                              float* activation_scales);
+
+/* quantize_activation_e4m3 alone (tuisko-kernels-sm120/src/fp8/projection.rs:71-88),
+ * for rows of `columns` BF16 values (columns % 8 == 0). */
+TK100_API tk100_status tk100_quantize_activation_e4m3(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                            int columns, const uint16_t* input,
+                                            uint8_t* activation_codes, float* activation_scales);
+
+/* FullAttentionQkvOp::launch / GdnInputProjectionOp::launch
+ * (tuisko-kernels-sm120/src/fp8/projection.rs:557-611, :660-702), same argument order.
+ * `out_rows` is the weight row count N (the reference fixes it per Arch; here it is a
+ * run-time value, N % 16 == 0) and the reduction length is config.hidden.
+ * input != NULL: quantise `input` into activation_codes/scales, then project (the
+ * reference's two launches).  input == NULL: activation_codes/scales already hold the
+ * fused producer's output and only the projection runs.
+ * Admitted rows: 1 <= rows <= config.max_rows; anything else is TK100_ERR_LAUNCH. */
+TK100_API tk100_status tk100_fp8_qkv(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
+                           const uint16_t* input, uint8_t* activation_codes,
+                           float* activation_scales, const uint8_t* weight_codes,
+                           const uint16_t* weight_scales, uint16_t* output);
+TK100_API tk100_status tk100_fp8_gdn_input(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
+                                 const uint16_t* input, uint8_t* activation_codes,
+                                 float* activation_scales, const uint8_t* weight_codes,
+                                 const uint16_t* weight_scales, uint16_t* output);
+/* Same operator for any reduction length `columns` (% 128 == 0): the GDN-output and
+ * dense-FP8 down planes (tuisko-kernels-sm120/src/fp8/gdn_output.rs:38-76, fp8/down.rs:197-207). */
+TK100_API tk100_status tk100_fp8_projection(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
+                                  int columns, const uint16_t* input, uint8_t* activation_codes,
+                                  float* activation_scales, const uint8_t* weight_codes,
+                                  const uint16_t* weight_scales, uint16_t* output);
+
+/* LmHeadOp::launch (tuisko-kernels-sm120/src/fp8/projection.rs:751-793) with the greedy
+ * selection of tuisko-engine/src/sampling.rs:162-173 folded into the same kernel.
+ * vocab_rows / vocab_offset describe this rank's contiguous shard of the vocabulary
+ * (248320 / 0 on one GPU).  output (BF16 logits [rows, vocab_rows]) is the reference's
+ * plane; logits_f32 and pairs are optional (NULL to skip).  argmax_scratch is a
+ * caller-owned array of `rows` 64-bit words that must be zero before the first launch;
+ * every launch leaves it zero again.  pairs[i].index is a global vocabulary index. */
+TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,
+                               int vocab_offset, const uint16_t* input, uint8_t* activation_codes,
+                               float* activation_scales, const uint8_t* weight_codes,
+                               const uint16_t* weight_scales, uint16_t* output, float* logits_f32,
+                               uint64_t* argmax_scratch, tk100_argmax_pair* pairs);
+
+/* Reduces the gathered per-shard pairs [shards, rows] to [rows] with the same rule as
+ * greedy_index (first maximum in total order; lowest global index on ties). */
+TK100_API tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, int shards,
+                                const tk100_argmax_pair* gathered, tk100_argmax_pair* output);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* TUISKO_SM100_H_ */

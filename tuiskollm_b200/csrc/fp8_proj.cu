@@ -1,0 +1,377 @@
+// FP8-E4M3 projection  out[m, n] = bf16( (sum_k a[m,k] * w[n,k]) * a_scale[m] * w_scale[n] )
+// for the QKV, GDN-input and LM-head planes, any 1 <= M, on the tcgen05 tensor cores.
+//
+// The reference computes this on CUDA cores, one warp per two weight rows, decoding
+// every weight byte in registers (tuisko-kernels-sm120/src/device/fp8_projection.rs:190-354)
+// and has one mma.sync route for exactly 16 tokens (:394-603).  Here the weight plane is
+// the 128-row UMMA operand ("swap-AB"): a CTA owns 128 weight rows x BLOCK_TOK tokens,
+// TMA streams 128-row x 128-byte weight tiles (128-byte swizzle) and the matching
+// activation-code tile through a shared-memory ring, one thread issues
+// tcgen05.mma kind::f8f6f4 into a TMEM accumulator (lane = weight row, column = token)
+// and four warps read it back with tcgen05.ld for the scale epilogue.  No CUDA core
+// touches a weight byte, so decode shapes are bounded by HBM alone.
+//
+// Small planes do not fill 148 SMs with 128-row tiles, so K can be split over
+// gridDim.z: every split writes its fp32 partial tile to scratch, the last CTA to
+// arrive (ticket counter) adds the partials in split order -- a fixed order, so the
+// result is bit-reproducible -- applies the epilogue and re-arms the counter.
+//
+// LM head: the same epilogue also folds a greedy argmax.  Key = the BF16-rounded
+// logit in IEEE total order, ties to the lowest index, exactly the host rule at
+// tuisko-engine/src/sampling.rs:162-173: 64-bit atomicMax on (key << 32 | ~index).
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tk100 {
+
+namespace {
+
+constexpr int kTileRows = 128;   // weight rows per CTA (UMMA M)
+constexpr int kTileKBytes = 128; // K bytes per stage (one 128-byte swizzle row)
+constexpr int kWStageBytes = kTileRows * kTileKBytes;
+constexpr int kThreads = 192;    // warp 0: TMA, warp 1: UMMA + TMEM, warps 2-5: epilogue
+constexpr int kEpilogueThreads = 128;
+
+__host__ __device__ constexpr int stages_for(int block_tok) {
+  return block_tok <= 16 ? 6 : block_tok <= 32 ? 5 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
+}
+
+template <int BLOCK_TOK>
+struct Control {
+  uint64_t full[stages_for(BLOCK_TOK)];
+  uint64_t empty[stages_for(BLOCK_TOK)];
+  uint64_t tmem_full;
+  unsigned long long red[BLOCK_TOK];  // per-token argmax keys of this CTA
+  float a_scale[BLOCK_TOK];
+  uint32_t tmem_base;
+  uint32_t is_last;
+};
+
+template <int BLOCK_TOK>
+__host__ __device__ constexpr size_t smem_bytes_for() {
+  return 1024 /* alignment slack */ +
+         static_cast<size_t>(stages_for(BLOCK_TOK)) * (kWStageBytes + BLOCK_TOK * kTileKBytes) +
+         sizeof(Control<BLOCK_TOK>);
+}
+
+__device__ __forceinline__ void epilogue_barrier() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+}
+
+// IEEE total-order key of an f32 bit pattern: larger key <=> greater under total_cmp.
+__device__ __forceinline__ uint32_t total_order_key(uint32_t bits) {
+  return bits ^ ((bits & 0x80000000u) ? 0xffffffffu : 0x80000000u);
+}
+
+template <int BLOCK_TOK>
+__global__ void __launch_bounds__(kThreads)
+    fp8_projection_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                          const __grid_constant__ CUtensorMap tmap_a, const Fp8ProjParams p) {
+  constexpr int STAGES = stages_for(BLOCK_TOK);
+  constexpr int A_STAGE_BYTES = BLOCK_TOK * kTileKBytes;
+  constexpr int STAGE_BYTES = kWStageBytes + A_STAGE_BYTES;
+  constexpr uint32_t TMEM_COLS = BLOCK_TOK < 32 ? 32 : BLOCK_TOK;
+  constexpr uint32_t IDESC = umma_idesc_e4m3(kTileRows, BLOCK_TOK);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  Control<BLOCK_TOK>* ctl = reinterpret_cast<Control<BLOCK_TOK>*>(smem + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  const int kb_total = p.k / kTileKBytes;
+  const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / p.splits);
+  const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / p.splits);
+  const int nkb = kb_end - kb_begin;
+
+  // A wait that timed out earlier in this stream has already made the results invalid:
+  // later CTAs leave at once instead of queueing more multi-second waits.
+  if (threadIdx.x == 0) ctl->is_last = *reinterpret_cast<volatile uint32_t*>(p.status);
+  __syncthreads();
+  if (ctl->is_last & STATUS_WAIT_TIMEOUT) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    mbar_init(&ctl->tmem_full, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_w);
+    prefetch_tensormap(&tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();  // weights are streamed once
+      const uint64_t pol_a = l2_policy_evict_last();   // activation codes are re-read by every CTA
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
+        if (!ok) break;
+        uint8_t* stage = smem + s * STAGE_BYTES;
+        mbar_arrive_expect_tx(&ctl->full[s], STAGE_BYTES);
+        const int kbyte = (kb_begin + i) * kTileKBytes;
+        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kTileRows, pol_w);
+        tma_load_2d(stage + kWStageBytes, &tmap_a, &ctl->full[s], kbyte, tile_m * BLOCK_TOK, pol_a);
+      }
+      if (!ok) {
+        // Give copies already in flight time to land before shared memory is released.
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- UMMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&ctl->full[s], phase, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t w_addr = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t desc_w = umma_desc_sw128(w_addr);
+        const uint64_t desc_a = umma_desc_sw128(w_addr + kWStageBytes);
+#pragma unroll
+        for (int k4 = 0; k4 < kTileKBytes / 32; ++k4) {
+          // +2 in the address field = +32 bytes along K inside the swizzled row
+          umma_f8f6f4(tmem, desc_w + 2 * k4, desc_a + 2 * k4, IDESC, (i | k4) != 0);
+        }
+        umma_commit(&ctl->empty[s]);  // frees the stage once these MMAs have read it
+      }
+      umma_commit(&ctl->tmem_full);  // accumulator complete (also releases the epilogue on error)
+    }
+  } else {
+    // ----------------------------------------------------------------- epilogue
+    const int et = threadIdx.x - 64;  // 0..127
+    const int quad = warp & 3;        // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    const int n = tile_n * kTileRows + row_in_tile;
+    const bool row_ok = n < p.out_rows;
+    const int tok0 = tile_m * BLOCK_TOK;
+    const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
+    const bool want_argmax = p.argmax_keys != nullptr;
+
+    for (int j = et; j < BLOCK_TOK; j += kEpilogueThreads) {
+      ctl->a_scale[j] = (j < valid_tok) ? p.act_scales[tok0 + j] : 0.0f;
+      ctl->red[j] = 0ull;
+    }
+    const float w_scale = row_ok ? bf16_bits_to_f32(p.w_scales[n]) : 0.0f;
+    epilogue_barrier();
+
+    mbar_wait(&ctl->tmem_full, 0, p.status);
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+
+    // Final value for (token tok0 + j, weight row n) from its fp32 accumulator.
+    auto emit = [&](int j, float acc) {
+      const float v = __fmul_rn(__fmul_rn(acc, ctl->a_scale[j]), w_scale);
+      const uint32_t b = f32_to_bf16_bits(v);
+      const size_t o = static_cast<size_t>(tok0 + j) * p.out_rows + n;
+      if (row_ok) {
+        if (p.out) p.out[o] = static_cast<uint16_t>(b);
+        if (p.logits_f32) p.logits_f32[o] = v;
+      }
+      if (want_argmax) {
+        unsigned long long packed = 0ull;
+        if (row_ok) {
+          if ((b & 0x7f80u) == 0x7f80u) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
+          packed = (static_cast<unsigned long long>(total_order_key(b << 16)) << 32) |
+                   static_cast<unsigned long long>(0xffffffffu -
+                                                   static_cast<uint32_t>(p.vocab_offset + n));
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) {
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, packed, o2);
+          packed = other > packed ? other : packed;
+        }
+        if (lane == 0) atomicMax(&ctl->red[j], packed);
+      }
+    };
+
+    if (p.splits == 1) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+        if (c0 >= valid_tok) break;  // warp-uniform
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok) emit(c0 + j, __uint_as_float(r[j]));
+        }
+      }
+    } else {
+      // Publish this split's partial tile: [split][tile_m][tile_n][token][row].
+      const size_t tile_index =
+          (static_cast<size_t>(split) * gridDim.y + tile_m) * gridDim.x + tile_n;
+      float* mine = p.partials + tile_index * (BLOCK_TOK * kTileRows) + row_in_tile;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+        if (c0 >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok) __stcg(mine + (c0 + j) * kTileRows, __uint_as_float(r[j]));
+        }
+      }
+      __threadfence();
+      epilogue_barrier();
+      if (et == 0) {
+        unsigned int* counter = p.counters + tile_m * gridDim.x + tile_n;
+        const unsigned int ticket = atomicAdd(counter, 1u);
+        const bool last = ticket == static_cast<unsigned int>(p.splits - 1);
+        if (last) *counter = 0u;  // re-armed for the next launch
+        ctl->is_last = last ? 1u : 0u;
+      }
+      epilogue_barrier();
+      if (ctl->is_last) {
+        __threadfence();
+        const size_t split_stride =
+            static_cast<size_t>(gridDim.y) * gridDim.x * (BLOCK_TOK * kTileRows);
+        const float* base = p.partials +
+                            (static_cast<size_t>(tile_m) * gridDim.x + tile_n) *
+                                (BLOCK_TOK * kTileRows) +
+                            row_in_tile;
+#pragma unroll 1
+        for (int j = 0; j < valid_tok; ++j) {
+          float acc = 0.0f;
+          for (int s = 0; s < p.splits; ++s) {
+            acc = __fadd_rn(acc, __ldcg(base + s * split_stride + j * kTileRows));
+          }
+          emit(j, acc);
+        }
+      }
+    }
+
+    if (want_argmax && (p.splits == 1 || ctl->is_last)) {
+      epilogue_barrier();
+      for (int j = et; j < valid_tok; j += kEpilogueThreads) {
+        const unsigned long long best = ctl->red[j];
+        if (best != 0ull) atomicMax(p.argmax_keys + tok0 + j, best);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+__global__ void argmax_finalize_kernel(int rows, unsigned long long* keys, ArgmaxPair* pairs) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows) return;
+  const unsigned long long packed = keys[t];
+  keys[t] = 0ull;
+  const uint32_t key = static_cast<uint32_t>(packed >> 32);
+  const uint32_t bits = key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu);
+  ArgmaxPair out;
+  out.value = __uint_as_float(bits);
+  out.index = packed == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(packed));
+  pairs[t] = out;
+}
+
+__global__ void argmax_merge_kernel(int rows, int shards, const ArgmaxPair* gathered,
+                                    ArgmaxPair* out) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows) return;
+  unsigned long long best = 0ull;
+  for (int s = 0; s < shards; ++s) {
+    const ArgmaxPair c = gathered[static_cast<size_t>(s) * rows + t];
+    if (c.index < 0) continue;
+    const unsigned long long packed =
+        (static_cast<unsigned long long>(total_order_key(__float_as_uint(c.value))) << 32) |
+        static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(c.index));
+    best = packed > best ? packed : best;
+  }
+  const uint32_t key = static_cast<uint32_t>(best >> 32);
+  ArgmaxPair o;
+  o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
+  o.index = best == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(best));
+  out[t] = o;
+}
+
+template <int BLOCK_TOK>
+cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
+                       const Fp8ProjParams& p) {
+  dim3 grid((p.out_rows + kTileRows - 1) / kTileRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK,
+            p.splits);
+  fp8_projection_kernel<BLOCK_TOK>
+      <<<grid, kThreads, smem_bytes_for<BLOCK_TOK>(), stream>>>(tmap_w, tmap_a, p);
+  return cudaGetLastError();
+}
+
+template <int BLOCK_TOK>
+cudaError_t prepare_one() {
+  return cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(smem_bytes_for<BLOCK_TOK>()));
+}
+
+}  // namespace
+
+size_t fp8_projection_smem_bytes(int block_tok) {
+  switch (block_tok) {
+    case 16: return smem_bytes_for<16>();
+    case 32: return smem_bytes_for<32>();
+    case 64: return smem_bytes_for<64>();
+    case 128: return smem_bytes_for<128>();
+    default: return smem_bytes_for<256>();
+  }
+}
+
+int fp8_projection_stages(int block_tok) { return stages_for(block_tok); }
+
+cudaError_t fp8_projection_prepare() {
+  cudaError_t e;
+  if ((e = prepare_one<16>()) != cudaSuccess) return e;
+  if ((e = prepare_one<32>()) != cudaSuccess) return e;
+  if ((e = prepare_one<64>()) != cudaSuccess) return e;
+  if ((e = prepare_one<128>()) != cudaSuccess) return e;
+  return prepare_one<256>();
+}
+
+cudaError_t launch_fp8_projection(cudaStream_t stream, int block_tok, const CUtensorMap& tmap_w,
+                                  const CUtensorMap& tmap_a, const Fp8ProjParams& p) {
+  switch (block_tok) {
+    case 16: return launch_one<16>(stream, tmap_w, tmap_a, p);
+    case 32: return launch_one<32>(stream, tmap_w, tmap_a, p);
+    case 64: return launch_one<64>(stream, tmap_w, tmap_a, p);
+    case 128: return launch_one<128>(stream, tmap_w, tmap_a, p);
+    case 256: return launch_one<256>(stream, tmap_w, tmap_a, p);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long long* keys,
+                                   ArgmaxPair* pairs) {
+  argmax_finalize_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(rows, keys, pairs);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,
+                                const ArgmaxPair* gathered, ArgmaxPair* out) {
+  argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(rows, shards, gathered, out);
+  return cudaGetLastError();
+}
+
+}  // namespace tk100

@@ -1,0 +1,56 @@
+// Internal launch interface between the operator layer (ops.cu) and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tk100 {
+
+// ---------------------------------------------------------------- norm_quant.cu
+// threads/chunks for a row of `hidden` BF16 values; false when the row is not admitted.
+bool norm_geometry(int hidden, int* threads, int* chunks);
+
+// One launch covering any of: residual add (branch != null), RMSNorm
+// (normalized_out != null) and E4M3 quantisation (codes != null).
+cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, const uint16_t* x,
+                                 const uint16_t* branch, const uint16_t* weight,
+                                 uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
+                                 float* scales, float eps, uint32_t* status);
+
+// ------------------------------------------------------------------ fp8_proj.cu
+struct Fp8ProjParams {
+  int rows;       // active tokens M
+  int out_rows;   // weight rows N (this shard)
+  int k;          // reduction length, multiple of 128
+  int splits;     // K splits (grid.z)
+  const float* act_scales;      // [rows]
+  const uint16_t* w_scales;     // [out_rows] BF16
+  uint16_t* out;                // [rows, out_rows] BF16, may be null for the LM head
+  float* logits_f32;            // [rows, out_rows] or null
+  unsigned long long* argmax_keys;  // [rows] packed (key, ~index) or null
+  int vocab_offset;             // global index of this shard's row 0
+  float* partials;              // split-K scratch
+  unsigned int* counters;       // one per output tile, zero between launches
+  uint32_t* status;
+};
+
+// block_tok is the token tile (16, 32, 64, 128 or 256).
+cudaError_t launch_fp8_projection(cudaStream_t stream, int block_tok, const CUtensorMap& tmap_w,
+                                  const CUtensorMap& tmap_a, const Fp8ProjParams& p);
+size_t fp8_projection_smem_bytes(int block_tok);
+int fp8_projection_stages(int block_tok);
+cudaError_t fp8_projection_prepare();  // sets the dynamic shared-memory attributes once
+
+struct ArgmaxPair {
+  float value;
+  int32_t index;
+};
+// keys -> pairs, and clears the keys for the next launch.
+cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long long* keys,
+                                   ArgmaxPair* pairs);
+// [shards, rows] pairs -> [rows] pairs with the first-maximum rule.
+cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,
+                                const ArgmaxPair* gathered, ArgmaxPair* out);
+
+}  // namespace tk100

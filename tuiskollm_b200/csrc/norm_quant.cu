@@ -1,0 +1,194 @@
+// Fused residual-add + zero-centred RMSNorm + per-token activation quantisation.
+//
+// One CTA owns one token row and keeps it in registers from the first load to the
+// last store: x (+ branch) is read once, the rounded residual, the normalised row,
+// the E4M3 codes and the fp32 scale are written once.  The reference runs this as
+// three launches that each re-read the row from global memory
+// (tuisko-kernels-sm120/src/residual_norm.rs:155-226 followed by
+// tuisko-kernels-sm120/src/device/fp8_projection.rs:54-126).
+//
+// Numeric contract (bit-exact parts marked *):
+//   res  = bf16_rn(f32(x) + f32(branch))                                  *
+//   r    = 1/sqrt(sum(res^2)/H + eps), fp32, fixed summation order
+//   y    = bf16_rn(res * r * (1 + w)), evaluated left to right in fp32
+//   amax = max |y|; scale = amax == 0 ? 1 : amax / 448   (IEEE fp32 divide)   *
+//   code = e4m3_rn_satfinite(y / scale)                  (IEEE fp32 divide)   *
+// The starred results are bit-exact functions of their inputs; `codes`/`scale`
+// are exact with respect to the normalised row this same kernel wrote.
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tk100 {
+
+namespace {
+
+constexpr int kMaxChunks = 4;  // 16-byte chunks (8 BF16) per thread
+
+struct alignas(16) Chunk {
+  uint32_t w[4];
+};
+
+template <bool HAS_BRANCH, bool DO_NORM, bool DO_QUANT, int CHUNKS>
+__global__ void __launch_bounds__(1024)
+    resnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ branch,
+                         const uint16_t* __restrict__ weight, uint16_t* __restrict__ residual_out,
+                         uint16_t* __restrict__ normalized_out, uint8_t* __restrict__ codes,
+                         float* __restrict__ scales, int hidden, float eps, uint32_t* status) {
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const int chunks_per_row = hidden >> 3;
+  const size_t row_off = static_cast<size_t>(row) * hidden;
+
+  float v[CHUNKS][8];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks_per_row) {
+      Chunk a = *reinterpret_cast<const Chunk*>(x + row_off + c * 8);
+      if (HAS_BRANCH) {
+        Chunk b = *reinterpret_cast<const Chunk*>(branch + row_off + c * 8);
+        Chunk r;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __fadd_rn(bf16x2_lo(a.w[j]), bf16x2_lo(b.w[j]));
+          const float hi = __fadd_rn(bf16x2_hi(a.w[j]), bf16x2_hi(b.w[j]));
+          r.w[j] = pack_bf16x2(lo, hi);
+        }
+        *reinterpret_cast<Chunk*>(residual_out + row_off + c * 8) = r;
+        a = r;  // the norm consumes the rounded residual
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[i][2 * j] = bf16x2_lo(a.w[j]);
+        v[i][2 * j + 1] = bf16x2_hi(a.w[j]);
+      }
+      if (DO_NORM) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum = __fmaf_rn(v[i][j], v[i][j], sum);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    }
+  }
+
+  float amax = 0.0f;
+  if (DO_NORM) {
+    sum = block_reduce<false>(sum, scratch);
+    const float mean = __fdiv_rn(sum, static_cast<float>(hidden));
+    const float inv_rms = __frsqrt_rn(__fadd_rn(mean, eps));
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < chunks_per_row) {
+        const Chunk wv = *reinterpret_cast<const Chunk*>(weight + c * 8);
+        Chunk o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __fmul_rn(__fmul_rn(v[i][2 * j], inv_rms),
+                                     __fadd_rn(1.0f, bf16x2_lo(wv.w[j])));
+          const float hi = __fmul_rn(__fmul_rn(v[i][2 * j + 1], inv_rms),
+                                     __fadd_rn(1.0f, bf16x2_hi(wv.w[j])));
+          o.w[j] = pack_bf16x2(lo, hi);
+          v[i][2 * j] = bf16x2_lo(o.w[j]);  // keep the rounded value for the quantiser
+          v[i][2 * j + 1] = bf16x2_hi(o.w[j]);
+        }
+        *reinterpret_cast<Chunk*>(normalized_out + row_off + c * 8) = o;
+      }
+    }
+  }
+
+  if (DO_QUANT) {
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    }
+    amax = block_reduce<true>(amax, scratch);
+    if (!(amax <= 3.0e38f) && threadIdx.x == 0) atomicOr(status, STATUS_NONFINITE_INPUT);
+    const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 448.0f);
+    if (threadIdx.x == 0) scales[row] = scale;
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < chunks_per_row) {
+        uint32_t q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          q[j] = f32x2_to_e4m3x2(__fdiv_rn(v[i][2 * j], scale), __fdiv_rn(v[i][2 * j + 1], scale));
+        }
+        uint2 packed;
+        packed.x = q[0] | (q[1] << 16);
+        packed.y = q[2] | (q[3] << 16);
+        *reinterpret_cast<uint2*>(codes + row_off + c * 8) = packed;
+      }
+    }
+  }
+}
+
+template <bool HAS_BRANCH, bool DO_NORM, bool DO_QUANT>
+cudaError_t launch_chunks(cudaStream_t stream, int rows, int hidden, int threads, int chunks,
+                          const uint16_t* x, const uint16_t* branch, const uint16_t* weight,
+                          uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
+                          float* scales, float eps, uint32_t* status) {
+#define TK100_LAUNCH(C)                                                                        \
+  resnorm_quant_kernel<HAS_BRANCH, DO_NORM, DO_QUANT, C><<<rows, threads, 0, stream>>>(        \
+      x, branch, weight, residual_out, normalized_out, codes, scales, hidden, eps, status)
+  switch (chunks) {
+    case 1: TK100_LAUNCH(1); break;
+    case 2: TK100_LAUNCH(2); break;
+    case 3: TK100_LAUNCH(3); break;
+    default: TK100_LAUNCH(4); break;
+  }
+#undef TK100_LAUNCH
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool norm_geometry(int hidden, int* threads, int* chunks) {
+  if (hidden <= 0 || (hidden & 7) != 0) return false;
+  const int row_chunks = hidden >> 3;
+  // One chunk per thread while the row fits a 1024-thread CTA, warp-multiple CTAs.
+  int c = (row_chunks + 1023) / 1024;
+  if (c > kMaxChunks) return false;
+  // Prefer CTAs of at most 640 threads (three co-resident per SM) when that costs
+  // no extra chunk, e.g. 5120 -> 640 x 1, 17408 -> 544 x 4.
+  int t = (row_chunks + c - 1) / c;
+  if (t > 704 && c < kMaxChunks) {
+    c = (row_chunks + 639) / 640;
+    if (c > kMaxChunks) c = kMaxChunks;
+    t = (row_chunks + c - 1) / c;
+  }
+  t = (t + 31) & ~31;
+  if (t > 1024) return false;
+  *threads = t;
+  *chunks = c;
+  return true;
+}
+
+cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, const uint16_t* x,
+                                 const uint16_t* branch, const uint16_t* weight,
+                                 uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
+                                 float* scales, float eps, uint32_t* status) {
+  int threads = 0, chunks = 0;
+  if (!norm_geometry(hidden, &threads, &chunks)) return cudaErrorInvalidValue;
+  const bool has_branch = branch != nullptr;
+  const bool do_norm = normalized_out != nullptr;
+  const bool do_quant = codes != nullptr;
+#define TK100_CASE(B, N, Q)                                                                      \
+  if (has_branch == B && do_norm == N && do_quant == Q)                                          \
+  return launch_chunks<B, N, Q>(stream, rows, hidden, threads, chunks, x, branch, weight,        \
+                                residual_out, normalized_out, codes, scales, eps, status)
+  TK100_CASE(true, true, true);
+  TK100_CASE(true, true, false);
+  TK100_CASE(false, true, true);
+  TK100_CASE(false, true, false);
+  TK100_CASE(false, false, true);
+#undef TK100_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace tk100

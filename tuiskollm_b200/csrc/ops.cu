@@ -1,0 +1,515 @@
+// Operator layer and the extern "C" boundary.
+#include "ops.hpp"
+
+#include <cudaTypedefs.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "ptx.cuh"
+
+namespace tk100 {
+
+namespace {
+
+thread_local std::string g_create_error;
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int env_int(const char* name) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : 0;
+}
+
+}  // namespace
+
+// --------------------------------------------------------------------- Context
+
+Status Context::check(cudaError_t e, const char* operation) {
+  if (e == cudaSuccess) return TK100_OK;
+  return fail(TK100_ERR_DRIVER,
+              std::string("[gpu.driver] ") + operation + ": " + cudaGetErrorString(e));
+}
+
+Status Context::create(const tk100_config& in, Context** out, std::string* error) {
+  tk100_config cfg = in;
+  if (cfg.abi_version != TK100_ABI_VERSION) {
+    *error = "[gpu.module] tk100_config.abi_version does not match this library";
+    return TK100_ERR_MODULE;
+  }
+  if (cfg.hidden == 0) cfg.hidden = 5120;
+  if (cfg.intermediate == 0) cfg.intermediate = 17408;
+  if (cfg.rms_norm_epsilon == 0.0f) cfg.rms_norm_epsilon = 1.0e-6f;
+  if (cfg.max_rows == 0) cfg.max_rows = 2048;
+  if (cfg.workspace_bytes == 0) cfg.workspace_bytes = 64ull << 20;
+  // tuisko-kernels-sm120/src/fp8/projection.rs require_fp8_geometry: the reduction
+  // length must tile; here one TMA stage is 128 bytes of K.
+  int threads = 0, chunks = 0;
+  if (cfg.hidden % 128 != 0 || !norm_geometry(static_cast<int>(cfg.hidden), &threads, &chunks)) {
+    *error = "[gpu.launch] hidden size " + std::to_string(cfg.hidden) +
+             " is not admitted (multiple of 128, at most 32768)";
+    return TK100_ERR_LAUNCH;
+  }
+
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count <= 0) {
+    *error = std::string("[gpu.driver] no CUDA device: ") + cudaGetErrorString(e);
+    return TK100_ERR_DRIVER;
+  }
+  if (cfg.device < 0 || cfg.device >= count) {
+    *error = "[gpu.context] device ordinal " + std::to_string(cfg.device) + " out of range";
+    return TK100_ERR_CONTEXT;
+  }
+  if ((e = cudaSetDevice(cfg.device)) != cudaSuccess) {
+    *error = std::string("[gpu.driver] cudaSetDevice: ") + cudaGetErrorString(e);
+    return TK100_ERR_DRIVER;
+  }
+  cudaDeviceProp prop{};
+  if ((e = cudaGetDeviceProperties(&prop, cfg.device)) != cudaSuccess) {
+    *error = std::string("[gpu.driver] cudaGetDeviceProperties: ") + cudaGetErrorString(e);
+    return TK100_ERR_DRIVER;
+  }
+  if (prop.major != 10) {
+    *error = "[gpu.module] device has compute capability " + std::to_string(prop.major) + "." +
+             std::to_string(prop.minor) + ", expected 10.x (sm_100a kernels only)";
+    return TK100_ERR_MODULE;
+  }
+
+  Context* ctx = new (std::nothrow) Context();
+  if (!ctx) {
+    *error = "[gpu.driver] out of host memory";
+    return TK100_ERR_DRIVER;
+  }
+  ctx->config_ = cfg;
+  ctx->sm_count_ = prop.multiProcessorCount;
+  ctx->forced_splits_ = env_int("TK100_SPLITS");
+  ctx->forced_block_tok_ = env_int("TK100_BLOCK_TOK");
+
+  cudaDriverEntryPointQueryResult q;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_fn_, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !ctx->encode_fn_) {
+    *error = "[gpu.module] cuTensorMapEncodeTiled is not available from this driver";
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
+  if ((e = fp8_projection_prepare()) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the FP8 projection routes: ") +
+             cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
+
+  ctx->partial_bytes_ = cfg.workspace_bytes;
+  ctx->counter_count_ = 1 << 16;
+  bool ok = cudaMalloc(&ctx->partials_, ctx->partial_bytes_) == cudaSuccess &&
+            cudaMalloc(&ctx->counters_, ctx->counter_count_ * sizeof(unsigned int)) ==
+                cudaSuccess &&
+            cudaMalloc(&ctx->status_, sizeof(uint32_t)) == cudaSuccess &&
+            cudaMemset(ctx->counters_, 0, ctx->counter_count_ * sizeof(unsigned int)) ==
+                cudaSuccess &&
+            cudaMemset(ctx->status_, 0, sizeof(uint32_t)) == cudaSuccess &&
+            cudaDeviceSynchronize() == cudaSuccess;
+  if (!ok) {
+    *error = std::string("[gpu.arena] allocating the context scratch: ") +
+             cudaGetErrorString(cudaGetLastError());
+    delete ctx;
+    return TK100_ERR_ARENA;
+  }
+  *out = ctx;
+  return TK100_OK;
+}
+
+Context::~Context() {
+  if (partials_) cudaFree(partials_);
+  if (counters_) cudaFree(counters_);
+  if (status_) cudaFree(status_);
+}
+
+Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                           CUtensorMap* out) {
+  char key[96];
+  std::snprintf(key, sizeof key, "%p:%llu:%llu:%u", base, static_cast<unsigned long long>(rows),
+                static_cast<unsigned long long>(row_bytes), box_rows);
+  auto it = maps_.find(key);
+  if (it != maps_.end()) {
+    *out = it->second;
+    return TK100_OK;
+  }
+  auto encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(encode_fn_);
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128u, box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(TK100_ERR_DRIVER, "[gpu.driver] cuTensorMapEncodeTiled failed with CUresult " +
+                                      std::to_string(static_cast<int>(r)));
+  }
+  if (maps_.size() > 4096) maps_.clear();
+  maps_.emplace(key, map);
+  *out = map;
+  return TK100_OK;
+}
+
+// -------------------------------------------------------------- ResidualNormOp
+
+namespace {
+
+Status check_rows(Context& ctx, const char* what, int rows) {
+  const int max_rows = static_cast<int>(ctx.config().max_rows);
+  if (rows < 1 || rows > max_rows) {
+    return ctx.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + what + " row count " +
+                                          std::to_string(rows) +
+                                          " is outside the admitted routes 1..=" +
+                                          std::to_string(max_rows));
+  }
+  return TK100_OK;
+}
+
+Status check_plane(Context& ctx, const char* what, const char* plane, const void* p,
+                   size_t alignment) {
+  if (p == nullptr) {
+    return ctx.fail(TK100_ERR_LAUNCH,
+                    std::string("[gpu.launch] ") + what + ": " + plane + " plane is null");
+  }
+  if (!aligned(p, alignment)) {
+    return ctx.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + what + ": " + plane +
+                                          " plane is not " + std::to_string(alignment) +
+                                          "-byte aligned");
+  }
+  return TK100_OK;
+}
+
+#define TK100_TRY(expr)                  \
+  do {                                   \
+    Status _s = (expr);                  \
+    if (_s != TK100_OK) return _s;       \
+  } while (0)
+
+}  // namespace
+
+Status ResidualNormOp::launch_plain(cudaStream_t stream, int batch, const uint16_t* input,
+                                    const uint16_t* weight, uint16_t* output) {
+  TK100_TRY(check_rows(ctx_, "residual norm", batch));
+  TK100_TRY(check_plane(ctx_, "residual norm", "input", input, 16));
+  TK100_TRY(check_plane(ctx_, "residual norm", "weight", weight, 16));
+  TK100_TRY(check_plane(ctx_, "residual norm", "output", output, 16));
+  ctx_.count_launch();
+  return ctx_.check(
+      launch_resnorm_quant(stream, batch, static_cast<int>(ctx_.config().hidden), input, nullptr,
+                           weight, nullptr, output, nullptr, nullptr,
+                           ctx_.config().rms_norm_epsilon, ctx_.status_word()),
+      "launching RMSNorm");
+}
+
+Status ResidualNormOp::launch_residual(cudaStream_t stream, int batch,
+                                       const uint16_t* residual_input, const uint16_t* branch,
+                                       const uint16_t* weight, uint16_t* residual_output,
+                                       uint16_t* normalized_output) {
+  TK100_TRY(check_plane(ctx_, "residual norm", "branch", branch, 16));
+  return launch_quantize(stream, batch, residual_input, branch, weight, residual_output,
+                         normalized_output, nullptr, nullptr);
+}
+
+Status ResidualNormOp::launch_quantize(cudaStream_t stream, int batch,
+                                       const uint16_t* residual_input, const uint16_t* branch,
+                                       const uint16_t* weight, uint16_t* residual_output,
+                                       uint16_t* normalized_output, uint8_t* activation_codes,
+                                       float* activation_scales) {
+  TK100_TRY(check_rows(ctx_, "residual norm", batch));
+  TK100_TRY(check_plane(ctx_, "residual norm", "residual input", residual_input, 16));
+  TK100_TRY(check_plane(ctx_, "residual norm", "weight", weight, 16));
+  TK100_TRY(check_plane(ctx_, "residual norm", "normalized output", normalized_output, 16));
+  if (branch) {
+    TK100_TRY(check_plane(ctx_, "residual norm", "branch", branch, 16));
+    TK100_TRY(check_plane(ctx_, "residual norm", "residual output", residual_output, 16));
+  }
+  if (activation_codes || activation_scales) {
+    TK100_TRY(check_plane(ctx_, "residual norm", "activation codes", activation_codes, 128));
+    TK100_TRY(check_plane(ctx_, "residual norm", "activation scales", activation_scales, 4));
+  }
+  ctx_.count_launch();
+  return ctx_.check(
+      launch_resnorm_quant(stream, batch, static_cast<int>(ctx_.config().hidden), residual_input,
+                           branch, weight, branch ? residual_output : nullptr, normalized_output,
+                           activation_codes, activation_scales, ctx_.config().rms_norm_epsilon,
+                           ctx_.status_word()),
+      "launching residual RMSNorm");
+}
+
+// ------------------------------------------------------------- Fp8ProjectionOp
+
+Status Fp8ProjectionOp::quantize(cudaStream_t stream, int rows, int columns,
+                                 const uint16_t* input, uint8_t* activation_codes,
+                                 float* activation_scales) {
+  TK100_TRY(check_rows(ctx_, name_, rows));
+  int threads = 0, chunks = 0;
+  if (!norm_geometry(columns, &threads, &chunks)) {
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name_ + ": " +
+                                           std::to_string(columns) +
+                                           " columns are not admitted (multiple of 8, <= 32768)");
+  }
+  TK100_TRY(check_plane(ctx_, name_, "input", input, 16));
+  TK100_TRY(check_plane(ctx_, name_, "activation codes", activation_codes, 16));
+  TK100_TRY(check_plane(ctx_, name_, "activation scales", activation_scales, 4));
+  ctx_.count_launch();
+  return ctx_.check(launch_resnorm_quant(stream, rows, columns, input, nullptr, nullptr, nullptr,
+                                         nullptr, activation_codes, activation_scales, 0.0f,
+                                         ctx_.status_word()),
+                    "launching the E4M3 activation quantiser");
+}
+
+Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int columns,
+                               const uint16_t* input, uint8_t* activation_codes,
+                               float* activation_scales, const uint8_t* weight_codes,
+                               const uint16_t* weight_scales, uint16_t* output, float* logits_f32,
+                               unsigned long long* argmax_scratch, tk100_argmax_pair* pairs,
+                               int vocab_offset) {
+  TK100_TRY(check_rows(ctx_, name_, rows));
+  if (out_rows < 16 || out_rows % 16 != 0) {
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name_ + ": " +
+                                           std::to_string(out_rows) +
+                                           " output rows are not admitted (multiple of 16)");
+  }
+  if (columns < 128 || columns % 128 != 0) {
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name_ + ": " +
+                                           std::to_string(columns) +
+                                           " columns are not admitted (multiple of 128)");
+  }
+  TK100_TRY(check_plane(ctx_, name_, "activation codes", activation_codes, 128));
+  TK100_TRY(check_plane(ctx_, name_, "activation scales", activation_scales, 4));
+  TK100_TRY(check_plane(ctx_, name_, "weight codes", weight_codes, 128));
+  TK100_TRY(check_plane(ctx_, name_, "weight scales", weight_scales, 2));
+  if (output == nullptr && logits_f32 == nullptr && pairs == nullptr) {
+    return ctx_.fail(TK100_ERR_LAUNCH,
+                     std::string("[gpu.launch] ") + name_ + ": every output plane is null");
+  }
+  if (output) TK100_TRY(check_plane(ctx_, name_, "output", output, 2));
+  if (pairs && argmax_scratch == nullptr) {
+    return ctx_.fail(TK100_ERR_LAUNCH,
+                     std::string("[gpu.launch] ") + name_ + ": argmax scratch plane is null");
+  }
+
+  if (input) TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
+
+  int block_tok = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+  if (ctx_.forced_block_tok() == 16 || ctx_.forced_block_tok() == 32 ||
+      ctx_.forced_block_tok() == 64 || ctx_.forced_block_tok() == 128 ||
+      ctx_.forced_block_tok() == 256) {
+    block_tok = ctx_.forced_block_tok();
+  }
+  const int tiles_n = (out_rows + 127) / 128;
+  const int tiles_m = (rows + block_tok - 1) / block_tok;
+  const long long tiles = static_cast<long long>(tiles_n) * tiles_m;
+  const int kb_total = columns / 128;
+  // Fill the SMs (two CTAs fit per SM up to 64-token tiles) by splitting K when the
+  // plane has few 128-row tiles.
+  const long long slots = static_cast<long long>(ctx_.sm_count()) * (block_tok <= 64 ? 2 : 1);
+  int splits = static_cast<int>(slots / tiles);
+  if (ctx_.forced_splits() > 0) splits = ctx_.forced_splits();
+  if (splits > 8) splits = 8;
+  if (splits > kb_total) splits = kb_total;
+  if (splits < 1) splits = 1;
+  while (splits > 1 &&
+         (static_cast<size_t>(splits) * tiles * block_tok * 128 * sizeof(float) >
+              ctx_.partial_bytes() ||
+          static_cast<size_t>(tiles) > ctx_.counter_count())) {
+    --splits;
+  }
+
+  CUtensorMap map_w, map_a;
+  TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(out_rows),
+                            static_cast<uint64_t>(columns), 128, &map_w));
+  TK100_TRY(ctx_.tensor_map(activation_codes, static_cast<uint64_t>(rows),
+                            static_cast<uint64_t>(columns), static_cast<uint32_t>(block_tok),
+                            &map_a));
+
+  Fp8ProjParams p{};
+  p.rows = rows;
+  p.out_rows = out_rows;
+  p.k = columns;
+  p.splits = splits;
+  p.act_scales = activation_scales;
+  p.w_scales = weight_scales;
+  p.out = output;
+  p.logits_f32 = logits_f32;
+  p.argmax_keys = pairs ? argmax_scratch : nullptr;
+  p.vocab_offset = vocab_offset;
+  p.partials = ctx_.partials();
+  p.counters = ctx_.counters();
+  p.status = ctx_.status_word();
+  ctx_.count_launch();
+  TK100_TRY(ctx_.check(launch_fp8_projection(stream, block_tok, map_w, map_a, p),
+                       "launching the FP8 projection"));
+  if (pairs) {
+    ctx_.count_launch();
+    TK100_TRY(ctx_.check(launch_argmax_finalize(stream, rows, argmax_scratch,
+                                                reinterpret_cast<ArgmaxPair*>(pairs)),
+                         "launching the argmax finalizer"));
+  }
+  return TK100_OK;
+}
+
+}  // namespace tk100
+
+// ------------------------------------------------------------------- C boundary
+
+using tk100::Context;
+
+struct tk100_ctx {
+  Context* impl;
+};
+
+extern "C" {
+
+tk100_status tk100_create(const tk100_config* config, tk100_ctx** out) {
+  if (!config || !out) {
+    tk100::g_create_error = "[gpu.launch] tk100_create: null argument";
+    return TK100_ERR_LAUNCH;
+  }
+  Context* impl = nullptr;
+  std::string error;
+  tk100_status s = Context::create(*config, &impl, &error);
+  if (s != TK100_OK) {
+    tk100::g_create_error = error;
+    return s;
+  }
+  *out = new tk100_ctx{impl};
+  return TK100_OK;
+}
+
+void tk100_destroy(tk100_ctx* ctx) {
+  if (!ctx) return;
+  delete ctx->impl;
+  delete ctx;
+}
+
+const char* tk100_last_error(const tk100_ctx* ctx) {
+  return ctx ? ctx->impl->last_error().c_str() : tk100::g_create_error.c_str();
+}
+
+tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* word) {
+  if (!ctx || !word) return TK100_ERR_LAUNCH;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(word, ctx->impl->status_word(), sizeof(uint32_t),
+                                  cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(ctx->impl->status_word(), 0, sizeof(uint32_t), s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  return ctx->impl->check(e, "reading the device status word");
+}
+
+uint64_t tk100_launch_count(const tk100_ctx* ctx) { return ctx ? ctx->impl->launches() : 0; }
+
+tk100_status tk100_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
+                            const uint16_t* weight, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::ResidualNormOp(*ctx->impl)
+      .launch_plain(static_cast<cudaStream_t>(stream), rows, input, weight, output);
+}
+
+tk100_status tk100_residual_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                     const uint16_t* residual_input, const uint16_t* branch,
+                                     const uint16_t* weight, uint16_t* residual_output,
+                                     uint16_t* normalized_output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::ResidualNormOp(*ctx->impl)
+      .launch_residual(static_cast<cudaStream_t>(stream), rows, residual_input, branch, weight,
+                       residual_output, normalized_output);
+}
+
+tk100_status tk100_residual_rms_norm_quantize(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                              const uint16_t* residual_input,
+                                              const uint16_t* branch, const uint16_t* weight,
+                                              uint16_t* residual_output,
+                                              uint16_t* normalized_output,
+                                              uint8_t* activation_codes,
+                                              float* activation_scales) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (!activation_codes || !activation_scales) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH,
+                           "[gpu.launch] residual norm: activation code/scale plane is null");
+  }
+  return tk100::ResidualNormOp(*ctx->impl)
+      .launch_quantize(static_cast<cudaStream_t>(stream), rows, residual_input, branch, weight,
+                       residual_output, normalized_output, activation_codes, activation_scales);
+}
+
+tk100_status tk100_quantize_activation_e4m3(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                            int columns, const uint16_t* input,
+                                            uint8_t* activation_codes, float* activation_scales) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::Fp8ProjectionOp(*ctx->impl, "FP8 activation quantiser")
+      .quantize(static_cast<cudaStream_t>(stream), rows, columns, input, activation_codes,
+                activation_scales);
+}
+
+tk100_status tk100_fp8_qkv(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
+                           const uint16_t* input, uint8_t* activation_codes,
+                           float* activation_scales, const uint8_t* weight_codes,
+                           const uint16_t* weight_scales, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::FullAttentionQkvOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, out_rows,
+              static_cast<int>(ctx->impl->config().hidden), input, activation_codes,
+              activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_fp8_gdn_input(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
+                                 const uint16_t* input, uint8_t* activation_codes,
+                                 float* activation_scales, const uint8_t* weight_codes,
+                                 const uint16_t* weight_scales, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::GdnInputProjectionOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, out_rows,
+              static_cast<int>(ctx->impl->config().hidden), input, activation_codes,
+              activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_fp8_projection(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
+                                  int columns, const uint16_t* input, uint8_t* activation_codes,
+                                  float* activation_scales, const uint8_t* weight_codes,
+                                  const uint16_t* weight_scales, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::Fp8ProjectionOp(*ctx->impl, "FP8 projection")
+      .launch(static_cast<cudaStream_t>(stream), rows, out_rows, columns, input,
+              activation_codes, activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,
+                               int vocab_offset, const uint16_t* input, uint8_t* activation_codes,
+                               float* activation_scales, const uint8_t* weight_codes,
+                               const uint16_t* weight_scales, uint16_t* output, float* logits_f32,
+                               uint64_t* argmax_scratch, tk100_argmax_pair* pairs) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (vocab_offset < 0) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH, "[gpu.launch] FP8 LM head: negative vocab offset");
+  }
+  return tk100::LmHeadOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, vocab_rows,
+              static_cast<int>(ctx->impl->config().hidden), input, activation_codes,
+              activation_scales, weight_codes, weight_scales, output, logits_f32,
+              reinterpret_cast<unsigned long long*>(argmax_scratch), pairs, vocab_offset);
+}
+
+tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, int shards,
+                                const tk100_argmax_pair* gathered, tk100_argmax_pair* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (rows < 1 || shards < 1 || !gathered || !output) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH, "[gpu.launch] argmax merge: bad argument");
+  }
+  ctx->impl->count_launch();
+  return ctx->impl->check(
+      tk100::launch_argmax_merge(static_cast<cudaStream_t>(stream), rows, shards,
+                                 reinterpret_cast<const tk100::ArgmaxPair*>(gathered),
+                                 reinterpret_cast<tk100::ArgmaxPair*>(output)),
+      "launching the argmax merge");
+}
+
+}  // extern "C"

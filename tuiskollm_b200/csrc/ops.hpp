@@ -1,0 +1,116 @@
+// Host-side operator layer: C++ counterparts of the reference's prepared operators
+// (ResidualNormOp, FullAttentionQkvOp, GdnInputProjectionOp, LmHeadOp, Nvfp4SwiGluOp,
+// Nvfp4DownOp) with the same method names, argument order and error behaviour.  The
+// extern "C" functions of include/tuisko_sm100.h are one-line calls into these.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+
+#include "../../include/tuisko_sm100.h"
+#include "kernels.h"
+
+namespace tk100 {
+
+// Result of a launch: the reference's GpuResult<()> flattened to a status code; the
+// message is kept on the context.
+using Status = tk100_status;
+
+class Context {
+ public:
+  static Status create(const tk100_config& config, Context** out, std::string* error);
+  ~Context();
+
+  Status fail(Status code, const std::string& message) {
+    last_error_ = message;
+    return code;
+  }
+  Status check(cudaError_t e, const char* operation);
+  const std::string& last_error() const { return last_error_; }
+
+  // Row-major u8 plane [rows, row_bytes] read through TMA in boxes of
+  // 128 bytes x box_rows with the 128-byte swizzle.  Encoded once per distinct plane.
+  Status tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                    CUtensorMap* out);
+
+  const tk100_config& config() const { return config_; }
+  int sm_count() const { return sm_count_; }
+  float* partials() const { return partials_; }
+  size_t partial_bytes() const { return partial_bytes_; }
+  unsigned int* counters() const { return counters_; }
+  size_t counter_count() const { return counter_count_; }
+  uint32_t* status_word() const { return status_; }
+  int forced_splits() const { return forced_splits_; }
+  int forced_block_tok() const { return forced_block_tok_; }
+  void count_launch(int n = 1) { launches_ += static_cast<uint64_t>(n); }
+  uint64_t launches() const { return launches_; }
+
+ private:
+  Context() = default;
+  tk100_config config_{};
+  int sm_count_ = 0;
+  float* partials_ = nullptr;
+  size_t partial_bytes_ = 0;
+  unsigned int* counters_ = nullptr;
+  size_t counter_count_ = 0;
+  uint32_t* status_ = nullptr;
+  int forced_splits_ = 0;
+  int forced_block_tok_ = 0;
+  uint64_t launches_ = 0;
+  std::string last_error_;
+  void* encode_fn_ = nullptr;
+  std::unordered_map<std::string, CUtensorMap> maps_;
+};
+
+// tuisko-kernels-sm120/src/residual_norm.rs:382-508
+class ResidualNormOp {
+ public:
+  explicit ResidualNormOp(Context& ctx) : ctx_(ctx) {}
+  Status launch_plain(cudaStream_t stream, int batch, const uint16_t* input,
+                      const uint16_t* weight, uint16_t* output);
+  Status launch_residual(cudaStream_t stream, int batch, const uint16_t* residual_input,
+                         const uint16_t* branch, const uint16_t* weight,
+                         uint16_t* residual_output, uint16_t* normalized_output);
+  // Fused producer: norm (+ residual when branch != null) + per-token E4M3 quantisation.
+  Status launch_quantize(cudaStream_t stream, int batch, const uint16_t* residual_input,
+                         const uint16_t* branch, const uint16_t* weight,
+                         uint16_t* residual_output, uint16_t* normalized_output,
+                         uint8_t* activation_codes, float* activation_scales);
+
+ private:
+  Context& ctx_;
+};
+
+// tuisko-kernels-sm120/src/fp8/projection.rs:510-794: one class serves the three planes;
+// `name` only labels error messages ("FP8 QKV", "FP8 GDN input", "FP8 LM head", ...).
+class Fp8ProjectionOp {
+ public:
+  Fp8ProjectionOp(Context& ctx, const char* name) : ctx_(ctx), name_(name) {}
+  Status quantize(cudaStream_t stream, int rows, int columns, const uint16_t* input,
+                  uint8_t* activation_codes, float* activation_scales);
+  Status launch(cudaStream_t stream, int rows, int out_rows, int columns, const uint16_t* input,
+                uint8_t* activation_codes, float* activation_scales, const uint8_t* weight_codes,
+                const uint16_t* weight_scales, uint16_t* output, float* logits_f32 = nullptr,
+                unsigned long long* argmax_scratch = nullptr, tk100_argmax_pair* pairs = nullptr,
+                int vocab_offset = 0);
+
+ private:
+  Context& ctx_;
+  const char* name_;
+};
+
+struct FullAttentionQkvOp : Fp8ProjectionOp {
+  explicit FullAttentionQkvOp(Context& c) : Fp8ProjectionOp(c, "FP8 QKV") {}
+};
+struct GdnInputProjectionOp : Fp8ProjectionOp {
+  explicit GdnInputProjectionOp(Context& c) : Fp8ProjectionOp(c, "FP8 GDN input") {}
+};
+struct LmHeadOp : Fp8ProjectionOp {
+  explicit LmHeadOp(Context& c) : Fp8ProjectionOp(c, "FP8 LM head") {}
+};
+
+}  // namespace tk100

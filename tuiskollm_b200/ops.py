@@ -1,0 +1,186 @@
+"""Python mirror of the reference's prepared operators over the C ABI.
+
+Names, argument order and error classes follow the reference
+(``ResidualNormOp::launch_plain/launch_residual``, ``FullAttentionQkvOp::launch``,
+``GdnInputProjectionOp::launch``, ``LmHeadOp::launch``).  Planes are torch CUDA tensors
+(or raw integer device addresses); BF16 planes may be ``torch.bfloat16`` or ``uint16``/
+``int16`` bit views.  Nothing here computes: every method is one C-ABI call.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+class GpuError(RuntimeError):
+    """Failure with the reference's stable category (``gpu.launch``, ``gpu.driver``, ...)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+        self.code = _lib.STATUS_NAMES.get(status, f"gpu.unknown({status})")
+
+
+def _ptr(t) -> Optional[int]:
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if not t.is_cuda:
+        raise GpuError(4, "[gpu.context] plane is not a CUDA tensor")
+    if not t.is_contiguous():
+        raise GpuError(5, "[gpu.launch] plane is not contiguous")
+    return t.data_ptr()
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+class Context:
+    """Owns one ``tk100_ctx`` (one per GPU / rank)."""
+
+    def __init__(self, device: int = 0, hidden: int = 5120, intermediate: int = 17408,
+                 rms_norm_epsilon: float = 1e-6, max_rows: int = 2048,
+                 workspace_bytes: int = 0):
+        self._lib = _lib.load()
+        cfg = _lib.Config(_lib.ABI_VERSION, device, hidden, intermediate, rms_norm_epsilon,
+                          max_rows, workspace_bytes)
+        handle = C.c_void_p()
+        status = self._lib.tk100_create(C.byref(cfg), C.byref(handle))
+        if status != 0:
+            raise GpuError(status, (self._lib.tk100_last_error(None) or b"").decode())
+        self.handle = handle
+        self.device = device
+        self.hidden = hidden
+        self.intermediate = intermediate
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self._lib.tk100_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, status: int):
+        if status != 0:
+            raise GpuError(status, (self._lib.tk100_last_error(self.handle) or b"").decode())
+
+    def device_status(self, stream=None) -> int:
+        word = C.c_uint32(0)
+        self.check(self._lib.tk100_device_status(self.handle, _stream(stream), C.byref(word)))
+        return word.value
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.tk100_launch_count(self.handle))
+
+
+class ResidualNormOp:
+    """tuisko-kernels-sm120/src/residual_norm.rs:382-508."""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def launch_plain(self, stream, batch, input, weight, output):
+        c = self.ctx
+        c.check(c._lib.tk100_rms_norm(c.handle, _stream(stream), batch, _ptr(input), _ptr(weight),
+                                      _ptr(output)))
+
+    def launch_residual(self, stream, batch, residual_input, branch, weight, residual_output,
+                        normalized_output):
+        c = self.ctx
+        c.check(c._lib.tk100_residual_rms_norm(c.handle, _stream(stream), batch,
+                                               _ptr(residual_input), _ptr(branch), _ptr(weight),
+                                               _ptr(residual_output), _ptr(normalized_output)))
+
+    def launch_quantize(self, stream, batch, residual_input, branch, weight, residual_output,
+                        normalized_output, activation_codes, activation_scales):
+        """Fused producer: (residual add +) RMSNorm + per-token E4M3 quantisation, one kernel."""
+        c = self.ctx
+        c.check(c._lib.tk100_residual_rms_norm_quantize(
+            c.handle, _stream(stream), batch, _ptr(residual_input), _ptr(branch), _ptr(weight),
+            _ptr(residual_output), _ptr(normalized_output), _ptr(activation_codes),
+            _ptr(activation_scales)))
+
+
+class Fp8ProjectionOp:
+    """Generic FP8 projection (any reduction length that is a multiple of 128)."""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def quantize(self, stream, rows, columns, input, activation_codes, activation_scales):
+        c = self.ctx
+        c.check(c._lib.tk100_quantize_activation_e4m3(c.handle, _stream(stream), rows, columns,
+                                                      _ptr(input), _ptr(activation_codes),
+                                                      _ptr(activation_scales)))
+
+    def launch(self, stream, rows, out_rows, columns, input, activation_codes, activation_scales,
+               weight_codes, weight_scales, output):
+        c = self.ctx
+        c.check(c._lib.tk100_fp8_projection(c.handle, _stream(stream), rows, out_rows, columns,
+                                            _ptr(input), _ptr(activation_codes),
+                                            _ptr(activation_scales), _ptr(weight_codes),
+                                            _ptr(weight_scales), _ptr(output)))
+
+
+class FullAttentionQkvOp:
+    """tuisko-kernels-sm120/src/fp8/projection.rs:510-611; ``out_rows`` is a run-time value."""
+
+    _entry = "tk100_fp8_qkv"
+
+    def __init__(self, context: Context, out_rows: int):
+        self.ctx = context
+        self.out_rows = out_rows
+
+    def launch(self, stream, rows, input, activation_codes, activation_scales, weight_codes,
+               weight_scales, output):
+        c = self.ctx
+        fn = getattr(c._lib, self._entry)
+        c.check(fn(c.handle, _stream(stream), rows, self.out_rows, _ptr(input),
+                   _ptr(activation_codes), _ptr(activation_scales), _ptr(weight_codes),
+                   _ptr(weight_scales), _ptr(output)))
+
+
+class GdnInputProjectionOp(FullAttentionQkvOp):
+    """tuisko-kernels-sm120/src/fp8/projection.rs:613-702."""
+
+    _entry = "tk100_fp8_gdn_input"
+
+
+class LmHeadOp:
+    """tuisko-kernels-sm120/src/fp8/projection.rs:704-793 plus the fused greedy argmax.
+
+    ``vocab_rows``/``vocab_offset`` describe this rank's shard of the vocabulary."""
+
+    def __init__(self, context: Context, vocab_rows: int, vocab_offset: int = 0):
+        self.ctx = context
+        self.vocab_rows = vocab_rows
+        self.vocab_offset = vocab_offset
+
+    def launch(self, stream, rows, input, activation_codes, activation_scales, weight_codes,
+               weight_scales, output, logits_f32=None, argmax_scratch=None, pairs=None):
+        c = self.ctx
+        c.check(c._lib.tk100_fp8_lm_head(c.handle, _stream(stream), rows, self.vocab_rows,
+                                         self.vocab_offset, _ptr(input), _ptr(activation_codes),
+                                         _ptr(activation_scales), _ptr(weight_codes),
+                                         _ptr(weight_scales), _ptr(output), _ptr(logits_f32),
+                                         _ptr(argmax_scratch), _ptr(pairs)))
+
+    def merge(self, stream, rows, shards, gathered_pairs, output_pairs):
+        c = self.ctx
+        c.check(c._lib.tk100_argmax_merge(c.handle, _stream(stream), rows, shards,
+                                          _ptr(gathered_pairs), _ptr(output_pairs)))
