@@ -402,6 +402,12 @@ tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* 
                                   cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaMemsetAsync(ctx->impl->status_word(), 0, sizeof(uint32_t), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && (*word & tk100::STATUS_WAIT_TIMEOUT)) {
+    // CTAs that gave up may have left split-K tickets behind: re-arm them.
+    e = cudaMemsetAsync(ctx->impl->counters(), 0,
+                        ctx->impl->counter_count() * sizeof(unsigned int), s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  }
   return ctx->impl->check(e, "reading the device status word");
 }
 
