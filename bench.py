@@ -190,6 +190,22 @@ def time_region(torch, fn, steps, sync_each=False):
     return start.elapsed_time(stop)
 
 
+def capture(torch, fn, reps=1):
+    """Records `reps` calls of fn into one CUDA graph (the reference times its operators as
+    graph replays too: qual/src/device_benchmark.rs:1026-1054)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()  # tensor maps are encoded and cached here, outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    return graph
+
+
 def extra_rows(torch, tk, ctx, peak_gbs):
     """Other configurations of the path on one GPU: decode projections with the weight plane
     rotated over several copies so that every launch streams from HBM, not from L2."""
@@ -220,10 +236,12 @@ def extra_rows(torch, tk, ctx, peak_gbs):
                 state["i"] += 1
                 op.launch(None, m, None, codes, scales, w, s, outp)
 
-            for _ in range(copies * 2):
-                proj()
-            iters = copies * 12
-            ms = time_region(torch, proj, iters) / iters
+            state["i"] = 0
+            graph = capture(torch, proj, copies)  # one launch per weight copy, in rotation
+            for _ in range(3):
+                graph.replay()
+            reps = 20
+            ms = time_region(torch, graph.replay, reps) / (reps * copies)
             b = algorithmic_bytes(m, n_rows, HIDDEN, 2)
             out.append({"op": name, "M": m, "N": n_rows, "us": ms * 1e3, "GB/s": b / ms / 1e6,
                         "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs,
@@ -247,10 +265,12 @@ def extra_rows(torch, tk, ctx, peak_gbs):
             state["i"] += 1
             normop.launch_quantize(None, m, xs[i], bs[i], w, res[i], nrm[i], codes[i], scales)
 
-        for _ in range(8):
-            norm()
-        iters = 200
-        ms = time_region(torch, norm, iters) / iters
+        state["i"] = 0
+        graph = capture(torch, norm, copies * 4)
+        for _ in range(3):
+            graph.replay()
+        reps = 20
+        ms = time_region(torch, graph.replay, reps) / (reps * copies * 4)
         b = 10 * m * HIDDEN + m * HIDDEN + 4 * m
         out.append({"op": "residual_rmsnorm_quant_e4m3", "M": m, "us": ms * 1e3,
                     "GB/s": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs})
@@ -278,8 +298,9 @@ def run_native(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     m = args.rows
-    assert VOCAB % world == 0
-    shard = VOCAB // world
+    vocab = args.vocab
+    assert vocab % (world * 16) == 0, "vocabulary must split into shards of a multiple of 16 rows"
+    shard = vocab // world
     offset = rank * shard
     ctx = tk.Context(device=local, max_rows=max(2048, m))
     dev = "cuda"
@@ -316,15 +337,33 @@ def run_native(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
+    for _ in range(3):
         step()
+    barrier()
+    # One step as a CUDA graph (kernels + the NCCL gather), replayed: the way the reference's
+    # engine runs this path (tuisko-engine/src/program.rs:149-154, 303-319).
+    mode = "graph"
+    launches0 = ctx.launch_count
+    try:
+        if args.eager:
+            raise RuntimeError("eager requested")
+        graph = capture(torch, step, 1)
+        run_step = graph.replay
+    except Exception as exc:  # capture of the collective can be refused by the backend
+        mode = f"eager ({type(exc).__name__})"
+        run_step = step
+        torch.cuda.synchronize()
+    launches_per_step = (ctx.launch_count - launches0) // 2 if mode == "graph" else None
+    for _ in range(max(3, args.warmup)):
+        run_step()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = ctx.launch_count
-    ms = time_region(torch, step, args.steps)
-    launches = ctx.launch_count - launches0
+    ms = time_region(torch, run_step, args.steps)
+    launches = (launches_per_step * args.steps if launches_per_step is not None
+                else ctx.launch_count - launches0)
     barrier()
     for _ in range(3):
         step_e2e()
@@ -342,7 +381,7 @@ def run_native(args):
     ms, ms_e2e, ms_proj = [float(v) for v in times.tolist()]
 
     # sanity: the selected token is the arg-max of the logits this step wrote
-    step()
+    run_step()
     torch.cuda.synchronize()
     final = (merged if world > 1 else pairs).cpu().numpy()
     mine = pairs.cpu().numpy()
@@ -355,7 +394,7 @@ def run_native(args):
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        total_bytes = algorithmic_bytes(m, VOCAB, HIDDEN, 4) + (world - 1) * (m * HIDDEN + 4 * m)
+        total_bytes = algorithmic_bytes(m, vocab, HIDDEN, 4) + (world - 1) * (m * HIDDEN + 4 * m)
         per_step = ms / args.steps
         value = total_bytes / per_step / 1e6
         e2e_value = total_bytes / (ms_e2e / args.steps) / 1e6
@@ -367,8 +406,9 @@ def run_native(args):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3",
             "data": "synthetic",
-            "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={VOCAB} M={m}",
+            "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={vocab} M={m}",
                        "rows": m, "vocab_shard_rows": shard, "parallelism": f"vocab-shard x{world}",
+                       "launch": mode,
                        "l2": "weight shard (%.0f MB) larger than L2, streamed once per step"
                              % (shard * HIDDEN / 1e6),
                        "tokens_per_s": m / (per_step * 1e-3), "us_per_step": per_step * 1e3},
@@ -405,6 +445,9 @@ def main():
     ap.add_argument("--rows", type=int, default=1, help="decode tokens M (1, 4 or 32 in the config)")
     ap.add_argument("--cpu-sample-rows", type=int, default=0,
                     help="vocabulary rows per CPU step (0 = sized from a probe)")
+    ap.add_argument("--vocab", type=int, default=VOCAB,
+                    help="vocabulary rows (a smaller plane makes a small profiling case)")
+    ap.add_argument("--eager", action="store_true", help="launch every step from the host")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
