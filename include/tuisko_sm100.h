@@ -165,6 +165,34 @@ TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, in
 TK100_API tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, int shards,
                                 const tk100_argmax_pair* gathered, tk100_argmax_pair* output);
 
+/* No counterpart in the reference.  The FP8 projection (activation codes and scales already
+ * produced, as with input == NULL above) for hosts that must not allocate device memory and
+ * therefore cannot use tk100_create, which allocates the split-K scratch: an engine that
+ * gives its whole device budget to one arena at start-up and fails its "no allocation after
+ * warm-up" gate on any later cudaMalloc, or code that runs as a guest inside a process whose
+ * CUDA allocator it does not own.  It takes no context; its scratch (split-K partial tiles,
+ * tile tickets, a fault word) is a fixed array inside the library image.
+ *
+ * Limits and rules:
+ *   - every GPU that loads this library holds TK100_STATIC_SCRATCH_BYTES of device memory
+ *     for that array until the process exits, whether or not this function is ever called;
+ *   - rows <= TK100_STATIC_MAX_ROWS; a problem whose split-K scratch would exceed the array
+ *     is refused with TK100_ERR_ARENA (nothing is launched), it is not run more slowly;
+ *   - the first call on each device looks up the array's device address, the SM count and
+ *     the kernel attributes (the device must be current); make that first call before any
+ *     stream capture begins;
+ *   - all calls on a device share the one array: each call clears the tickets and the fault
+ *     word on `stream` before its kernel, and two calls whose kernels could overlap on the
+ *     GPU (different streams, no dependency) race on it -- serialise them;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ * `message` (may be NULL) receives the failure text, at most message_capacity bytes. */
+#define TK100_STATIC_MAX_ROWS 256
+#define TK100_STATIC_SCRATCH_BYTES ((8u << 20) + (16u << 10))
+TK100_API tk100_status tk100_fp8_projection_static(
+    tk100_stream stream, int rows, int out_rows, int columns, const uint8_t* activation_codes,
+    const float* activation_scales, const uint8_t* weight_codes, const uint16_t* weight_scales,
+    uint16_t* output, char* message, size_t message_capacity);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

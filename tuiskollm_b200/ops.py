@@ -184,3 +184,26 @@ class LmHeadOp:
         c = self.ctx
         c.check(c._lib.tk100_argmax_merge(c.handle, _stream(stream), rows, shards,
                                           _ptr(gathered_pairs), _ptr(output_pairs)))
+
+
+STATIC_MAX_ROWS = 256
+STATIC_SCRATCH_BYTES = (8 << 20) + (16 << 10)
+
+
+def fp8_projection_static(stream, rows, out_rows, columns, activation_codes, activation_scales,
+                          weight_codes, weight_scales, output):
+    """FP8 projection without a context, for hosts that may not allocate device memory (an
+    engine with a fixed arena and a no-allocation gate, or guest code in a process whose
+    allocator it does not own).  The split-K scratch is a fixed ``STATIC_SCRATCH_BYTES`` array
+    inside the library that every GPU loading it keeps until exit; ``rows`` is limited to
+    ``STATIC_MAX_ROWS`` and larger scratch needs are refused with ``gpu.arena``.  The first call
+    on a device does the one-time set-up and should come before any stream capture; calls
+    share the array, so calls that could overlap on the GPU must be serialised."""
+    lib = _lib.load()
+    message = C.create_string_buffer(320)
+    status = lib.tk100_fp8_projection_static(_stream(stream), rows, out_rows, columns,
+                                             _ptr(activation_codes), _ptr(activation_scales),
+                                             _ptr(weight_codes), _ptr(weight_scales), _ptr(output),
+                                             message, len(message))
+    if status != 0:
+        raise GpuError(status, message.value.decode())
