@@ -165,6 +165,42 @@ TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, in
 TK100_API tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, int shards,
                                 const tk100_argmax_pair* gathered, tk100_argmax_pair* output);
 
+/* NVFP4 activation quantiser for the W4A4 tensor-core route.  The reference's NVFP4
+ * operators multiply BF16 activations (A16) and have no such step; the definition is this
+ * library's own, symmetric to the weight convention: per 16 columns
+ *   scale = e4m3_rne_sat((amax * divisor) / 6),  code = e2m1_rne_sat((x * divisor) / scale),
+ * represented value = e2m1 * scale / divisor.  activation_codes [rows, columns/2] (low
+ * nibble = even column); activation_scales in the same 128-row x 4-group tiles as weight
+ * scales with row = token, sized ceil(rows/128)*128 * columns/16 bytes.  columns % 256 == 0. */
+TK100_API tk100_status tk100_nvfp4_quantize_activation(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                             int columns, const uint16_t* input,
+                                             float input_global_divisor,
+                                             uint8_t* activation_codes,
+                                             uint8_t* activation_scales);
+
+/* Nvfp4SwiGluOp::launch (tuisko-kernels-sm89/src/nvfp4/swiglu.rs:525-571): weight_codes is the
+ * fused [2 * intermediate, hidden/2] plane (gate rows, then up rows), weight_scales its
+ * swizzled [2 * intermediate, hidden/16] E4M3 plane, weight_scale_divisor finite and > 0;
+ * output [rows, intermediate] = bf16(silu(gate) * up).  Added to the reference signature:
+ * the activation code / scale planes (caller-owned, as for the FP8 operators) and the
+ * checkpoint's input_global_scale divisor (tuisko-model/src/bindings.rs:880-883), because
+ * the contraction runs W4A4 on tcgen05.mma kind::mxf4nvf4.block_scale.
+ * input != NULL: quantise it first; input == NULL: the planes already hold codes/scales. */
+TK100_API tk100_status tk100_nvfp4_gate_up_swiglu(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                        const uint16_t* input, uint8_t* activation_codes,
+                                        uint8_t* activation_scales, float input_global_divisor,
+                                        const uint8_t* weight_codes, const uint8_t* weight_scales,
+                                        float weight_scale_divisor, uint16_t* output);
+
+/* Nvfp4DownOp::launch (tuisko-kernels-sm89/src/nvfp4/down.rs:510-556): weight_codes
+ * [hidden, intermediate/2], weight_scales swizzled [hidden, intermediate/16];
+ * input / activation planes are [rows, intermediate]; output [rows, hidden]. */
+TK100_API tk100_status tk100_nvfp4_down(tk100_ctx* ctx, tk100_stream stream, int rows,
+                              const uint16_t* input, uint8_t* activation_codes,
+                              uint8_t* activation_scales, float input_global_divisor,
+                              const uint8_t* weight_codes, const uint8_t* weight_scales,
+                              float weight_scale_divisor, uint16_t* output);
+
 /* No counterpart in the reference.  The FP8 projection (activation codes and scales already
  * produced, as with input == NULL above) for hosts that must not allocate device memory and
  * therefore cannot use tk100_create, which allocates the split-K scratch: an engine that

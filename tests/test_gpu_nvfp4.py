@@ -1,0 +1,261 @@
+"""GPU parity for the NVFP4 MLP projections (W4A4 on block-scaled tcgen05).
+
+Weight side: pinned by the reference's fixtures (qual/src/nvfp4_swiglu.rs:196-234,
+qual/src/nvfp4_down.rs:196-230) -- their inputs are exactly representable in NVFP4 with a
+power-of-two divisor, so the reference's A16 closed form applies unchanged.
+Activation quantiser: PARITY UNPINNED (no reference counterpart); the GPU must match this
+build's own oracle definition bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+import fixtures_ref as F
+from gpu_util import (assert_inactive_untouched, check_close, dev, graph_replay, host,
+                      max_relative_error, sentinel_plane)
+
+pytestmark = pytest.mark.gpu
+
+HIDDEN, INTER = 5120, 17408
+
+
+@pytest.fixture(scope="module")
+def tk():
+    import tuiskollm_b200 as tk
+    return tk
+
+
+@pytest.fixture(scope="module")
+def ctx(tk):
+    return tk.Context(device=0)
+
+
+def _u16(t):
+    return host(t.view(torch.int16)).view(np.uint16)
+
+
+def act_planes(tk, max_rows, k):
+    from tuiskollm_b200 import ops
+    codes = sentinel_plane((max_rows, k // 2), torch.uint8)
+    scales = sentinel_plane((ops.nvfp4_scale_plane_bytes(max_rows, k),), torch.uint8)
+    return codes, scales
+
+
+def check_quantiser(oracle, xb, divisor, codes, scales, rows):
+    k = xb.shape[1]
+    oc, osc = oracle.nvfp4_quantize(xb[:rows], divisor)
+    assert np.array_equal(host(codes)[:rows], oc), "NVFP4 activation codes"
+    offs = oracle.nvfp4_scale_offsets(rows, k // 16)
+    got = host(scales)
+    assert np.array_equal(got[offs], osc[offs]), "NVFP4 activation scales"
+    # every other byte of the plane (rows >= `rows` of the padded tiles) is untouched
+    mask = np.ones(got.size, bool)
+    mask[offs.reshape(-1)] = False
+    assert (got[mask] == 0xA5).all(), "scale entries of inactive rows were written"
+    assert_inactive_untouched(codes, rows)
+    return oc, osc
+
+
+@pytest.mark.parametrize("rows,k", [(1, 5120), (5, 5120), (130, 5120), (3, 17408), (33, 256)])
+def test_activation_quantiser_is_bit_exact(tk, ctx, oracle, rows, k):
+    from tuiskollm_b200 import synth
+
+    xb = synth.normal_bf16(21, rows + k, (rows, k))
+    xb[0, :16] = 0          # an all-zero block (scale 0, signed-zero codes)
+    xb[0, 3] = 0x8000
+    xb[rows - 1, 16:32] = synth.f32_to_bf16_bits(np.full(16, 1e-30, np.float32))  # underflowing scale
+    divisor = float(np.float32(448.0 * 6.0 / 4.5))
+    codes, scales = act_planes(tk, rows + 2, k)
+    tk.Nvfp4SwiGluOp(ctx).quantize(None, rows, k, dev(xb.view(np.int16)), divisor, codes, scales)
+    torch.cuda.synchronize()
+    check_quantiser(oracle, xb, divisor, codes, scales, rows)
+
+
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_reference_fixture_gate_up_swiglu(tk, ctx, oracle, batch):
+    """qual/src/nvfp4_swiglu.rs: structured fixture at full size, exact batches 1..8; tolerance
+    max(1/4, 2.5 %) of the f64 represented-value oracle (:248), sentinels, graph replay."""
+    x = F.nvfp4_input(8, HIDDEN)
+    wc, wsc = cached_fixture("gate_up")
+    # amax of every 16-block is 0.5 * token factor, so divisor 12 makes every block scale a
+    # power of two and every activation an exact E2M1 value: W4A4 == A16 on this fixture
+    divisor = 12.0
+    codes, scales = act_planes(tk, 8, HIDDEN)
+    out = sentinel_plane((8, INTER), torch.int16)
+    w, s, xd = dev(wc), dev(wsc), dev(x.view(np.int16))
+    op = tk.Nvfp4SwiGluOp(ctx)
+    launch = lambda: op.launch(None, batch, xd, w, s, F.NVFP4_WEIGHT_SCALE_DIVISOR, out,
+                               activation_codes=codes, activation_scales=scales,
+                               input_global_divisor=divisor)
+    launch()
+    torch.cuda.synchronize()
+    oc, osc = check_quantiser(oracle, x, divisor, codes, scales, batch)
+    dots = oracle.nvfp4_a16_dot(x[:batch], wc, wsc, F.NVFP4_WEIGHT_SCALE_DIVISOR)
+    w4a4 = oracle.nvfp4_w4a4_dot(oc, osc, divisor, wc, wsc, F.NVFP4_WEIGHT_SCALE_DIVISOR)
+    np.testing.assert_allclose(w4a4, dots, rtol=1e-12, atol=1e-12)  # lossless activations
+    exp = oracle.silu_mul(dots[:, :INTER], dots[:, INTER:])
+    for token in (0, batch - 1):
+        for row in (0, 1, 127, 128, INTER - 1):
+            g = F.nvfp4_closed_form_dot(x, token, row, wc, wsc, HIDDEN)
+            u = F.nvfp4_closed_form_dot(x, token, row + INTER, wc, wsc, HIDDEN)
+            assert exp[token, row] == pytest.approx(g / (1 + np.exp(-g)) * u, rel=1e-12, abs=1e-12)
+    got = _u16(out)
+    check_close(got[:batch], exp, 0.25, 0.025, "NVFP4 SwiGLU")
+    assert_inactive_untouched(out, batch)
+    eager = host(out.view(torch.uint8)).copy()
+    g = graph_replay(launch)
+    out.view(torch.uint8).fill_(0xA5)
+    g.replay()
+    g.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(host(out.view(torch.uint8)), eager)
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("batch", [1, 4, 8])
+def test_reference_fixture_down(tk, ctx, oracle, batch):
+    """qual/src/nvfp4_down.rs: structured fixture at full size (K = 17408, split-K route)."""
+    x = F.nvfp4_input(8, INTER)
+    wc, wsc = cached_fixture("down")
+    divisor = 12.0
+    codes, scales = act_planes(tk, 8, INTER)
+    out = sentinel_plane((8, HIDDEN), torch.int16)
+    op = tk.Nvfp4DownOp(ctx)
+    w, s, xd = dev(wc), dev(wsc), dev(x.view(np.int16))
+    launch = lambda: op.launch(None, batch, xd, w, s, F.NVFP4_WEIGHT_SCALE_DIVISOR, out,
+                               activation_codes=codes, activation_scales=scales,
+                               input_global_divisor=divisor)
+    launch()
+    torch.cuda.synchronize()
+    check_quantiser(oracle, x, divisor, codes, scales, batch)
+    exp = oracle.nvfp4_a16_dot(x[:batch], wc, wsc, F.NVFP4_WEIGHT_SCALE_DIVISOR)
+    for row in (0, 1, 127, 128, HIDDEN - 1):
+        assert exp[0, row] == pytest.approx(F.nvfp4_closed_form_dot(x, 0, row, wc, wsc, INTER), rel=1e-12)
+    check_close(_u16(out)[:batch], exp, 0.25, 0.025, "NVFP4 down")
+    assert_inactive_untouched(out, batch)
+    eager = host(out.view(torch.uint8)).copy()
+    g = graph_replay(launch)
+    out.view(torch.uint8).fill_(0xA5)
+    g.replay()
+    g.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(host(out.view(torch.uint8)), eager)
+    assert ctx.device_status() == 0
+
+
+_FIXTURES = {}
+
+
+def cached_fixture(kind):
+    if kind not in _FIXTURES:
+        if kind == "gate_up":
+            _FIXTURES[kind] = F.nvfp4_weights(2 * INTER, HIDDEN, gate_up_split=INTER)
+        else:
+            _FIXTURES[kind] = F.nvfp4_weights(HIDDEN, INTER, gate_up_split=None)
+    return _FIXTURES[kind]
+
+
+@pytest.mark.parametrize("rows", [1, 32, 100, 256])
+def test_synthetic_mlp_small_geometry(tk, oracle, rows):
+    """Random N(0,1) activations and N(0,0.02) weights on a small geometry (hidden 1024,
+    intermediate 512) where the whole W4A4 oracle is cheap: gate_up+SwiGLU, re-quantise,
+    down; max relative error 1e-2 at every step against the oracle run on the device's own
+    quantised operands."""
+    from tuiskollm_b200 import synth
+
+    hidden, inter = 1024, 512
+    ctx = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=512)
+    xb = synth.normal_bf16(4, rows, (rows, hidden))
+    gu_codes, gu_scales, gu_div = synth.nvfp4_weights(4, 1, 2 * inter, hidden)
+    dn_codes, dn_scales, dn_div = synth.nvfp4_weights(4, 2, hidden, inter)
+    a_div = float(np.float32(448.0 * 6.0 / 5.0))  # calibration: |x| stays below ~5
+    codes, scales = act_planes(tk, rows + 1, hidden)
+    mid = sentinel_plane((rows + 1, inter), torch.int16)
+    tk.Nvfp4SwiGluOp(ctx).launch(None, rows, dev(xb.view(np.int16)), dev(gu_codes), dev(gu_scales),
+                                 float(gu_div), mid, activation_codes=codes,
+                                 activation_scales=scales, input_global_divisor=a_div)
+    torch.cuda.synchronize()
+    oc, osc = check_quantiser(oracle, xb, a_div, codes, scales, rows)
+    dots = oracle.nvfp4_w4a4_dot(oc, osc, a_div, gu_codes, gu_scales, float(gu_div))
+    exp_mid = oracle.silu_mul(dots[:, :inter], dots[:, inter:])
+    got_mid = _u16(mid)[:rows]
+    scale_mid = float(np.abs(exp_mid).mean())
+    assert max_relative_error(got_mid, exp_mid, 4 * scale_mid) <= 1e-2
+    check_close(got_mid, exp_mid, 0.25, 0.025, "gate_up")
+    assert_inactive_untouched(mid, rows)
+    # down projection from the device's own intermediate
+    m_div = float(np.float32(448.0 * 6.0) / max(np.abs(oracle.bf16_to_f32(got_mid)).max(), 1e-6))
+    codes2, scales2 = act_planes(tk, rows + 1, inter)
+    out = sentinel_plane((rows + 1, hidden), torch.int16)
+    tk.Nvfp4DownOp(ctx).launch(None, rows, mid, dev(dn_codes), dev(dn_scales), float(dn_div), out,
+                               activation_codes=codes2, activation_scales=scales2,
+                               input_global_divisor=m_div)
+    torch.cuda.synchronize()
+    oc2, osc2 = check_quantiser(oracle, got_mid, m_div, codes2, scales2, rows)
+    exp_out = oracle.nvfp4_w4a4_dot(oc2, osc2, m_div, dn_codes, dn_scales, float(dn_div))
+    got_out = _u16(out)[:rows]
+    assert max_relative_error(got_out, exp_out, 4 * float(np.abs(exp_out).mean())) <= 1e-2
+    assert_inactive_untouched(out, rows)
+    assert ctx.device_status() == 0
+
+
+def test_full_size_prefill_sampled_tiles(tk, ctx, oracle):
+    """Configuration 4 (M = 2048, gate_up 34816 x 5120, down 5120 x 17408): too large for the
+    CPU oracle as a whole, so whole 128-row tiles are sampled -- first, last and two inner
+    weight tiles x first and last token tiles -- and checked against the W4A4 oracle."""
+    from tuiskollm_b200 import ops, synth
+
+    rows = 2048
+    x = synth.torch_normal_bf16(12, 1, (rows, HIDDEN), "cuda")
+    gu_codes, gu_scales, gu_div = synth.torch_nvfp4_weights(12, 2, 2 * INTER, HIDDEN, "cuda")
+    a_div = float(np.float32(448.0 * 6.0 / 6.0))
+    codes, scales = act_planes(tk, rows, HIDDEN)
+    mid = sentinel_plane((rows, INTER), torch.int16)
+    tk.Nvfp4SwiGluOp(ctx).launch(None, rows, x, gu_codes, gu_scales, gu_div, mid,
+                                 activation_codes=codes, activation_scales=scales,
+                                 input_global_divisor=a_div)
+    torch.cuda.synchronize()
+    g_in, g_w = HIDDEN // 16, HIDDEN // 16
+    tok_tiles, w_tiles = [0, rows // 128 - 1], [0, 57, 100, INTER // 128 - 1]
+
+    def tile_slice(plane, tile, groups):
+        return plane[tile * 128 * groups:(tile + 1) * 128 * groups]
+
+    xb = _u16(x.view(torch.int16))
+    for tt in tok_tiles:
+        oc, osc = oracle.nvfp4_quantize(xb[tt * 128:(tt + 1) * 128], a_div)
+        assert np.array_equal(host(codes[tt * 128:(tt + 1) * 128]), oc)
+        assert np.array_equal(host(tile_slice(scales, tt, g_in)), osc)
+        for wt in w_tiles:
+            rows_g = slice(wt * 128, (wt + 1) * 128)
+            rows_u = slice(INTER + wt * 128, INTER + (wt + 1) * 128)
+            wc = np.concatenate([host(gu_codes[rows_g]), host(gu_codes[rows_u])])
+            ws = np.concatenate([host(tile_slice(gu_scales, wt, g_w)),
+                                 host(tile_slice(gu_scales, INTER // 128 + wt, g_w))])
+            dots = oracle.nvfp4_w4a4_dot(oc, osc, a_div, wc, ws, gu_div)
+            exp = oracle.silu_mul(dots[:, :128], dots[:, 128:])
+            got = _u16(mid)[tt * 128:(tt + 1) * 128, rows_g]
+            assert max_relative_error(got, exp, 4 * float(np.abs(exp).mean())) <= 1e-2
+    assert ctx.device_status() == 0
+
+
+def test_rejected_launches(tk, ctx):
+    codes, scales = act_planes(tk, 8, HIDDEN)
+    x = torch.zeros((8, HIDDEN), dtype=torch.int16, device="cuda")
+    w = torch.zeros((2 * INTER, HIDDEN // 2), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((2 * INTER * HIDDEN // 16,), dtype=torch.uint8, device="cuda")
+    out = torch.zeros((8, INTER), dtype=torch.int16, device="cuda")
+    op = tk.Nvfp4SwiGluOp(ctx)
+    kw = dict(activation_codes=codes, activation_scales=scales, input_global_divisor=1.0)
+    for bad in (0.0, -1.0, float("inf"), float("nan")):
+        with pytest.raises(tk.GpuError) as info:
+            op.launch(None, 1, x, w, s, bad, out, **kw)
+        assert info.value.code == "gpu.launch"
+        assert "weight scale divisor must be finite and positive" in str(info.value)
+    with pytest.raises(tk.GpuError) as info:
+        op.launch(None, 0, x, w, s, 1.0, out, **kw)
+    assert "NVFP4 SwiGLU row count" in str(info.value)
+    with pytest.raises(tk.GpuError) as info:
+        op.launch(None, 1, x, w, s, 1.0, out, activation_codes=codes, activation_scales=scales,
+                  input_global_divisor=0.0)
+    assert "input scale divisor" in str(info.value)
+    torch.cuda.synchronize()

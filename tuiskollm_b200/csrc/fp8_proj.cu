@@ -249,13 +249,27 @@ __global__ void __launch_bounds__(kThreads)
                             (static_cast<size_t>(tile_m) * gridDim.x + tile_n) *
                                 (BLOCK_TOK * kTileRows) +
                             row_in_tile;
+        // Eight tokens at a time: all loads of a batch are issued before the first add, so
+        // the L2 round trips overlap instead of forming one dependent chain per token.
 #pragma unroll 1
-        for (int j = 0; j < valid_tok; ++j) {
-          float acc = 0.0f;
+        for (int j0 = 0; j0 < valid_tok; j0 += 8) {
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
           for (int s = 0; s < p.splits; ++s) {
-            acc = __fadd_rn(acc, __ldcg(base + s * split_stride + j * kTileRows));
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[j] = (j0 + j < valid_tok) ? __ldcg(base + s * split_stride + (j0 + j) * kTileRows)
+                                          : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], v[j]);
           }
-          emit(j, acc);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (j0 + j < valid_tok) emit(j0 + j, acc[j]);
+          }
         }
       }
     }

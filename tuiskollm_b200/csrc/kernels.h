@@ -53,4 +53,29 @@ cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long 
 cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,
                                 const ArgmaxPair* gathered, ArgmaxPair* out);
 
+// -------------------------------------------------------------------- nvfp4.cu
+struct Nvfp4Params {
+  int rows;            // active tokens M
+  int out_rows;        // outputs per token (weight rows of one tile family), multiple of 128
+  int k;               // reduction length in elements, multiple of 256
+  int splits;          // K splits (1 with gate/up fusion)
+  int up_row_offset;   // gate/up fusion: first weight row of the up half (= out_rows)
+  const uint8_t* w_scales;  // swizzled E4M3 weight scales
+  const uint8_t* a_scales;  // swizzled E4M3 activation scales
+  float out_scale;     // 1 / (weight divisor * activation divisor)
+  uint16_t* out;       // [rows, out_rows] BF16
+  float* partials;
+  unsigned int* counters;
+  uint32_t* status;
+};
+
+cudaError_t nvfp4_prepare();
+// block_tok 32 or 128.  gate_up: weight plane holds gate rows then up rows; output is
+// bf16(silu(gate) * up).
+cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,
+                              const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
+                              const Nvfp4Params& p);
+cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const uint16_t* x,
+                                  float divisor, uint8_t* codes, uint8_t* scales);
+
 }  // namespace tk100

@@ -1,0 +1,414 @@
+// NVFP4 MLP projections on the block-scaled tcgen05 tensor cores (W4A4).
+//
+// Weights are the reference's planes unchanged: E2M1 codes [rows_w, K/2] (low nibble = even
+// column), one E4M3 scale per 16 columns in 128-row x 4-group tiles
+// (tuisko-model/src/materialize.rs:410-422) and an fp32 global divisor, value =
+// e2m1 * e4m3(scale) / divisor (tuisko-kernels-sm89/src/nvfp4/swiglu.rs:211-212).  The
+// reference multiplies them with BF16 activations on CUDA cores (A16,
+// tuisko-kernels-sm89/src/nvfp4/swiglu.rs:166-320, nvfp4/down.rs:158-305); here the
+// activations are quantised to the same format per 16-column block (definition in
+// nvfp4_quantize_kernel below; the reference has no counterpart for that step) so that
+// tcgen05.mma kind::mxf4nvf4.block_scale consumes both operands and their scale tiles
+// directly.  That 128 x 4 tile order is exactly what tcgen05.cp.32x128b.warpx4 moves into
+// TMEM as a scale-factor operand, so the weight scale plane is streamed as is.
+//
+// Kernel shape (swap-AB, as the FP8 projection): a CTA owns 128 weight rows x BLOCK_TOK
+// tokens; a stage is 256 K-elements: 128 rows x 128 bytes of codes per weight tile, the
+// token tile, and 2 KB of scales per tile.  With GATE_UP the CTA holds the gate tile
+// (rows r) and the up tile (rows I + r) of the same outputs in two TMEM accumulators and
+// the epilogue writes bf16(silu(gate) * up) -- the fusion the reference has
+// (nvfp4/swiglu.rs:300-320), now after a tensor-core contraction.
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tk100 {
+
+namespace {
+
+constexpr int kRows = 128;           // weight rows per tile (UMMA M)
+constexpr int kStageKBytes = 128;    // code bytes per row per stage = 256 elements
+constexpr int kStageK = 256;         // elements
+constexpr int kWTile = kRows * kStageKBytes;  // 16 KB
+constexpr int kSfChunk = 512;        // scales of 128 rows x 4 groups (one UMMA K = 64)
+constexpr int kSfStage = 4 * kSfChunk;  // 2 KB: 128 rows x 16 groups
+constexpr int kThreads = 192;
+constexpr int kSfSlots = 8;          // TMEM scale slots in rotation
+constexpr int kSfSlotCols = 16;      // columns per slot: SFA0 [0,4) SFA1 [4,8) SFB [8,12)
+
+__host__ __device__ constexpr int nv_stages(int block_tok, bool gate_up) {
+  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 8 : 6);
+}
+
+__host__ __device__ constexpr int nv_stage_bytes(int block_tok, bool gate_up) {
+  return (gate_up ? 2 : 1) * (kWTile + kSfStage) + block_tok * kStageKBytes + kSfStage;
+}
+
+template <int STAGES, int BLOCK_TOK>
+struct NvControl {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  uint32_t flag;
+};
+
+template <int BLOCK_TOK, bool GATE_UP>
+__host__ __device__ constexpr size_t nv_smem_bytes() {
+  return 1024 + static_cast<size_t>(nv_stages(BLOCK_TOK, GATE_UP)) *
+                    nv_stage_bytes(BLOCK_TOK, GATE_UP) +
+         sizeof(NvControl<nv_stages(BLOCK_TOK, GATE_UP), BLOCK_TOK>);
+}
+
+__device__ __forceinline__ void nv_epilogue_barrier() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// silu(v) in the sign-stable form of the reference's NVFP4 route
+// (tuisko-kernels-sm89/src/nvfp4/swiglu.rs:142-155), ex2.approx for the exponential.
+__device__ __forceinline__ float silu_stable(float v) {
+  const float e = -fabsf(v) * 1.4426950408889634f;
+  float ex = 0.0f;
+  if (e >= -126.0f) asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(e));
+  return v >= 0.0f ? __fdiv_rn(v, 1.0f + ex) : __fdiv_rn(v * ex, 1.0f + ex);
+}
+
+template <int BLOCK_TOK, bool GATE_UP>
+__global__ void __launch_bounds__(kThreads)
+    nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                      const __grid_constant__ CUtensorMap tmap_a, const Nvfp4Params p) {
+  constexpr int STAGES = nv_stages(BLOCK_TOK, GATE_UP);
+  constexpr int STAGE_BYTES = nv_stage_bytes(BLOCK_TOK, GATE_UP);
+  constexpr int NW = GATE_UP ? 2 : 1;
+  // stage layout: [W0][W1?][A][SFA0][SFA1?][SFB]
+  constexpr int OFF_A = NW * kWTile;
+  constexpr int OFF_SFA = OFF_A + BLOCK_TOK * kStageKBytes;
+  constexpr int OFF_SFB = OFF_SFA + NW * kSfStage;
+  constexpr uint32_t ACC_COLS = NW * BLOCK_TOK;
+  constexpr uint32_t NEED_COLS = ACC_COLS + kSfSlots * kSfSlotCols;
+  constexpr uint32_t TMEM_COLS = NEED_COLS <= 32 ? 32 : NEED_COLS <= 64 ? 64 : NEED_COLS <= 128 ? 128 : NEED_COLS <= 256 ? 256 : 512;
+  constexpr uint32_t IDESC = umma_idesc_nvfp4(kRows, BLOCK_TOK);
+  using Ctl = NvControl<STAGES, BLOCK_TOK>;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  const int kb_total = p.k / kStageK;
+  const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / p.splits);
+  const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / p.splits);
+  const int nkb = kb_end - kb_begin;
+  const int tok0 = tile_m * BLOCK_TOK;
+
+  if (threadIdx.x == 0) ctl->flag = *reinterpret_cast<volatile uint32_t*>(p.status);
+  __syncthreads();
+  if (ctl->flag & STATUS_WAIT_TIMEOUT) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    mbar_init(&ctl->tmem_full, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_w);
+    prefetch_tensormap(&tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_a = l2_policy_evict_last();
+      // Scale tiles: chunk (tile, kb) of a plane with G = K/16 groups per row starts at
+      // ((tile * G/4) + 4 * kb) * 512 bytes and is 2 KB long (4 consecutive 512-byte chunks).
+      const size_t chunks_per_tile = static_cast<size_t>(p.k / 64);
+      const uint8_t* sfa0 = p.w_scales + (static_cast<size_t>(tile_n) * chunks_per_tile) * kSfChunk;
+      const uint8_t* sfa1 =
+          p.w_scales + (static_cast<size_t>(p.up_row_offset / kRows + tile_n) * chunks_per_tile) * kSfChunk;
+      const uint8_t* sfb = p.a_scales + (static_cast<size_t>(tok0 / kRows) * chunks_per_tile) * kSfChunk;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
+        if (!ok) break;
+        uint8_t* stage = smem + s * STAGE_BYTES;
+        mbar_arrive_expect_tx(&ctl->full[s], STAGE_BYTES);
+        const int kb = kb_begin + i;
+        const int kbyte = kb * kStageKBytes;
+        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kRows, pol_w);
+        if (GATE_UP) {
+          tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
+                      p.up_row_offset + tile_n * kRows, pol_w);
+        }
+        tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kbyte, tok0, pol_a);
+        const size_t sf_off = static_cast<size_t>(kb) * kSfStage;
+        bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, kSfStage, &ctl->full[s], pol_w);
+        if (GATE_UP) {
+          bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, kSfStage, &ctl->full[s], pol_w);
+        }
+        bulk_load_1d(stage + OFF_SFB, sfb + sf_off, kSfStage, &ctl->full[s], pol_a);
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t sf_base = tmem + ACC_COLS;
+      // a BLOCK_TOK < 128 tile sits in one 32-row quartile of its 128-row scale tile:
+      // quartile q of the chunk lands in TMEM column q
+      const uint32_t sfb_quartile = static_cast<uint32_t>((tok0 % kRows) / 32);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&ctl->full[s], phase, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t desc_w0 = umma_desc_sw128(base);
+        const uint64_t desc_w1 = umma_desc_sw128(base + kWTile);
+        const uint64_t desc_a = umma_desc_sw128(base + OFF_A);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint32_t slot = sf_base + static_cast<uint32_t>(((i * 4 + k4) % kSfSlots) * kSfSlotCols);
+          tmem_cp_32x128b_warpx4(slot, umma_desc_noswizzle_rows16(base + OFF_SFA + k4 * kSfChunk));
+          if (GATE_UP) {
+            tmem_cp_32x128b_warpx4(
+                slot + 4, umma_desc_noswizzle_rows16(base + OFF_SFA + kSfStage + k4 * kSfChunk));
+          }
+          tmem_cp_32x128b_warpx4(slot + 8, umma_desc_noswizzle_rows16(base + OFF_SFB + k4 * kSfChunk));
+          const uint32_t acc = (i | k4) != 0;
+          umma_nvfp4(tmem, desc_w0 + 2 * k4, desc_a + 2 * k4, IDESC, slot, slot + 8 + sfb_quartile, acc);
+          if (GATE_UP) {
+            umma_nvfp4(tmem + BLOCK_TOK, desc_w1 + 2 * k4, desc_a + 2 * k4, IDESC, slot + 4,
+                       slot + 8 + sfb_quartile, acc);
+          }
+        }
+        umma_commit(&ctl->empty[s]);
+      }
+      umma_commit(&ctl->tmem_full);
+    }
+  } else {
+    const int et = threadIdx.x - 64;
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const int n = tile_n * kRows + row_in_tile;
+    const bool row_ok = n < p.out_rows;
+    const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
+    const float s = p.out_scale;
+
+    mbar_wait(&ctl->tmem_full, 0, p.status);
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+
+    if (GATE_UP) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+        if (c0 >= valid_tok) break;
+        uint32_t g[16], u[16];
+        tmem_ld16(taddr + c0, g);
+        tmem_ld16(taddr + BLOCK_TOK + c0, u);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok && row_ok) {
+            const float gate = __fmul_rn(__uint_as_float(g[j]), s);
+            const float up = __fmul_rn(__uint_as_float(u[j]), s);
+            p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
+                static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up)));
+          }
+        }
+      }
+    } else if (p.splits == 1) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+        if (c0 >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok && row_ok) {
+            p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
+                static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(__uint_as_float(r[j]), s)));
+          }
+        }
+      }
+    } else {
+      // split-K: fixed-order sum of fp32 partial tiles by the last CTA to arrive
+      const size_t tile_elems = static_cast<size_t>(BLOCK_TOK) * kRows;
+      const size_t tile_index = (static_cast<size_t>(split) * gridDim.y + tile_m) * gridDim.x + tile_n;
+      float* mine = p.partials + tile_index * tile_elems + row_in_tile;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+        if (c0 >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok) __stcg(mine + (c0 + j) * kRows, __uint_as_float(r[j]));
+        }
+      }
+      __threadfence();
+      nv_epilogue_barrier();
+      if (et == 0) {
+        unsigned int* counter = p.counters + tile_m * gridDim.x + tile_n;
+        const unsigned int ticket = atomicAdd(counter, 1u);
+        const bool last = ticket == static_cast<unsigned int>(p.splits - 1);
+        if (last) *counter = 0u;
+        ctl->flag = last ? 1u : 0u;
+      }
+      nv_epilogue_barrier();
+      if (ctl->flag) {
+        __threadfence();
+        const size_t split_stride = static_cast<size_t>(gridDim.y) * gridDim.x * tile_elems;
+        const float* base =
+            p.partials + (static_cast<size_t>(tile_m) * gridDim.x + tile_n) * tile_elems + row_in_tile;
+#pragma unroll 1
+        for (int j0 = 0; j0 < valid_tok; j0 += 8) {
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+          for (int sp = 0; sp < p.splits; ++sp) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[j] = (j0 + j < valid_tok) ? __ldcg(base + sp * split_stride + (j0 + j) * kRows) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], v[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (j0 + j < valid_tok && row_ok) {
+              p.out[static_cast<size_t>(tok0 + j0 + j) * p.out_rows + n] =
+                  static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(acc[j], s)));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// Activation quantiser, one thread per 16-column block.  This build's own definition (the
+// reference never quantises NVFP4 activations), all steps IEEE fp32:
+//   amax   = max |x|                              s_code = e4m3_rne_sat((amax * divisor) / 6)
+//   s      = decode(s_code)                       code_j = e2m1_rne_sat((x_j * divisor) / s)
+// and signed zeros when s == 0.  Scales go to the 128-row x 4-group tile order with
+// row = token; entries of rows >= `rows` are left untouched.
+__global__ void __launch_bounds__(256)
+    nvfp4_quantize_kernel(const uint16_t* __restrict__ x, int rows, int k, float divisor,
+                          uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const int groups = k >> 4;
+  const long long total = static_cast<long long>(rows) * groups;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(idx / groups);
+    const int g = static_cast<int>(idx - static_cast<long long>(r) * groups);
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * k + g * 16);
+    const uint4 a = src[0], b = src[1];
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[2 * j] = bf16x2_lo(w[j]);
+      v[2 * j + 1] = bf16x2_hi(w[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+    }
+    const float raw = __fdiv_rn(__fmul_rn(amax, divisor), 6.0f);
+    const uint32_t sc = f32x2_to_e4m3x2(raw, 0.0f) & 0xffu;
+    const float s = e4m3_to_f32(sc);
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t byte;
+      if (s == 0.0f) {
+        byte = (signbit(v[2 * j]) ? 0x08u : 0u) | (signbit(v[2 * j + 1]) ? 0x80u : 0u);
+      } else {
+        byte = f32x2_to_e2m1x2(__fdiv_rn(__fmul_rn(v[2 * j], divisor), s),
+                               __fdiv_rn(__fmul_rn(v[2 * j + 1], divisor), s)) & 0xffu;
+      }
+      packed[j >> 2] |= byte << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint2*>(codes + static_cast<size_t>(r) * (k >> 1) + g * 8) =
+        make_uint2(packed[0], packed[1]);
+    const size_t off = (static_cast<size_t>(r >> 7) * (groups >> 2) + (g >> 2)) * 512 +
+                       static_cast<size_t>(r & 31) * 16 + ((r & 127) >> 5) * 4 + (g & 3);
+    scales[off] = static_cast<uint8_t>(sc);
+  }
+}
+
+template <int BLOCK_TOK, bool GATE_UP>
+cudaError_t nv_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
+                      const Nvfp4Params& p) {
+  dim3 grid((p.out_rows + kRows - 1) / kRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK, p.splits);
+  nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>
+      <<<grid, kThreads, nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream>>>(tmap_w, tmap_a, p);
+  return cudaGetLastError();
+}
+
+template <int BLOCK_TOK, bool GATE_UP>
+cudaError_t nv_prepare() {
+  return cudaFuncSetAttribute(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(nv_smem_bytes<BLOCK_TOK, GATE_UP>()));
+}
+
+}  // namespace
+
+cudaError_t nvfp4_prepare() {
+  cudaError_t e;
+  if ((e = nv_prepare<32, true>()) != cudaSuccess) return e;
+  if ((e = nv_prepare<128, true>()) != cudaSuccess) return e;
+  if ((e = nv_prepare<32, false>()) != cudaSuccess) return e;
+  return nv_prepare<128, false>();
+}
+
+cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,
+                              const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
+                              const Nvfp4Params& p) {
+  if (block_tok == 32) {
+    return gate_up ? nv_launch<32, true>(stream, tmap_w, tmap_a, p)
+                   : nv_launch<32, false>(stream, tmap_w, tmap_a, p);
+  }
+  if (block_tok == 128) {
+    return gate_up ? nv_launch<128, true>(stream, tmap_w, tmap_a, p)
+                   : nv_launch<128, false>(stream, tmap_w, tmap_a, p);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const uint16_t* x,
+                                  float divisor, uint8_t* codes, uint8_t* scales) {
+  const long long total = static_cast<long long>(rows) * (k / 16);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  nvfp4_quantize_kernel<<<static_cast<unsigned int>(blocks), 256, 0, stream>>>(x, rows, k, divisor,
+                                                                             codes, scales);
+  return cudaGetLastError();
+}
+
+}  // namespace tk100

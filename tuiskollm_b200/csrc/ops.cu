@@ -3,6 +3,7 @@
 
 #include <cudaTypedefs.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -97,6 +98,12 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
   }
   if ((e = fp8_projection_prepare()) != cudaSuccess) {
     *error = std::string("[gpu.module] preparing the FP8 projection routes: ") +
+             cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
+  if ((e = nvfp4_prepare()) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the NVFP4 projection routes: ") +
              cudaGetErrorString(e);
     delete ctx;
     return TK100_ERR_MODULE;
@@ -357,6 +364,114 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   return TK100_OK;
 }
 
+// ------------------------------------------------------------------ Nvfp4MlpOp
+
+Status Nvfp4MlpOp::quantize(cudaStream_t stream, int rows, int columns, const uint16_t* input,
+                            float input_global_divisor, uint8_t* activation_codes,
+                            uint8_t* activation_scales) {
+  TK100_TRY(check_rows(ctx_, "NVFP4 activation quantiser", rows));
+  if (columns < 256 || columns % 256 != 0) {
+    return ctx_.fail(TK100_ERR_LAUNCH, "[gpu.launch] NVFP4 activation quantiser: " +
+                                           std::to_string(columns) +
+                                           " columns are not admitted (multiple of 256)");
+  }
+  if (!std::isfinite(input_global_divisor) || input_global_divisor <= 0.0f) {
+    return ctx_.fail(TK100_ERR_LAUNCH,
+                     "[gpu.launch] NVFP4 input scale divisor must be finite and positive");
+  }
+  TK100_TRY(check_plane(ctx_, "NVFP4 activation quantiser", "input", input, 32));
+  TK100_TRY(check_plane(ctx_, "NVFP4 activation quantiser", "activation codes", activation_codes,
+                        128));
+  TK100_TRY(check_plane(ctx_, "NVFP4 activation quantiser", "activation scales",
+                        activation_scales, 128));
+  ctx_.count_launch();
+  return ctx_.check(launch_nvfp4_quantize(stream, rows, columns, input, input_global_divisor,
+                                          activation_codes, activation_scales),
+                    "launching the NVFP4 activation quantiser");
+}
+
+Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_rows, int columns,
+                          const uint16_t* input, uint8_t* activation_codes,
+                          uint8_t* activation_scales, float input_global_divisor,
+                          const uint8_t* weight_codes, const uint8_t* weight_scales,
+                          float weight_scale_divisor, uint16_t* output) {
+  const char* name = gate_up ? "NVFP4 SwiGLU" : "NVFP4 down";
+  TK100_TRY(check_rows(ctx_, name, rows));
+  // tuisko-kernels-sm89/src/nvfp4/swiglu.rs:535-539
+  if (!std::isfinite(weight_scale_divisor) || weight_scale_divisor <= 0.0f) {
+    return ctx_.fail(TK100_ERR_LAUNCH,
+                     "[gpu.launch] NVFP4 weight scale divisor must be finite and positive");
+  }
+  if (!std::isfinite(input_global_divisor) || input_global_divisor <= 0.0f) {
+    return ctx_.fail(TK100_ERR_LAUNCH,
+                     "[gpu.launch] NVFP4 input scale divisor must be finite and positive");
+  }
+  // the scale tiles cover 128 rows x 4 groups (tuisko-model/src/materialize.rs:366-376)
+  if (out_rows < 128 || out_rows % 128 != 0) {
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name + ": " +
+                                           std::to_string(out_rows) +
+                                           " output rows are not admitted (multiple of 128)");
+  }
+  if (columns < 256 || columns % 256 != 0) {
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name + ": " +
+                                           std::to_string(columns) +
+                                           " columns are not admitted (multiple of 256)");
+  }
+  TK100_TRY(check_plane(ctx_, name, "activation codes", activation_codes, 128));
+  TK100_TRY(check_plane(ctx_, name, "activation scales", activation_scales, 128));
+  TK100_TRY(check_plane(ctx_, name, "weight codes", weight_codes, 128));
+  TK100_TRY(check_plane(ctx_, name, "weight scales", weight_scales, 128));
+  TK100_TRY(check_plane(ctx_, name, "output", output, 2));
+  if (input) {
+    TK100_TRY(quantize(stream, rows, columns, input, input_global_divisor, activation_codes,
+                       activation_scales));
+  }
+
+  const int block_tok = rows <= 32 ? 32 : 128;
+  const int tiles_n = out_rows / 128;
+  const int tiles_m = (rows + block_tok - 1) / block_tok;
+  const long long tiles = static_cast<long long>(tiles_n) * tiles_m;
+  const int kb_total = columns / 256;
+  int splits = 1;
+  if (!gate_up) {
+    splits = static_cast<int>(ctx_.sm_count() / tiles);
+    if (ctx_.forced_splits() > 0) splits = ctx_.forced_splits();
+    if (splits > 8) splits = 8;
+    if (splits > kb_total) splits = kb_total;
+    if (splits < 1) splits = 1;
+    while (splits > 1 &&
+           (static_cast<size_t>(splits) * tiles * block_tok * 128 * sizeof(float) >
+                ctx_.partial_bytes() ||
+            static_cast<size_t>(tiles) > ctx_.counter_count())) {
+      --splits;
+    }
+  }
+  const uint64_t weight_rows = static_cast<uint64_t>(out_rows) * (gate_up ? 2 : 1);
+  CUtensorMap map_w, map_a;
+  TK100_TRY(ctx_.tensor_map(weight_codes, weight_rows, static_cast<uint64_t>(columns / 2), 128,
+                            &map_w));
+  TK100_TRY(ctx_.tensor_map(activation_codes, static_cast<uint64_t>(rows),
+                            static_cast<uint64_t>(columns / 2), static_cast<uint32_t>(block_tok),
+                            &map_a));
+  Nvfp4Params p{};
+  p.rows = rows;
+  p.out_rows = out_rows;
+  p.k = columns;
+  p.splits = splits;
+  p.up_row_offset = gate_up ? out_rows : 0;
+  p.w_scales = weight_scales;
+  p.a_scales = activation_scales;
+  // the reference passes 1/divisor to its kernel (nvfp4/swiglu.rs:541); both divisors here
+  p.out_scale = 1.0f / (weight_scale_divisor * input_global_divisor);
+  p.out = output;
+  p.partials = ctx_.partials();
+  p.counters = ctx_.counters();
+  p.status = ctx_.status_word();
+  ctx_.count_launch();
+  return ctx_.check(launch_nvfp4_gemm(stream, block_tok, gate_up, map_w, map_a, p),
+                    "launching the NVFP4 projection");
+}
+
 }  // namespace tk100
 
 // ------------------------------------------------------------------- C boundary
@@ -516,6 +631,43 @@ tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, i
                                  reinterpret_cast<const tk100::ArgmaxPair*>(gathered),
                                  reinterpret_cast<tk100::ArgmaxPair*>(output)),
       "launching the argmax merge");
+}
+
+tk100_status tk100_nvfp4_quantize_activation(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                             int columns, const uint16_t* input,
+                                             float input_global_divisor,
+                                             uint8_t* activation_codes,
+                                             uint8_t* activation_scales) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::Nvfp4MlpOp(*ctx->impl)
+      .quantize(static_cast<cudaStream_t>(stream), rows, columns, input, input_global_divisor,
+                activation_codes, activation_scales);
+}
+
+tk100_status tk100_nvfp4_gate_up_swiglu(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                        const uint16_t* input, uint8_t* activation_codes,
+                                        uint8_t* activation_scales, float input_global_divisor,
+                                        const uint8_t* weight_codes, const uint8_t* weight_scales,
+                                        float weight_scale_divisor, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  const tk100_config& c = ctx->impl->config();
+  return tk100::Nvfp4MlpOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), true, rows, static_cast<int>(c.intermediate),
+              static_cast<int>(c.hidden), input, activation_codes, activation_scales,
+              input_global_divisor, weight_codes, weight_scales, weight_scale_divisor, output);
+}
+
+tk100_status tk100_nvfp4_down(tk100_ctx* ctx, tk100_stream stream, int rows,
+                              const uint16_t* input, uint8_t* activation_codes,
+                              uint8_t* activation_scales, float input_global_divisor,
+                              const uint8_t* weight_codes, const uint8_t* weight_scales,
+                              float weight_scale_divisor, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  const tk100_config& c = ctx->impl->config();
+  return tk100::Nvfp4MlpOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), false, rows, static_cast<int>(c.hidden),
+              static_cast<int>(c.intermediate), input, activation_codes, activation_scales,
+              input_global_divisor, weight_codes, weight_scales, weight_scale_divisor, output);
 }
 
 }  // extern "C"

@@ -113,4 +113,24 @@ struct LmHeadOp : Fp8ProjectionOp {
   explicit LmHeadOp(Context& c) : Fp8ProjectionOp(c, "FP8 LM head") {}
 };
 
+// tuisko-kernels-sm89/src/nvfp4/swiglu.rs:470-571 and nvfp4/down.rs:455-556, with the
+// activation side quantised to NVFP4 as well (caller-owned code / scale planes, like the FP8
+// operators' activation planes) so that both operands feed the block-scaled tensor cores.
+class Nvfp4MlpOp {
+ public:
+  explicit Nvfp4MlpOp(Context& ctx) : ctx_(ctx) {}
+  Status quantize(cudaStream_t stream, int rows, int columns, const uint16_t* input,
+                  float input_global_divisor, uint8_t* activation_codes,
+                  uint8_t* activation_scales);
+  // gate_up = true: weights [2 * out_rows, columns / 2], output bf16(silu(gate) * up);
+  // gate_up = false: weights [out_rows, columns / 2], plain projection.
+  Status launch(cudaStream_t stream, bool gate_up, int rows, int out_rows, int columns,
+                const uint16_t* input, uint8_t* activation_codes, uint8_t* activation_scales,
+                float input_global_divisor, const uint8_t* weight_codes,
+                const uint8_t* weight_scales, float weight_scale_divisor, uint16_t* output);
+
+ private:
+  Context& ctx_;
+};
+
 }  // namespace tk100

@@ -186,6 +186,47 @@ class LmHeadOp:
                                           _ptr(gathered_pairs), _ptr(output_pairs)))
 
 
+def nvfp4_scale_plane_bytes(rows: int, columns: int) -> int:
+    """Bytes of a swizzled NVFP4 scale plane: rows padded to 128, one byte per 16 columns."""
+    return ((rows + 127) // 128) * 128 * (columns // 16)
+
+
+class _Nvfp4Op:
+    _entry = ""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def quantize(self, stream, rows, columns, input, input_global_divisor, activation_codes,
+                 activation_scales):
+        """NVFP4 activation quantiser (this library's own definition; see the header)."""
+        c = self.ctx
+        c.check(c._lib.tk100_nvfp4_quantize_activation(
+            c.handle, _stream(stream), rows, columns, _ptr(input), input_global_divisor,
+            _ptr(activation_codes), _ptr(activation_scales)))
+
+    def launch(self, stream, batch, input, weight_codes, weight_scales, weight_scale_divisor,
+               output, *, activation_codes, activation_scales, input_global_divisor):
+        """The reference's argument order, followed by the W4A4 additions as keywords."""
+        c = self.ctx
+        fn = getattr(c._lib, self._entry)
+        c.check(fn(c.handle, _stream(stream), batch, _ptr(input), _ptr(activation_codes),
+                   _ptr(activation_scales), input_global_divisor, _ptr(weight_codes),
+                   _ptr(weight_scales), weight_scale_divisor, _ptr(output)))
+
+
+class Nvfp4SwiGluOp(_Nvfp4Op):
+    """tuisko-kernels-sm89/src/nvfp4/swiglu.rs:470-571 (gate/up projection + SiLU * up)."""
+
+    _entry = "tk100_nvfp4_gate_up_swiglu"
+
+
+class Nvfp4DownOp(_Nvfp4Op):
+    """tuisko-kernels-sm89/src/nvfp4/down.rs:455-556."""
+
+    _entry = "tk100_nvfp4_down"
+
+
 STATIC_MAX_ROWS = 256
 STATIC_SCRATCH_BYTES = (8 << 20) + (16 << 10)
 

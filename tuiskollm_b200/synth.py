@@ -167,3 +167,50 @@ def torch_fp8_weights(seed: int, stream: int, out_rows: int, k: int, device, std
         codes[r0:r1] = q.view(torch.uint8)
         scales[r0:r1] = s
     return codes, scales
+
+
+def torch_nvfp4_quantize(w):
+    """fp32 CUDA tensor [rows, k] -> (codes uint8 [rows, k/2], swizzled scales uint8 [plane],
+    divisor float).  Same recipe as :func:`nvfp4_quantize_weights`, on the GPU."""
+    import torch
+
+    rows, k = w.shape
+    groups = k // 16
+    dev = w.device
+    amax_t = w.abs().max()
+    divisor = (torch.tensor(448.0 * 6.0, dtype=torch.float32, device=dev) / amax_t).float()
+    blocks = w.reshape(rows, groups, 16)
+    amax_b = blocks.abs().amax(dim=2)
+    raw = (amax_b * divisor) / 6.0
+    sc8 = raw.clamp(max=448.0).to(torch.float8_e4m3fn)
+    s = sc8.float()
+    safe = torch.where(s == 0, torch.ones_like(s), s)
+    q = (blocks * divisor) / safe[:, :, None]
+    a = q.abs()
+    mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=torch.float32, device=dev)
+    odd = torch.tensor([0, 1, 0, 1, 0, 1, 0], dtype=torch.bool, device=dev)
+    code = torch.zeros_like(a, dtype=torch.uint8)
+    for c in range(7):
+        up = (a > mids[c]) | ((a == mids[c]) & odd[c])
+        code += up.to(torch.uint8)
+    code = torch.where((s == 0)[:, :, None], torch.zeros_like(code), code)
+    sign = (torch.signbit(blocks).to(torch.uint8) << 3)
+    nib = (code | sign).reshape(rows, k)
+    codes = (nib[:, 0::2] | (nib[:, 1::2] << 4)).contiguous()
+    padded = ((rows + 127) // 128) * 128
+    plane = torch.zeros((padded // 128, groups // 4, 32, 4, 4), dtype=torch.uint8, device=dev)
+    sc = sc8.view(torch.uint8)
+    if padded != rows:
+        sc = torch.cat([sc, torch.zeros((padded - rows, groups), dtype=torch.uint8, device=dev)])
+    # [tile, quartile, row%32, group/4, group%4] -> [tile, group/4, row%32, quartile, group%4]
+    plane.copy_(sc.reshape(padded // 128, 4, 32, groups // 4, 4).permute(0, 3, 2, 1, 4))
+    return codes, plane.reshape(-1), float(divisor.item())
+
+
+def torch_nvfp4_weights(seed: int, stream: int, rows: int, k: int, device, std: float = 0.02):
+    import torch
+
+    g = torch.Generator(device=device)
+    g.manual_seed((seed * 1000003 + stream) & 0x7FFFFFFFFFFFFFFF)
+    w = torch.randn((rows, k), generator=g, device=device, dtype=torch.float32) * std
+    return torch_nvfp4_quantize(w)
