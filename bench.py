@@ -274,6 +274,160 @@ def extra_rows(torch, tk, ctx, peak_gbs):
         b = 10 * m * HIDDEN + m * HIDDEN + 4 * m
         out.append({"op": "residual_rmsnorm_quant_e4m3", "M": m, "us": ms * 1e3,
                     "GB/s": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs})
+    out.extend(nvfp4_rows(torch, tk, ctx))
+    out.extend(layer_slice_rows(torch, tk, ctx))
+    return out
+
+
+def measured_tensor_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+class MlpPlanes:
+    """Synthetic NVFP4 MLP weights + activation planes for `m` tokens."""
+
+    def __init__(self, torch, ops, synth, m, dev="cuda"):
+        inter = synth.INTERMEDIATE
+        self.m = m
+        self.gu_codes, self.gu_scales, self.gu_div = synth.torch_nvfp4_weights(
+            SEED, 300, 2 * inter, HIDDEN, dev)
+        self.dn_codes, self.dn_scales, self.dn_div = synth.torch_nvfp4_weights(
+            SEED, 301, HIDDEN, inter, dev)
+        self.a_codes = torch.empty((m, HIDDEN // 2), dtype=torch.uint8, device=dev)
+        self.a_scales = torch.zeros((ops.nvfp4_scale_plane_bytes(m, HIDDEN),), dtype=torch.uint8,
+                                    device=dev)
+        self.mid = torch.empty((m, inter), dtype=torch.bfloat16, device=dev)
+        self.m_codes = torch.empty((m, inter // 2), dtype=torch.uint8, device=dev)
+        self.m_scales = torch.zeros((ops.nvfp4_scale_plane_bytes(m, inter),), dtype=torch.uint8,
+                                    device=dev)
+        self.out = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=dev)
+        # activation divisors: a calibration constant for ~N(0,1) rows and for the SwiGLU
+        # output of these weights (|silu(g) * u| stays below ~8)
+        self.a_div = 448.0 * 6.0 / 6.0
+        self.m_div = 448.0 * 6.0 / 8.0
+
+
+def nvfp4_rows(torch, tk, ctx):
+    """NVFP4 MLP (configuration 4 at M = 2048, and decode shapes): each kernel as graph
+    replays; prefill in TFLOP/s against the block-scaled FP4 peak, decode in GB/s."""
+    from tuiskollm_b200 import ops, synth
+
+    inter = synth.INTERMEDIATE
+    burst, sustained, kind = measured_tensor_peaks()
+    hbm, _ = measured_peak()
+    out = []
+    for m in (2048, 256, 32, 8, 1):
+        pl = MlpPlanes(torch, ops, synth, m)
+        x = synth.torch_normal_bf16(SEED, 310, (m, HIDDEN), "cuda")
+        gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
+
+        def quant_in():
+            gu.quantize(None, m, HIDDEN, x, pl.a_div, pl.a_codes, pl.a_scales)
+
+        def gate_up():
+            gu.launch(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+                      activation_codes=pl.a_codes, activation_scales=pl.a_scales,
+                      input_global_divisor=pl.a_div)
+
+        def quant_mid():
+            dn.quantize(None, m, inter, pl.mid, pl.m_div, pl.m_codes, pl.m_scales)
+
+        def down():
+            dn.launch(None, m, None, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
+                      activation_codes=pl.m_codes, activation_scales=pl.m_scales,
+                      input_global_divisor=pl.m_div)
+
+        def mlp():
+            quant_in(); gate_up(); quant_mid(); down()
+
+        for fn in (quant_in, gate_up, quant_mid, down):
+            fn()
+        torch.cuda.synchronize()
+        times = {}
+        for name, fn in (("quant_in", quant_in), ("gate_up_swiglu", gate_up),
+                         ("quant_mid", quant_mid), ("down", down), ("mlp_total", mlp)):
+            graph = capture(torch, fn, 4)
+            for _ in range(3):
+                graph.replay()
+            reps = 10
+            times[name] = time_region(torch, graph.replay, reps) / (reps * 4)
+        f_gu = 2.0 * m * 2 * inter * HIDDEN
+        f_dn = 2.0 * m * HIDDEN * inter
+        b_gu = 2 * inter * HIDDEN // 2 + 2 * inter * HIDDEN // 16 + m * HIDDEN // 2 + m * HIDDEN // 16 + 2 * m * inter
+        b_dn = HIDDEN * inter // 2 + HIDDEN * inter // 16 + m * inter // 2 + m * inter // 16 + 2 * m * HIDDEN
+        row = {"op": "nvfp4_mlp", "M": m, "us": {k: v * 1e3 for k, v in times.items()},
+               "gate_up_TFLOPs": f_gu / times["gate_up_swiglu"] / 1e9,
+               "down_TFLOPs": f_dn / times["down"] / 1e9,
+               "mlp_TFLOPs": (f_gu + f_dn) / times["mlp_total"] / 1e9,
+               "gate_up_GBs": b_gu / times["gate_up_swiglu"] / 1e6,
+               "down_GBs": b_dn / times["down"] / 1e6}
+        if m >= 256:
+            row["gemm_frac_of_9PF"] = (f_gu + f_dn) / (times["gate_up_swiglu"] + times["down"]) / 1e9 / 9000.0
+            row["gemm_frac_of_4x_measured_bf16"] = ((f_gu + f_dn) / (times["gate_up_swiglu"] + times["down"])
+                                                    / 1e9 / (4 * burst))
+            row["tensor_peak_kind"] = kind
+        else:
+            row["gate_up_frac_of_measured_hbm"] = row["gate_up_GBs"] / hbm
+            row["down_frac_of_measured_hbm"] = row["down_GBs"] / hbm
+        out.append(row)
+        del pl
+    return out
+
+
+def layer_slice_rows(torch, tk, ctx):
+    """Configuration 5, one GPU: residual add + RMSNorm + E4M3 quantise -> FP8 QKV (N = 8192)
+    -> FP8 GDN-input (N = 12288) -> NVFP4 gate_up + SwiGLU -> NVFP4 down, as one CUDA graph."""
+    from tuiskollm_b200 import ops, synth
+
+    out = []
+    dev = "cuda"
+    qkv_w = synth.torch_fp8_weights(SEED, 400, synth.QKV_ROWS, HIDDEN, dev)
+    gdn_w = synth.torch_fp8_weights(SEED, 401, synth.GDN_ROWS, HIDDEN, dev)
+    nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)
+    weight_bytes = (synth.QKV_ROWS + synth.GDN_ROWS) * HIDDEN + 3 * synth.INTERMEDIATE * HIDDEN * 9 // 16
+    for m in (1, 256, 512):
+        pl = MlpPlanes(torch, ops, synth, m)
+        x = synth.torch_normal_bf16(SEED, 410, (m, HIDDEN), dev)
+        br = synth.torch_normal_bf16(SEED, 411, (m, HIDDEN), dev)
+        res = torch.empty_like(x)
+        nrm = torch.empty_like(x)
+        codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+        scales = torch.empty((m,), dtype=torch.float32, device=dev)
+        qkv = torch.empty((m, synth.QKV_ROWS), dtype=torch.bfloat16, device=dev)
+        gdn = torch.empty((m, synth.GDN_ROWS), dtype=torch.bfloat16, device=dev)
+        norm = tk.ResidualNormOp(ctx)
+        qkv_op = tk.FullAttentionQkvOp(ctx, synth.QKV_ROWS)
+        gdn_op = tk.GdnInputProjectionOp(ctx, synth.GDN_ROWS)
+        gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
+
+        def slice_():
+            norm.launch_quantize(None, m, x, br, nw, res, nrm, codes, scales)
+            qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
+            gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
+            gu.launch(None, m, nrm, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+                      activation_codes=pl.a_codes, activation_scales=pl.a_scales,
+                      input_global_divisor=pl.a_div)
+            dn.launch(None, m, pl.mid, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
+                      activation_codes=pl.m_codes, activation_scales=pl.m_scales,
+                      input_global_divisor=pl.m_div)
+
+        slice_()
+        torch.cuda.synchronize()
+        graph = capture(torch, slice_, 1)
+        for _ in range(5):
+            graph.replay()
+        reps = 50
+        ms = time_region(torch, graph.replay, reps) / reps
+        flops = 2.0 * m * HIDDEN * (synth.QKV_ROWS + synth.GDN_ROWS + 3 * synth.INTERMEDIATE)
+        out.append({"op": "layer_slice", "M": m, "us": ms * 1e3, "kernels": 7,
+                    "weight_stream_GBs": weight_bytes / ms / 1e6, "TFLOPs": flops / ms / 1e9,
+                    "floor_us_at_measured_hbm": weight_bytes / measured_peak()[0] / 1e3})
+        del pl
     return out
 
 

@@ -87,7 +87,9 @@ __global__ void __launch_bounds__(kThreads)
   const int nkb = kb_end - kb_begin;
 
   // A wait that timed out earlier in this stream has already made the results invalid:
-  // later CTAs leave at once instead of queueing more multi-second waits.
+  // later CTAs leave at once instead of queueing more multi-second waits.  (Under
+  // programmatic launch the predecessor may still be running; a fault it raises after this
+  // read is caught by this kernel's own bounded waits.)
   if (threadIdx.x == 0) ctl->is_last = *reinterpret_cast<volatile uint32_t*>(p.status);
   __syncthreads();
   if (ctl->is_last & STATUS_WAIT_TIMEOUT) return;
@@ -110,14 +112,29 @@ __global__ void __launch_bounds__(kThreads)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_base;
+  pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();  // weights are streamed once
       const uint64_t pol_a = l2_policy_evict_last();   // activation codes are re-read by every CTA
+      // First pass over the ring: the weight tiles do not depend on the predecessor kernel,
+      // so they are requested before pdl_wait(); the activation-code tiles of the same
+      // stages follow once the predecessor (the quantiser) is known to be complete.
+      const int pre = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&ctl->full[i], STAGE_BYTES);
+        tma_load_2d(smem + i * STAGE_BYTES, &tmap_w, &ctl->full[i], (kb_begin + i) * kTileKBytes,
+                    tile_n * kTileRows, pol_w);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        tma_load_2d(smem + i * STAGE_BYTES + kWStageBytes, &tmap_a, &ctl->full[i],
+                    (kb_begin + i) * kTileKBytes, tile_m * BLOCK_TOK, pol_a);
+      }
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
+      for (int i = pre; i < nkb && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (i / STAGES) & 1;
         ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
@@ -166,6 +183,7 @@ __global__ void __launch_bounds__(kThreads)
     const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
     const bool want_argmax = p.argmax_keys != nullptr;
 
+    pdl_wait();  // activation scales, scratch and outputs belong to the predecessor until now
     for (int j = et; j < BLOCK_TOK; j += kEpilogueThreads) {
       ctl->a_scale[j] = (j < valid_tok) ? p.act_scales[tok0 + j] : 0.0f;
       ctl->red[j] = 0ull;
@@ -292,6 +310,8 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 __global__ void argmax_finalize_kernel(int rows, unsigned long long* keys, ArgmaxPair* pairs) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows) return;
   const unsigned long long packed = keys[t];
@@ -306,6 +326,8 @@ __global__ void argmax_finalize_kernel(int rows, unsigned long long* keys, Argma
 
 __global__ void argmax_merge_kernel(int rows, int shards, const ArgmaxPair* gathered,
                                     ArgmaxPair* out) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows) return;
   unsigned long long best = 0ull;
@@ -329,9 +351,8 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUt
                        const Fp8ProjParams& p) {
   dim3 grid((p.out_rows + kTileRows - 1) / kTileRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK,
             p.splits);
-  fp8_projection_kernel<BLOCK_TOK>
-      <<<grid, kThreads, smem_bytes_for<BLOCK_TOK>(), stream>>>(tmap_w, tmap_a, p);
-  return cudaGetLastError();
+  return launch_kernel(fp8_projection_kernel<BLOCK_TOK>, grid, dim3(kThreads),
+                       smem_bytes_for<BLOCK_TOK>(), stream, tmap_w, tmap_a, p);
 }
 
 template <int BLOCK_TOK>
@@ -378,14 +399,14 @@ cudaError_t launch_fp8_projection(cudaStream_t stream, int block_tok, const CUte
 
 cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long long* keys,
                                    ArgmaxPair* pairs) {
-  argmax_finalize_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(rows, keys, pairs);
-  return cudaGetLastError();
+  return launch_kernel(argmax_finalize_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, rows,
+                       keys, pairs);
 }
 
 cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,
                                 const ArgmaxPair* gathered, ArgmaxPair* out) {
-  argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(rows, shards, gathered, out);
-  return cudaGetLastError();
+  return launch_kernel(argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, rows,
+                       shards, gathered, out);
 }
 
 }  // namespace tk100

@@ -15,6 +15,8 @@
 //   code = e4m3_rn_satfinite(y / scale)                  (IEEE fp32 divide)   *
 // The starred results are bit-exact functions of their inputs; `codes`/`scale`
 // are exact with respect to the normalised row this same kernel wrote.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -36,6 +38,8 @@ __global__ void __launch_bounds__(1024)
                          uint16_t* __restrict__ normalized_out, uint8_t* __restrict__ codes,
                          float* __restrict__ scales, int hidden, float eps, uint32_t* status) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();  // x / branch may be the predecessor's output
   const int row = blockIdx.x;
   const int chunks_per_row = hidden >> 3;
   const size_t row_off = static_cast<size_t>(row) * hidden;
@@ -133,20 +137,28 @@ cudaError_t launch_chunks(cudaStream_t stream, int rows, int hidden, int threads
                           const uint16_t* x, const uint16_t* branch, const uint16_t* weight,
                           uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
                           float* scales, float eps, uint32_t* status) {
-#define TK100_LAUNCH(C)                                                                        \
-  resnorm_quant_kernel<HAS_BRANCH, DO_NORM, DO_QUANT, C><<<rows, threads, 0, stream>>>(        \
-      x, branch, weight, residual_out, normalized_out, codes, scales, hidden, eps, status)
+#define TK100_LAUNCH(C)                                                                       \
+  launch_kernel(resnorm_quant_kernel<HAS_BRANCH, DO_NORM, DO_QUANT, C>, dim3(rows), dim3(threads), \
+                0, stream, x, branch, weight, residual_out, normalized_out, codes, scales, hidden, \
+                eps, status)
   switch (chunks) {
-    case 1: TK100_LAUNCH(1); break;
-    case 2: TK100_LAUNCH(2); break;
-    case 3: TK100_LAUNCH(3); break;
-    default: TK100_LAUNCH(4); break;
+    case 1: return TK100_LAUNCH(1);
+    case 2: return TK100_LAUNCH(2);
+    case 3: return TK100_LAUNCH(3);
+    default: return TK100_LAUNCH(4);
   }
 #undef TK100_LAUNCH
-  return cudaGetLastError();
 }
 
 }  // namespace
+
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* v = std::getenv("TK100_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
 
 bool norm_geometry(int hidden, int* threads, int* chunks) {
   if (hidden <= 0 || (hidden & 7) != 0) return false;

@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(kThreads)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_base;
+  pdl_trigger();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -137,28 +138,40 @@ __global__ void __launch_bounds__(kThreads)
       const uint8_t* sfa1 =
           p.w_scales + (static_cast<size_t>(p.up_row_offset / kRows + tile_n) * chunks_per_tile) * kSfChunk;
       const uint8_t* sfb = p.a_scales + (static_cast<size_t>(tok0 / kRows) * chunks_per_tile) * kSfChunk;
+      auto load_weights = [&](int i, int s) {
+        uint8_t* stage = smem + s * STAGE_BYTES;
+        const int kb = kb_begin + i;
+        const int kbyte = kb * kStageKBytes;
+        const size_t sf_off = static_cast<size_t>(kb) * kSfStage;
+        mbar_arrive_expect_tx(&ctl->full[s], STAGE_BYTES);
+        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kRows, pol_w);
+        bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, kSfStage, &ctl->full[s], pol_w);
+        if (GATE_UP) {
+          tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
+                      p.up_row_offset + tile_n * kRows, pol_w);
+          bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, kSfStage, &ctl->full[s], pol_w);
+        }
+      };
+      auto load_activations = [&](int i, int s) {
+        uint8_t* stage = smem + s * STAGE_BYTES;
+        const int kb = kb_begin + i;
+        tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kb * kStageKBytes, tok0, pol_a);
+        bulk_load_1d(stage + OFF_SFB, sfb + static_cast<size_t>(kb) * kSfStage, kSfStage,
+                     &ctl->full[s], pol_a);
+      };
+      // weights of the first ring pass before pdl_wait(), activation operands after it
+      const int pre = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < pre; ++i) load_weights(i, i);
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) load_activations(i, i);
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
+      for (int i = pre; i < nkb && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (i / STAGES) & 1;
         ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
         if (!ok) break;
-        uint8_t* stage = smem + s * STAGE_BYTES;
-        mbar_arrive_expect_tx(&ctl->full[s], STAGE_BYTES);
-        const int kb = kb_begin + i;
-        const int kbyte = kb * kStageKBytes;
-        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kRows, pol_w);
-        if (GATE_UP) {
-          tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
-                      p.up_row_offset + tile_n * kRows, pol_w);
-        }
-        tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kbyte, tok0, pol_a);
-        const size_t sf_off = static_cast<size_t>(kb) * kSfStage;
-        bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, kSfStage, &ctl->full[s], pol_w);
-        if (GATE_UP) {
-          bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, kSfStage, &ctl->full[s], pol_w);
-        }
-        bulk_load_1d(stage + OFF_SFB, sfb + sf_off, kSfStage, &ctl->full[s], pol_a);
+        load_weights(i, s);
+        load_activations(i, s);
       }
       if (!ok) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -210,6 +223,7 @@ __global__ void __launch_bounds__(kThreads)
     const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
     const float s = p.out_scale;
 
+    pdl_wait();  // scratch and outputs belong to the predecessor until now
     mbar_wait(&ctl->tmem_full, 0, p.status);
     tc_fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
@@ -321,6 +335,8 @@ __global__ void __launch_bounds__(kThreads)
 __global__ void __launch_bounds__(256)
     nvfp4_quantize_kernel(const uint16_t* __restrict__ x, int rows, int k, float divisor,
                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  pdl_trigger();
+  pdl_wait();
   const int groups = k >> 4;
   const long long total = static_cast<long long>(rows) * groups;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -365,9 +381,8 @@ template <int BLOCK_TOK, bool GATE_UP>
 cudaError_t nv_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                       const Nvfp4Params& p) {
   dim3 grid((p.out_rows + kRows - 1) / kRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK, p.splits);
-  nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>
-      <<<grid, kThreads, nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream>>>(tmap_w, tmap_a, p);
-  return cudaGetLastError();
+  return launch_kernel(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid, dim3(kThreads),
+                       nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, tmap_w, tmap_a, p);
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
@@ -406,9 +421,8 @@ cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const ui
   const long long total = static_cast<long long>(rows) * (k / 16);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  nvfp4_quantize_kernel<<<static_cast<unsigned int>(blocks), 256, 0, stream>>>(x, rows, k, divisor,
-                                                                             codes, scales);
-  return cudaGetLastError();
+  return launch_kernel(nvfp4_quantize_kernel, dim3(static_cast<unsigned int>(blocks)), dim3(256), 0,
+                       stream, x, rows, k, divisor, codes, scales);
 }
 
 }  // namespace tk100

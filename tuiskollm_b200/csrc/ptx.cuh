@@ -41,6 +41,18 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialisation attribute may start while
+// its predecessor in the stream is still running.  pdl_wait() blocks until every
+// predecessor grid has completed and its writes are visible; everything a kernel does
+// before it must not depend on, or disturb, the predecessor (weight prefetch, barrier and
+// TMEM set-up only).  pdl_trigger() lets the successor start launching.  Both are no-ops
+// for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------------------------------------ mbarrier
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
