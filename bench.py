@@ -312,7 +312,7 @@ class MlpPlanes:
         self.m_div = 448.0 * 6.0 / 8.0
 
 
-def nvfp4_rows(torch, tk, ctx):
+def nvfp4_rows(torch, tk, ctx, row_counts=(2048, 256, 32, 8, 1)):
     """NVFP4 MLP (configuration 4 at M = 2048, and decode shapes): each kernel as graph
     replays; prefill in TFLOP/s against the block-scaled FP4 peak, decode in GB/s."""
     from tuiskollm_b200 import ops, synth
@@ -321,7 +321,7 @@ def nvfp4_rows(torch, tk, ctx):
     burst, sustained, kind = measured_tensor_peaks()
     hbm, _ = measured_peak()
     out = []
-    for m in (2048, 256, 32, 8, 1):
+    for m in row_counts:
         pl = MlpPlanes(torch, ops, synth, m)
         x = synth.torch_normal_bf16(SEED, 310, (m, HIDDEN), "cuda")
         gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
@@ -429,6 +429,39 @@ def layer_slice_rows(torch, tk, ctx):
                     "floor_us_at_measured_hbm": weight_bytes / measured_peak()[0] / 1e3})
         del pl
     return out
+
+
+def run_case(args):
+    """One small side case on one GPU (for profiling): `nvfp4:M` or `fp8:N:M`."""
+    import torch
+
+    import tuiskollm_b200 as tk
+    from tuiskollm_b200 import synth
+
+    torch.cuda.set_device(0)
+    ctx = tk.Context(device=0)
+    parts = args.case.split(":")
+    if parts[0] == "nvfp4":
+        rows = nvfp4_rows(torch, tk, ctx, (int(parts[1]),))
+    elif parts[0] == "fp8":
+        n_rows, m = int(parts[1]), int(parts[2])
+        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, "cuda") for c in range(4)]
+        x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), "cuda")
+        codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device="cuda")
+        scales = torch.empty((m,), dtype=torch.float32, device="cuda")
+        outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device="cuda")
+        op = tk.GdnInputProjectionOp(ctx, n_rows)
+        op.launch(None, m, x, codes, scales, planes[0][0], planes[0][1], outp)
+        t0 = time.perf_counter()
+        for i in range(12):
+            op.launch(None, m, None, codes, scales, planes[i % 4][0], planes[i % 4][1], outp)
+        torch.cuda.synchronize()
+        rows = [{"op": "fp8", "N": n_rows, "M": m, "host_us_per_launch": (time.perf_counter() - t0) / 12 * 1e6}]
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    assert ctx.device_status() == 0
+    print(json.dumps({"case": args.case, "rows": rows}), flush=True)
+    return 0
 
 
 def run_native(args):
@@ -604,9 +637,12 @@ def main():
     ap.add_argument("--eager", action="store_true", help="launch every step from the host")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--case", default="", help="run one side case only: nvfp4:M or fp8:N:M")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.case:
+        return run_case(args)
     return run_native(args)
 
 
