@@ -431,6 +431,76 @@ def layer_slice_rows(torch, tk, ctx):
     return out
 
 
+def tp_layer_slice(torch, tk, dist, rank, world, m, local):
+    """Configuration 5 on `world` GPUs: norm + quantise replicated; QKV / GDN-input / gate-up
+    column-parallel; down row-parallel with fp32 partial sums, one NCCL all-reduce of
+    [m, hidden] fp32 and one rounding to BF16.  Returns the device time per replay (ms)."""
+    from tuiskollm_b200 import dist as tkd, ops, synth
+
+    dev = "cuda"
+    inter = synth.INTERMEDIATE
+    qkv_rows = tkd.column_shard(synth.QKV_ROWS, world, rank).rows
+    gdn_rows = tkd.column_shard(synth.GDN_ROWS, world, rank).rows
+    i_shard = tkd.column_shard(inter, world, rank).rows
+    ctx = tk.Context(device=local, hidden=HIDDEN, intermediate=i_shard, max_rows=max(2048, m))
+    qkv_w = synth.torch_fp8_weights(SEED, 500 + rank, qkv_rows, HIDDEN, dev)
+    gdn_w = synth.torch_fp8_weights(SEED, 520 + rank, gdn_rows, HIDDEN, dev)
+    gu_codes, gu_scales, gu_div = synth.torch_nvfp4_weights(SEED, 540 + rank, 2 * i_shard, HIDDEN, dev)
+    dn_codes, dn_scales, dn_div = synth.torch_nvfp4_weights(SEED, 560 + rank, HIDDEN, i_shard, dev)
+    nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)
+    x = synth.torch_normal_bf16(SEED, 410, (m, HIDDEN), dev)
+    br = synth.torch_normal_bf16(SEED, 411, (m, HIDDEN), dev)
+    res, nrm = torch.empty_like(x), torch.empty_like(x)
+    codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+    scales = torch.empty((m,), dtype=torch.float32, device=dev)
+    qkv = torch.empty((m, qkv_rows), dtype=torch.bfloat16, device=dev)
+    gdn = torch.empty((m, gdn_rows), dtype=torch.bfloat16, device=dev)
+    a_codes = torch.empty((m, HIDDEN // 2), dtype=torch.uint8, device=dev)
+    a_scales = torch.zeros((ops.nvfp4_scale_plane_bytes(m, HIDDEN),), dtype=torch.uint8, device=dev)
+    mid = torch.empty((m, i_shard), dtype=torch.bfloat16, device=dev)
+    m_codes = torch.empty((m, i_shard // 2), dtype=torch.uint8, device=dev)
+    m_scales = torch.zeros((ops.nvfp4_scale_plane_bytes(m, i_shard),), dtype=torch.uint8, device=dev)
+    partial = torch.empty((m, HIDDEN), dtype=torch.float32, device=dev)
+    out = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=dev)
+    norm = tk.ResidualNormOp(ctx)
+    qkv_op = tk.FullAttentionQkvOp(ctx, qkv_rows)
+    gdn_op = tk.GdnInputProjectionOp(ctx, gdn_rows)
+    gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
+    a_div, m_div = 448.0 * 6.0 / 6.0, 448.0 * 6.0 / 8.0
+
+    def slice_():
+        norm.launch_quantize(None, m, x, br, nw, res, nrm, codes, scales)
+        qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
+        gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
+        gu.launch(None, m, nrm, gu_codes, gu_scales, gu_div, mid, activation_codes=a_codes,
+                  activation_scales=a_scales, input_global_divisor=a_div)
+        dn.launch_partial(None, m, mid, dn_codes, dn_scales, dn_div, partial,
+                          activation_codes=m_codes, activation_scales=m_scales,
+                          input_global_divisor=m_div)
+        if world > 1:
+            dist.all_reduce(partial)
+        ops.f32_to_bf16(ctx, None, m * HIDDEN, partial, out)
+
+    slice_()
+    torch.cuda.synchronize()
+    mode = "graph"
+    try:
+        graph = capture(torch, slice_, 1)
+        run = graph.replay
+    except Exception as exc:
+        mode = f"eager ({type(exc).__name__})"
+        run = slice_
+        torch.cuda.synchronize()
+    for _ in range(5):
+        run()
+    if world > 1:
+        dist.barrier()
+    reps = 50
+    ms = time_region(torch, run, reps) / reps
+    assert ctx.device_status() == 0
+    return ms, mode
+
+
 def run_case(args):
     """One small side case on one GPU (for profiling): `nvfp4:M` or `fp8:N:M`."""
     import torch
@@ -452,15 +522,23 @@ def run_case(args):
         outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device="cuda")
         op = tk.GdnInputProjectionOp(ctx, n_rows)
         op.launch(None, m, x, codes, scales, planes[0][0], planes[0][1], outp)
-        t0 = time.perf_counter()
-        for i in range(12):
-            op.launch(None, m, None, codes, scales, planes[i % 4][0], planes[i % 4][1], outp)
-        torch.cuda.synchronize()
-        rows = [{"op": "fp8", "N": n_rows, "M": m, "host_us_per_launch": (time.perf_counter() - t0) / 12 * 1e6}]
+        state = {"i": 0}
+
+        def proj():
+            w, sc = planes[state["i"] % 4]
+            state["i"] += 1
+            op.launch(None, m, None, codes, scales, w, sc, outp)
+
+        graph = capture(torch, proj, 8)
+        for _ in range(3):
+            graph.replay()
+        ms = time_region(torch, graph.replay, 20) / 160
+        rows = [{"op": "fp8", "N": n_rows, "M": m, "us": ms * 1e3,
+                 "GB/s": algorithmic_bytes(m, n_rows, HIDDEN, 2) / ms / 1e6}]
     else:
         raise SystemExit(f"unknown case {args.case}")
-    assert ctx.device_status() == 0
-    print(json.dumps({"case": args.case, "rows": rows}), flush=True)
+    status = ctx.device_status()
+    print(json.dumps({"debug": os.environ.get("TK100_DEBUG", "0"), "status": status, "case": args.case, "rows": rows}), flush=True)
     return 0
 
 
@@ -562,10 +640,18 @@ def run_native(args):
     ms_proj = time_region(torch, projection_only, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([ms, ms_e2e, ms_proj], dtype=torch.float64, device=dev)
+    tp = []
+    if world > 1 and not args.no_extra:
+        for m_tp in (256, 1):
+            t_ms, t_mode = tp_layer_slice(torch, tk, dist, rank, world, m_tp, local)
+            tp.append([m_tp, t_ms, t_mode])
+    times = torch.tensor([ms, ms_e2e, ms_proj] + [t[1] for t in tp], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, ms_e2e, ms_proj = [float(v) for v in times.tolist()]
+    vals = [float(v) for v in times.tolist()]
+    ms, ms_e2e, ms_proj = vals[:3]
+    for t, v in zip(tp, vals[3:]):
+        t[1] = v
 
     # sanity: the selected token is the arg-max of the logits this step wrote
     run_step()
@@ -609,6 +695,11 @@ def run_native(args):
             "clocks": clocks,
             "selected_tokens": final[:, 1].tolist()[:8],
         }
+        if tp:
+            line["tp_layer_slice"] = [
+                {"M": t[0], "us": t[1] * 1e3, "launch": t[2], "all_reduce_bytes": t[0] * HIDDEN * 4,
+                 "parallelism": f"column(QKV,GDN-in,gate_up) + row(down) x{world}, fp32 all-reduce"}
+                for t in tp]
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, note, _ = cpu_lm_head(m, 3, 1, budget_s=15.0,
                                                     sample_rows=args.cpu_sample_rows)

@@ -171,7 +171,7 @@ TK100_API tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, i
  *   scale = e4m3_rne_sat((amax * divisor) / 6),  code = e2m1_rne_sat((x * divisor) / scale),
  * represented value = e2m1 * scale / divisor.  activation_codes [rows, columns/2] (low
  * nibble = even column); activation_scales in the same 128-row x 4-group tiles as weight
- * scales with row = token, sized ceil(rows/128)*128 * columns/16 bytes.  columns % 256 == 0. */
+ * scales with row = token, sized ceil(rows/128)*128 * columns/16 bytes.  columns % 64 == 0. */
 TK100_API tk100_status tk100_nvfp4_quantize_activation(tk100_ctx* ctx, tk100_stream stream, int rows,
                                              int columns, const uint16_t* input,
                                              float input_global_divisor,
@@ -200,6 +200,20 @@ TK100_API tk100_status tk100_nvfp4_down(tk100_ctx* ctx, tk100_stream stream, int
                               uint8_t* activation_scales, float input_global_divisor,
                               const uint8_t* weight_codes, const uint8_t* weight_scales,
                               float weight_scale_divisor, uint16_t* output);
+
+/* Tensor-parallel form of tk100_nvfp4_down (no reference counterpart: the reference is
+ * single-GPU).  A rank that owns a slice of the reduction (config.intermediate = its slice,
+ * a multiple of 64 columns; weight and activation planes hold only that slice) writes its
+ * unrounded fp32 partial sums [rows, hidden]; the ranks' partials are summed with one NCCL
+ * all-reduce and rounded once with tk100_f32_to_bf16. */
+TK100_API tk100_status tk100_nvfp4_down_partial(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                      const uint16_t* input, uint8_t* activation_codes,
+                                      uint8_t* activation_scales, float input_global_divisor,
+                                      const uint8_t* weight_codes, const uint8_t* weight_scales,
+                                      float weight_scale_divisor, float* partial_output);
+/* fp32 -> BF16, round to nearest even; count % 4 == 0. */
+TK100_API tk100_status tk100_f32_to_bf16(tk100_ctx* ctx, tk100_stream stream, size_t count,
+                               const float* input, uint16_t* output);
 
 /* No counterpart in the reference.  The FP8 projection (activation codes and scales already
  * produced, as with input == NULL above) for hosts that must not allocate device memory and

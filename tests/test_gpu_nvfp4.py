@@ -198,6 +198,55 @@ def test_synthetic_mlp_small_geometry(tk, oracle, rows):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("world,rows", [(2, 5), (8, 40), (8, 200)])
+def test_row_parallel_down_shards_sum_to_the_full_projection(tk, oracle, world, rows):
+    """Tensor-parallel down projection emulated on one GPU: every rank's reduction shard
+    (at world 8 the shard is 384 columns = one full 256-column stage + a 128-column tail)
+    produces fp32 partial sums; their sum, rounded once, matches the W4A4 oracle on the whole
+    reduction and the single-rank kernel."""
+    from tuiskollm_b200 import ops, synth
+
+    hidden, inter = 1024, 3072
+    xb = synth.normal_bf16(6, rows, (rows, inter))
+    w_codes, w_scales, w_div = synth.nvfp4_weights(6, 1, hidden, inter)
+    a_div = float(np.float32(448.0 * 6.0 / 5.0))
+    full_ctx = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=256)
+    codes, scales = act_planes(tk, rows, inter)
+    full = sentinel_plane((rows, hidden), torch.int16)
+    tk.Nvfp4DownOp(full_ctx).launch(None, rows, dev(xb.view(np.int16)), dev(w_codes), dev(w_scales),
+                                    float(w_div), full, activation_codes=codes,
+                                    activation_scales=scales, input_global_divisor=a_div)
+    torch.cuda.synchronize()
+    oc, osc = oracle.nvfp4_quantize(xb, a_div)
+    exp = oracle.nvfp4_w4a4_dot(oc, osc, a_div, w_codes, w_scales, float(w_div))
+    ks = inter // world
+    shard_ctx = tk.Context(device=0, hidden=hidden, intermediate=ks, max_rows=256)
+    total = np.zeros((rows, hidden), np.float64)
+    for r in range(world):
+        wc_r, ws_r = synth.nvfp4_reduction_shard(w_codes, w_scales, inter, world, r)
+        x_r = np.ascontiguousarray(xb[:, r * ks:(r + 1) * ks])
+        c_r, s_r = act_planes(tk, rows, ks)
+        part = sentinel_plane((rows + 1, hidden), torch.float32)
+        tk.Nvfp4DownOp(shard_ctx).launch_partial(None, rows, dev(x_r.view(np.int16)), dev(wc_r),
+                                                 dev(ws_r), float(w_div), part, activation_codes=c_r,
+                                                 activation_scales=s_r, input_global_divisor=a_div)
+        torch.cuda.synchronize()
+        # block-local quantisation: the shard's codes are the matching columns of the full plane
+        assert np.array_equal(host(c_r)[:rows], oc[:, r * ks // 2:(r + 1) * ks // 2])
+        assert_inactive_untouched(part, rows)
+        total += host(part)[:rows].astype(np.float64)
+    floor = 4 * float(np.abs(exp).mean())
+    assert (np.abs(total - exp) / np.maximum(np.abs(exp), floor)).max() <= 2e-3
+    summed = torch.from_numpy(total.astype(np.float32)).cuda()
+    rounded = sentinel_plane((rows, hidden), torch.int16)
+    ops.f32_to_bf16(shard_ctx, None, rows * hidden, summed, rounded)
+    torch.cuda.synchronize()
+    assert np.array_equal(_u16(rounded), oracle.f32_to_bf16(total.astype(np.float32)))
+    assert max_relative_error(_u16(rounded), exp, floor) <= 1e-2
+    assert max_relative_error(_u16(full), exp, floor) <= 1e-2
+    assert shard_ctx.device_status() == 0 and full_ctx.device_status() == 0
+
+
 def test_full_size_prefill_sampled_tiles(tk, ctx, oracle):
     """Configuration 4 (M = 2048, gate_up 34816 x 5120, down 5120 x 17408): too large for the
     CPU oracle as a whole, so whole 128-row tiles are sampled -- first, last and two inner

@@ -32,9 +32,12 @@ constexpr int kTileKBytes = 128; // K bytes per stage (one 128-byte swizzle row)
 constexpr int kWStageBytes = kTileRows * kTileKBytes;
 constexpr int kThreads = 192;    // warp 0: TMA, warp 1: UMMA + TMEM, warps 2-5: epilogue
 constexpr int kEpilogueThreads = 128;
+constexpr int kMaxSplits = 8;     // upper bound of gridDim.z (the host never asks for more)
 
 __host__ __device__ constexpr int stages_for(int block_tok) {
-  return block_tok <= 16 ? 6 : block_tok <= 32 ? 5 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
+  // <= 32 tokens: three CTAs share an SM (a third slot lets the next kernel's CTAs start their
+  // weight prefetch under this kernel's tail); 64: two; 128 and 256: one.
+  return block_tok <= 16 ? 4 : block_tok <= 32 ? 3 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
 }
 
 template <int BLOCK_TOK>
@@ -65,7 +68,7 @@ __device__ __forceinline__ uint32_t total_order_key(uint32_t bits) {
 }
 
 template <int BLOCK_TOK>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? 3 : (BLOCK_TOK <= 64 ? 2 : 1))
     fp8_projection_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_a, const Fp8ProjParams p) {
   constexpr int STAGES = stages_for(BLOCK_TOK);
@@ -92,7 +95,18 @@ __global__ void __launch_bounds__(kThreads)
   // read is caught by this kernel's own bounded waits.)
   if (threadIdx.x == 0) ctl->is_last = *reinterpret_cast<volatile uint32_t*>(p.status);
   __syncthreads();
-  if (ctl->is_last & STATUS_WAIT_TIMEOUT) return;
+  const bool dead = (ctl->is_last & STATUS_WAIT_TIMEOUT) != 0;
+  const bool clustered = p.cluster != 0 && p.splits > 1;
+  if (dead) {
+    // still owed to the other CTAs of the cluster: both cluster barriers
+    if (clustered) {
+      cluster_arrive();
+      cluster_wait();
+      cluster_arrive();
+      cluster_wait();
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -122,14 +136,16 @@ __global__ void __launch_bounds__(kThreads)
       // First pass over the ring: the weight tiles do not depend on the predecessor kernel,
       // so they are requested before pdl_wait(); the activation-code tiles of the same
       // stages follow once the predecessor (the quantiser) is known to be complete.
+      const bool load_a = !(p.debug & DBG_NO_ACT);
+      const uint32_t tx_bytes = load_a ? STAGE_BYTES : kWStageBytes;
       const int pre = nkb < STAGES ? nkb : STAGES;
       for (int i = 0; i < pre; ++i) {
-        mbar_arrive_expect_tx(&ctl->full[i], STAGE_BYTES);
+        mbar_arrive_expect_tx(&ctl->full[i], tx_bytes);
         tma_load_2d(smem + i * STAGE_BYTES, &tmap_w, &ctl->full[i], (kb_begin + i) * kTileKBytes,
                     tile_n * kTileRows, pol_w);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i) {
+      for (int i = 0; i < pre && load_a; ++i) {
         tma_load_2d(smem + i * STAGE_BYTES + kWStageBytes, &tmap_a, &ctl->full[i],
                     (kb_begin + i) * kTileKBytes, tile_m * BLOCK_TOK, pol_a);
       }
@@ -140,10 +156,12 @@ __global__ void __launch_bounds__(kThreads)
         ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
         if (!ok) break;
         uint8_t* stage = smem + s * STAGE_BYTES;
-        mbar_arrive_expect_tx(&ctl->full[s], STAGE_BYTES);
+        mbar_arrive_expect_tx(&ctl->full[s], tx_bytes);
         const int kbyte = (kb_begin + i) * kTileKBytes;
         tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kTileRows, pol_w);
-        tma_load_2d(stage + kWStageBytes, &tmap_a, &ctl->full[s], kbyte, tile_m * BLOCK_TOK, pol_a);
+        if (load_a) {
+          tma_load_2d(stage + kWStageBytes, &tmap_a, &ctl->full[s], kbyte, tile_m * BLOCK_TOK, pol_a);
+        }
       }
       if (!ok) {
         // Give copies already in flight time to land before shared memory is released.
@@ -165,6 +183,7 @@ __global__ void __launch_bounds__(kThreads)
         const uint64_t desc_a = umma_desc_sw128(w_addr + kWStageBytes);
 #pragma unroll
         for (int k4 = 0; k4 < kTileKBytes / 32; ++k4) {
+          if (p.debug & DBG_NO_MMA) break;
           // +2 in the address field = +32 bytes along K inside the swizzled row
           umma_f8f6f4(tmem, desc_w + 2 * k4, desc_a + 2 * k4, IDESC, (i | k4) != 0);
         }
@@ -221,7 +240,9 @@ __global__ void __launch_bounds__(kThreads)
       }
     };
 
-    if (p.splits == 1) {
+    if (p.debug & DBG_NO_EPILOGUE) {
+      // experiment: accumulator left unread
+    } else if (p.splits == 1) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
         if (c0 >= valid_tok) break;  // warp-uniform
@@ -231,6 +252,21 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (c0 + j < valid_tok) emit(c0 + j, __uint_as_float(r[j]));
+        }
+      }
+    } else if (clustered) {
+      // Own partial tile -> own shared memory ([token][row] fp32, over ring stage 0, which
+      // this CTA's MMAs have finished reading once tmem_full has fired).
+      float* mine = reinterpret_cast<float*>(smem) + row_in_tile;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+        if (c0 >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok) mine[(c0 + j) * kTileRows] = __uint_as_float(r[j]);
         }
       }
     } else {
@@ -246,10 +282,10 @@ __global__ void __launch_bounds__(kThreads)
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          if (c0 + j < valid_tok) __stcg(mine + (c0 + j) * kTileRows, __uint_as_float(r[j]));
+          if (c0 + j < valid_tok && !(p.debug & 8)) __stcg(mine + (c0 + j) * kTileRows, __uint_as_float(r[j]));
         }
       }
-      __threadfence();
+      if (!(p.debug & 16)) __threadfence();
       epilogue_barrier();
       if (et == 0) {
         unsigned int* counter = p.counters + tile_m * gridDim.x + tile_n;
@@ -259,7 +295,7 @@ __global__ void __launch_bounds__(kThreads)
         ctl->is_last = last ? 1u : 0u;
       }
       epilogue_barrier();
-      if (ctl->is_last) {
+      if (ctl->is_last && !(p.debug & 32)) {
         __threadfence();
         const size_t split_stride =
             static_cast<size_t>(gridDim.y) * gridDim.x * (BLOCK_TOK * kTileRows);
@@ -267,38 +303,86 @@ __global__ void __launch_bounds__(kThreads)
                             (static_cast<size_t>(tile_m) * gridDim.x + tile_n) *
                                 (BLOCK_TOK * kTileRows) +
                             row_in_tile;
-        // Eight tokens at a time: all loads of a batch are issued before the first add, so
-        // the L2 round trips overlap instead of forming one dependent chain per token.
+        // Four tokens at a time, every split's value of the batch requested before the
+        // first add: one L2 round trip per batch instead of one per (token, split).
 #pragma unroll 1
-        for (int j0 = 0; j0 < valid_tok; j0 += 8) {
-          float acc[8];
+        for (int j0 = 0; j0 < valid_tok; j0 += 4) {
+          float v[kMaxSplits][4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-          for (int s = 0; s < p.splits; ++s) {
-            float v[8];
+          for (int s = 0; s < kMaxSplits; ++s) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              v[j] = (j0 + j < valid_tok) ? __ldcg(base + s * split_stride + (j0 + j) * kTileRows)
-                                          : 0.0f;
+            for (int j = 0; j < 4; ++j) {
+              v[s][j] = (s < p.splits && j0 + j < valid_tok)
+                            ? __ldcg(base + s * split_stride + (j0 + j) * kTileRows)
+                            : 0.0f;
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], v[j]);
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (j0 + j < valid_tok) emit(j0 + j, acc[j]);
+          for (int j = 0; j < 4; ++j) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int s = 0; s < kMaxSplits; ++s) {
+              if (s < p.splits) acc = __fadd_rn(acc, v[s][j]);  // fixed split order
+            }
+            if (j0 + j < valid_tok) emit(j0 + j, acc);
           }
         }
       }
     }
 
-    if (want_argmax && (p.splits == 1 || ctl->is_last)) {
+    if (clustered) {
+      // Every CTA of the cluster has published its tile after the first barrier; CTA `rank`
+      // then finishes the tokens j = rank, rank + splits, ...: partials are read from the
+      // peers' shared memory and added in split order (fixed, so bit-reproducible).
+      cluster_arrive();
+      cluster_wait();
+      if (!(p.debug & DBG_NO_EPILOGUE)) {
+        const uint32_t rank = cluster_cta_rank();
+        const uint32_t my_addr = smem_u32(reinterpret_cast<float*>(smem) + row_in_tile);
+#pragma unroll 1
+        for (int j0 = static_cast<int>(rank); j0 < valid_tok; j0 += 2 * p.splits) {
+          float v[2][kMaxSplits];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int j = j0 + u * p.splits;
+#pragma unroll
+            for (int s = 0; s < kMaxSplits; ++s) {
+              v[u][s] = (j < valid_tok && s < p.splits)
+                            ? ld_dsmem_f32(my_addr + j * kTileRows * 4, static_cast<uint32_t>(s))
+                            : 0.0f;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int j = j0 + u * p.splits;
+            float acc = 0.0f;
+#pragma unroll
+            for (int s = 0; s < kMaxSplits; ++s) {
+              if (s < p.splits) acc = __fadd_rn(acc, v[u][s]);
+            }
+            if (j < valid_tok) emit(j, acc);
+          }
+        }
+      }
+      cluster_arrive();  // nobody's shared memory may go away while a peer still reads it
+      cluster_wait();
+    }
+
+    if (want_argmax && !(p.debug & DBG_NO_EPILOGUE) &&
+        (p.splits == 1 || clustered || ctl->is_last)) {
       epilogue_barrier();
       for (int j = et; j < valid_tok; j += kEpilogueThreads) {
         const unsigned long long best = ctl->red[j];
         if (best != 0ull) atomicMax(p.argmax_keys + tok0 + j, best);
       }
     }
+  }
+  if (clustered && warp < 2) {
+    // the TMA and UMMA warps take part in the two cluster barriers of the reduction
+    cluster_arrive();
+    cluster_wait();
+    cluster_arrive();
+    cluster_wait();
   }
 
   tc_fence_before_sync();
@@ -351,8 +435,9 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUt
                        const Fp8ProjParams& p) {
   dim3 grid((p.out_rows + kTileRows - 1) / kTileRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK,
             p.splits);
-  return launch_kernel(fp8_projection_kernel<BLOCK_TOK>, grid, dim3(kThreads),
-                       smem_bytes_for<BLOCK_TOK>(), stream, tmap_w, tmap_a, p);
+  const unsigned int cluster_z = (p.cluster && p.splits > 1) ? static_cast<unsigned int>(p.splits) : 1u;
+  return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK>, grid, dim3(kThreads),
+                               smem_bytes_for<BLOCK_TOK>(), stream, cluster_z, tmap_w, tmap_a, p);
 }
 
 template <int BLOCK_TOK>

@@ -13,20 +13,43 @@ namespace tk100 {
 // that a kernel's set-up and weight prefetch overlap the tail of its predecessor.
 bool pdl_enabled();
 
+// Performance-experiment switches read once from TK100_DEBUG (results are wrong when any is
+// set): 1 = skip the epilogue, 2 = skip the UMMA issue, 4 = skip the activation loads.
+enum : uint32_t { DBG_NO_EPILOGUE = 1, DBG_NO_MMA = 2, DBG_NO_ACT = 4 };
+uint32_t debug_flags();
+
+// cluster_z > 1 launches thread-block clusters of (1, 1, cluster_z) CTAs.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                          cudaStream_t stream, Args&&... args) {
+cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, unsigned int cluster_z, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args&&... args) {
+  return launch_kernel_cluster(kernel, grid, block, smem, stream, 1u, std::forward<Args>(args)...);
 }
 
 // ---------------------------------------------------------------- norm_quant.cu
@@ -46,6 +69,8 @@ struct Fp8ProjParams {
   int out_rows;   // weight rows N (this shard)
   int k;          // reduction length, multiple of 128
   int splits;     // K splits (grid.z)
+  int cluster;    // 1: the splits of a tile form a thread-block cluster and reduce over
+                  // distributed shared memory; 0: fp32 partial tiles in `partials` + tickets
   const float* act_scales;      // [rows]
   const uint16_t* w_scales;     // [out_rows] BF16
   uint16_t* out;                // [rows, out_rows] BF16, may be null for the LM head
@@ -55,6 +80,7 @@ struct Fp8ProjParams {
   float* partials;              // split-K scratch
   unsigned int* counters;       // one per output tile, zero between launches
   uint32_t* status;
+  uint32_t debug;               // experiment switches (debug_flags()); 0 in normal use
 };
 
 // block_tok is the token tile (16, 32, 64, 128 or 256).
@@ -86,9 +112,11 @@ struct Nvfp4Params {
   const uint8_t* a_scales;  // swizzled E4M3 activation scales
   float out_scale;     // 1 / (weight divisor * activation divisor)
   uint16_t* out;       // [rows, out_rows] BF16
+  float* out_f32;      // when set (plain projection only): unrounded fp32 output instead
   float* partials;
   unsigned int* counters;
   uint32_t* status;
+  uint32_t debug;      // experiment switches (debug_flags()); 0 in normal use
 };
 
 cudaError_t nvfp4_prepare();
@@ -97,6 +125,7 @@ cudaError_t nvfp4_prepare();
 cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,
                               const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                               const Nvfp4Params& p);
+cudaError_t launch_f32_to_bf16(cudaStream_t stream, long long n, const float* in, uint16_t* out);
 cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const uint16_t* x,
                                   float divisor, uint8_t* codes, uint8_t* scales);
 

@@ -160,6 +160,14 @@ bool pdl_enabled() {
   return enabled;
 }
 
+uint32_t debug_flags() {
+  static const uint32_t flags = [] {
+    const char* v = std::getenv("TK100_DEBUG");
+    return v ? static_cast<uint32_t>(std::atoi(v)) : 0u;
+  }();
+  return flags;
+}
+
 bool norm_geometry(int hidden, int* threads, int* chunks) {
   if (hidden <= 0 || (hidden & 7) != 0) return false;
   const int row_chunks = hidden >> 3;

@@ -32,7 +32,8 @@ constexpr int kStageK = 256;         // elements
 constexpr int kWTile = kRows * kStageKBytes;  // 16 KB
 constexpr int kSfChunk = 512;        // scales of 128 rows x 4 groups (one UMMA K = 64)
 constexpr int kSfStage = 4 * kSfChunk;  // 2 KB: 128 rows x 16 groups
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;        // warp 0: TMA, warp 1: UMMA + TMEM, warps 2-9: epilogue
+constexpr int kEpilogueThreads = 256; // two warps per TMEM lane quadrant, alternate 16-column chunks
 constexpr int kSfSlots = 8;          // TMEM scale slots in rotation
 constexpr int kSfSlotCols = 16;      // columns per slot: SFA0 [0,4) SFA1 [4,8) SFB [8,12)
 
@@ -61,7 +62,7 @@ __host__ __device__ constexpr size_t nv_smem_bytes() {
 }
 
 __device__ __forceinline__ void nv_epilogue_barrier() {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 }
 
 // silu(v) in the sign-stable form of the reference's NVFP4 route
@@ -70,7 +71,7 @@ __device__ __forceinline__ float silu_stable(float v) {
   const float e = -fabsf(v) * 1.4426950408889634f;
   float ex = 0.0f;
   if (e >= -126.0f) asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(e));
-  return v >= 0.0f ? __fdiv_rn(v, 1.0f + ex) : __fdiv_rn(v * ex, 1.0f + ex);
+  return __fdividef(v >= 0.0f ? v : v * ex, 1.0f + ex);
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
@@ -96,8 +97,11 @@ __global__ void __launch_bounds__(kThreads)
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + STAGES * STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
-  const int kb_total = p.k / kStageK;
+  // token tiles vary fastest so that the CTAs sharing a weight tile run together (L2 reuse)
+  const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
+  const int tiles_m = gridDim.x, tiles_n = gridDim.y;
+  // K is a multiple of 64 (one UMMA K); the last 256-element stage may hold 1..4 such steps.
+  const int kb_total = (p.k + kStageK - 1) / kStageK;
   const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / p.splits);
   const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / p.splits);
   const int nkb = kb_end - kb_begin;
@@ -129,8 +133,9 @@ __global__ void __launch_bounds__(kThreads)
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_a = l2_policy_evict_last();
+      // weights are streamed once when there is a single token tile, shared otherwise
+      const uint64_t pol_w = tiles_m == 1 ? l2_policy_evict_first() : pol_a;
       // Scale tiles: chunk (tile, kb) of a plane with G = K/16 groups per row starts at
       // ((tile * G/4) + 4 * kb) * 512 bytes and is 2 KB long (4 consecutive 512-byte chunks).
       const size_t chunks_per_tile = static_cast<size_t>(p.k / 64);
@@ -143,20 +148,29 @@ __global__ void __launch_bounds__(kThreads)
         const int kb = kb_begin + i;
         const int kbyte = kb * kStageKBytes;
         const size_t sf_off = static_cast<size_t>(kb) * kSfStage;
-        mbar_arrive_expect_tx(&ctl->full[s], STAGE_BYTES);
+        // scale bytes of this stage: 512 per 64-element step that exists (the code tiles always
+        // arrive as full boxes, zero-filled beyond the end of the row)
+        const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
+        const uint32_t code_bytes = NW * kWTile + BLOCK_TOK * kStageKBytes;
+        mbar_arrive_expect_tx(&ctl->full[s],
+                              (p.debug & DBG_NO_ACT)
+                                  ? NW * (kWTile + sf_bytes)
+                                  : code_bytes + (NW + 1) * sf_bytes);
         tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kRows, pol_w);
-        bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, kSfStage, &ctl->full[s], pol_w);
+        bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, sf_bytes, &ctl->full[s], pol_w);
         if (GATE_UP) {
           tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
                       p.up_row_offset + tile_n * kRows, pol_w);
-          bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, kSfStage, &ctl->full[s], pol_w);
+          bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, sf_bytes, &ctl->full[s], pol_w);
         }
       };
       auto load_activations = [&](int i, int s) {
+        if (p.debug & DBG_NO_ACT) return;
         uint8_t* stage = smem + s * STAGE_BYTES;
         const int kb = kb_begin + i;
         tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kb * kStageKBytes, tok0, pol_a);
-        bulk_load_1d(stage + OFF_SFB, sfb + static_cast<size_t>(kb) * kSfStage, kSfStage,
+        const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
+        bulk_load_1d(stage + OFF_SFB, sfb + static_cast<size_t>(kb) * kSfStage, sf_bytes,
                      &ctl->full[s], pol_a);
       };
       // weights of the first ring pass before pdl_wait(), activation operands after it
@@ -194,8 +208,10 @@ __global__ void __launch_bounds__(kThreads)
         const uint64_t desc_w0 = umma_desc_sw128(base);
         const uint64_t desc_w1 = umma_desc_sw128(base + kWTile);
         const uint64_t desc_a = umma_desc_sw128(base + OFF_A);
+        const int steps = min(4, (p.k - (kb_begin + i) * kStageK) / 64);
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
+          if (k4 >= steps || (p.debug & DBG_NO_MMA)) break;
           const uint32_t slot = sf_base + static_cast<uint32_t>(((i * 4 + k4) % kSfSlots) * kSfSlotCols);
           tmem_cp_32x128b_warpx4(slot, umma_desc_noswizzle_rows16(base + OFF_SFA + k4 * kSfChunk));
           if (GATE_UP) {
@@ -215,8 +231,9 @@ __global__ void __launch_bounds__(kThreads)
       umma_commit(&ctl->tmem_full);
     }
   } else {
-    const int et = threadIdx.x - 64;
-    const int quad = warp & 3;
+    const int et = threadIdx.x - 64;   // 0..255
+    const int quad = warp & 3;         // TMEM lane quadrant of this warp
+    const int half = (warp - 2) >> 2;  // which of the two warps of the quadrant
     const int row_in_tile = quad * 32 + lane;
     const int n = tile_n * kRows + row_in_tile;
     const bool row_ok = n < p.out_rows;
@@ -228,9 +245,11 @@ __global__ void __launch_bounds__(kThreads)
     tc_fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
-    if (GATE_UP) {
+    if (p.debug & DBG_NO_EPILOGUE) {
+      // experiment: accumulators left unread
+    } else if (GATE_UP) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
         if (c0 >= valid_tok) break;
         uint32_t g[16], u[16];
         tmem_ld16(taddr + c0, g);
@@ -248,7 +267,7 @@ __global__ void __launch_bounds__(kThreads)
       }
     } else if (p.splits == 1) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
         if (c0 >= valid_tok) break;
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
@@ -256,18 +275,20 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (c0 + j < valid_tok && row_ok) {
-            p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
-                static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(__uint_as_float(r[j]), s)));
+            const size_t o = static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n;
+            const float v = __fmul_rn(__uint_as_float(r[j]), s);
+            if (p.out_f32) p.out_f32[o] = v;
+            else p.out[o] = static_cast<uint16_t>(f32_to_bf16_bits(v));
           }
         }
       }
     } else {
       // split-K: fixed-order sum of fp32 partial tiles by the last CTA to arrive
       const size_t tile_elems = static_cast<size_t>(BLOCK_TOK) * kRows;
-      const size_t tile_index = (static_cast<size_t>(split) * gridDim.y + tile_m) * gridDim.x + tile_n;
+      const size_t tile_index = (static_cast<size_t>(split) * tiles_m + tile_m) * tiles_n + tile_n;
       float* mine = p.partials + tile_index * tile_elems + row_in_tile;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
         if (c0 >= valid_tok) break;
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
@@ -280,7 +301,7 @@ __global__ void __launch_bounds__(kThreads)
       __threadfence();
       nv_epilogue_barrier();
       if (et == 0) {
-        unsigned int* counter = p.counters + tile_m * gridDim.x + tile_n;
+        unsigned int* counter = p.counters + tile_m * tiles_n + tile_n;
         const unsigned int ticket = atomicAdd(counter, 1u);
         const bool last = ticket == static_cast<unsigned int>(p.splits - 1);
         if (last) *counter = 0u;
@@ -289,28 +310,37 @@ __global__ void __launch_bounds__(kThreads)
       nv_epilogue_barrier();
       if (ctl->flag) {
         __threadfence();
-        const size_t split_stride = static_cast<size_t>(gridDim.y) * gridDim.x * tile_elems;
+        const size_t split_stride = static_cast<size_t>(tiles_m) * tiles_n * tile_elems;
         const float* base =
-            p.partials + (static_cast<size_t>(tile_m) * gridDim.x + tile_n) * tile_elems + row_in_tile;
+            p.partials + (static_cast<size_t>(tile_m) * tiles_n + tile_n) * tile_elems + row_in_tile;
 #pragma unroll 1
-        for (int j0 = 0; j0 < valid_tok; j0 += 8) {
-          float acc[8];
+        for (int j0 = half * 8; j0 < valid_tok; j0 += 16) {
+          float v[8][8];  // [split][token]: every load of the batch is issued before the adds
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-          for (int sp = 0; sp < p.splits; ++sp) {
-            float v[8];
+          for (int sp = 0; sp < 8; ++sp) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              v[j] = (j0 + j < valid_tok) ? __ldcg(base + sp * split_stride + (j0 + j) * kRows) : 0.0f;
+              v[sp][j] = (sp < p.splits && j0 + j < valid_tok)
+                             ? __ldcg(base + sp * split_stride + (j0 + j) * kRows)
+                             : 0.0f;
             }
+          }
+          float acc[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], v[j]);
+          for (int j = 0; j < 8; ++j) {
+            acc[j] = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+              if (sp < p.splits) acc[j] = __fadd_rn(acc[j], v[sp][j]);  // fixed split order
+            }
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (j0 + j < valid_tok && row_ok) {
-              p.out[static_cast<size_t>(tok0 + j0 + j) * p.out_rows + n] =
-                  static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(acc[j], s)));
+              const size_t o = static_cast<size_t>(tok0 + j0 + j) * p.out_rows + n;
+              const float v = __fmul_rn(acc[j], s);
+              if (p.out_f32) p.out_f32[o] = v;
+              else p.out[o] = static_cast<uint16_t>(f32_to_bf16_bits(v));
             }
           }
         }
@@ -377,10 +407,22 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// fp32 -> BF16 (round to nearest even), 4 values per thread; n is a multiple of 4.
+__global__ void __launch_bounds__(256)
+    f32_to_bf16_kernel(const float4* __restrict__ in, uint2* __restrict__ out, long long n4) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = in[i];
+    out[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+}
+
 template <int BLOCK_TOK, bool GATE_UP>
 cudaError_t nv_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                       const Nvfp4Params& p) {
-  dim3 grid((p.out_rows + kRows - 1) / kRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK, p.splits);
+  dim3 grid((p.rows + BLOCK_TOK - 1) / BLOCK_TOK, (p.out_rows + kRows - 1) / kRows, p.splits);
   return launch_kernel(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid, dim3(kThreads),
                        nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, tmap_w, tmap_a, p);
 }
@@ -414,6 +456,15 @@ cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,
                    : nv_launch<128, false>(stream, tmap_w, tmap_a, p);
   }
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_f32_to_bf16(cudaStream_t stream, long long n, const float* in, uint16_t* out) {
+  const long long n4 = n / 4;
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  return launch_kernel(f32_to_bf16_kernel, dim3(static_cast<unsigned int>(blocks)), dim3(256), 0,
+                       stream, reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n4);
 }
 
 cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const uint16_t* x,

@@ -19,6 +19,15 @@ thread_local std::string g_create_error;
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// TK100_CLUSTER=0 falls back to the global-scratch split-K reduction (for A/B runs).
+bool cluster_reduce_enabled() {
+  static const bool enabled = [] {
+    const char* v = std::getenv("TK100_CLUSTER");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
+
 int env_int(const char* name) {
   const char* v = std::getenv(name);
   return v ? std::atoi(v) : 0;
@@ -343,6 +352,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.out_rows = out_rows;
   p.k = columns;
   p.splits = splits;
+  p.cluster = cluster_reduce_enabled() ? 1 : 0;
   p.act_scales = activation_scales;
   p.w_scales = weight_scales;
   p.out = output;
@@ -352,6 +362,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.partials = ctx_.partials();
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
+  p.debug = debug_flags();
   ctx_.count_launch();
   TK100_TRY(ctx_.check(launch_fp8_projection(stream, block_tok, map_w, map_a, p),
                        "launching the FP8 projection"));
@@ -370,10 +381,10 @@ Status Nvfp4MlpOp::quantize(cudaStream_t stream, int rows, int columns, const ui
                             float input_global_divisor, uint8_t* activation_codes,
                             uint8_t* activation_scales) {
   TK100_TRY(check_rows(ctx_, "NVFP4 activation quantiser", rows));
-  if (columns < 256 || columns % 256 != 0) {
+  if (columns < 64 || columns % 64 != 0) {
     return ctx_.fail(TK100_ERR_LAUNCH, "[gpu.launch] NVFP4 activation quantiser: " +
                                            std::to_string(columns) +
-                                           " columns are not admitted (multiple of 256)");
+                                           " columns are not admitted (multiple of 64)");
   }
   if (!std::isfinite(input_global_divisor) || input_global_divisor <= 0.0f) {
     return ctx_.fail(TK100_ERR_LAUNCH,
@@ -394,7 +405,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
                           const uint16_t* input, uint8_t* activation_codes,
                           uint8_t* activation_scales, float input_global_divisor,
                           const uint8_t* weight_codes, const uint8_t* weight_scales,
-                          float weight_scale_divisor, uint16_t* output) {
+                          float weight_scale_divisor, uint16_t* output, float* output_f32) {
   const char* name = gate_up ? "NVFP4 SwiGLU" : "NVFP4 down";
   TK100_TRY(check_rows(ctx_, name, rows));
   // tuisko-kernels-sm89/src/nvfp4/swiglu.rs:535-539
@@ -412,16 +423,24 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
                                            std::to_string(out_rows) +
                                            " output rows are not admitted (multiple of 128)");
   }
-  if (columns < 256 || columns % 256 != 0) {
+  // whole groups of four 16-column scale blocks (tuisko-model/src/materialize.rs:366-376)
+  if (columns < 64 || columns % 64 != 0) {
     return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name + ": " +
                                            std::to_string(columns) +
-                                           " columns are not admitted (multiple of 256)");
+                                           " columns are not admitted (multiple of 64)");
   }
   TK100_TRY(check_plane(ctx_, name, "activation codes", activation_codes, 128));
   TK100_TRY(check_plane(ctx_, name, "activation scales", activation_scales, 128));
   TK100_TRY(check_plane(ctx_, name, "weight codes", weight_codes, 128));
   TK100_TRY(check_plane(ctx_, name, "weight scales", weight_scales, 128));
-  TK100_TRY(check_plane(ctx_, name, "output", output, 2));
+  if (output_f32) {
+    if (gate_up) {
+      return ctx_.fail(TK100_ERR_LAUNCH, "[gpu.launch] NVFP4 SwiGLU has no fp32 output");
+    }
+    TK100_TRY(check_plane(ctx_, name, "fp32 output", output_f32, 16));
+  } else {
+    TK100_TRY(check_plane(ctx_, name, "output", output, 2));
+  }
   if (input) {
     TK100_TRY(quantize(stream, rows, columns, input, input_global_divisor, activation_codes,
                        activation_scales));
@@ -431,7 +450,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   const int tiles_n = out_rows / 128;
   const int tiles_m = (rows + block_tok - 1) / block_tok;
   const long long tiles = static_cast<long long>(tiles_n) * tiles_m;
-  const int kb_total = columns / 256;
+  const int kb_total = (columns + 255) / 256;
   int splits = 1;
   if (!gate_up) {
     splits = static_cast<int>(ctx_.sm_count() / tiles);
@@ -464,9 +483,11 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   // the reference passes 1/divisor to its kernel (nvfp4/swiglu.rs:541); both divisors here
   p.out_scale = 1.0f / (weight_scale_divisor * input_global_divisor);
   p.out = output;
+  p.out_f32 = output_f32;
   p.partials = ctx_.partials();
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
+  p.debug = debug_flags();
   ctx_.count_launch();
   return ctx_.check(launch_nvfp4_gemm(stream, block_tok, gate_up, map_w, map_a, p),
                     "launching the NVFP4 projection");
@@ -668,6 +689,38 @@ tk100_status tk100_nvfp4_down(tk100_ctx* ctx, tk100_stream stream, int rows,
       .launch(static_cast<cudaStream_t>(stream), false, rows, static_cast<int>(c.hidden),
               static_cast<int>(c.intermediate), input, activation_codes, activation_scales,
               input_global_divisor, weight_codes, weight_scales, weight_scale_divisor, output);
+}
+
+tk100_status tk100_nvfp4_down_partial(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                      const uint16_t* input, uint8_t* activation_codes,
+                                      uint8_t* activation_scales, float input_global_divisor,
+                                      const uint8_t* weight_codes, const uint8_t* weight_scales,
+                                      float weight_scale_divisor, float* partial_output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  const tk100_config& c = ctx->impl->config();
+  if (!partial_output) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH, "[gpu.launch] NVFP4 down: fp32 output plane is null");
+  }
+  return tk100::Nvfp4MlpOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), false, rows, static_cast<int>(c.hidden),
+              static_cast<int>(c.intermediate), input, activation_codes, activation_scales,
+              input_global_divisor, weight_codes, weight_scales, weight_scale_divisor, nullptr,
+              partial_output);
+}
+
+tk100_status tk100_f32_to_bf16(tk100_ctx* ctx, tk100_stream stream, size_t count,
+                               const float* input, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (count == 0 || count % 4 != 0 || !input || !output ||
+      (reinterpret_cast<uintptr_t>(input) & 15) || (reinterpret_cast<uintptr_t>(output) & 7)) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH,
+                           "[gpu.launch] fp32 -> BF16: count must be a positive multiple of 4 and "
+                           "the planes 16-byte aligned");
+  }
+  ctx->impl->count_launch();
+  return ctx->impl->check(tk100::launch_f32_to_bf16(static_cast<cudaStream_t>(stream),
+                                                    static_cast<long long>(count), input, output),
+                          "launching fp32 -> BF16");
 }
 
 }  // extern "C"

@@ -127,7 +127,8 @@ class Nvfp4MlpOp {
   Status launch(cudaStream_t stream, bool gate_up, int rows, int out_rows, int columns,
                 const uint16_t* input, uint8_t* activation_codes, uint8_t* activation_scales,
                 float input_global_divisor, const uint8_t* weight_codes,
-                const uint8_t* weight_scales, float weight_scale_divisor, uint16_t* output);
+                const uint8_t* weight_scales, float weight_scale_divisor, uint16_t* output,
+                float* output_f32 = nullptr);
 
  private:
   Context& ctx_;

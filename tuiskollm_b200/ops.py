@@ -226,6 +226,22 @@ class Nvfp4DownOp(_Nvfp4Op):
 
     _entry = "tk100_nvfp4_down"
 
+    def launch_partial(self, stream, batch, input, weight_codes, weight_scales,
+                       weight_scale_divisor, partial_output, *, activation_codes,
+                       activation_scales, input_global_divisor):
+        """Row-parallel shard: unrounded fp32 partial sums for a later all-reduce."""
+        c = self.ctx
+        c.check(c._lib.tk100_nvfp4_down_partial(
+            c.handle, _stream(stream), batch, _ptr(input), _ptr(activation_codes),
+            _ptr(activation_scales), input_global_divisor, _ptr(weight_codes),
+            _ptr(weight_scales), weight_scale_divisor, _ptr(partial_output)))
+
+
+def f32_to_bf16(context: Context, stream, count, input, output):
+    """fp32 -> BF16 (nearest even) of `count` values, e.g. after the tensor-parallel all-reduce."""
+    context.check(context._lib.tk100_f32_to_bf16(context.handle, _stream(stream), count,
+                                                 _ptr(input), _ptr(output)))
+
 
 STATIC_MAX_ROWS = 256
 STATIC_SCRATCH_BYTES = (8 << 20) + (16 << 10)

@@ -91,6 +91,29 @@ def nvfp4_scale_offsets(rows: int, groups: int) -> np.ndarray:
     return ((r // 128) * (groups // 4) + g // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + g % 4
 
 
+def nvfp4_swizzle(scale_matrix: np.ndarray) -> np.ndarray:
+    """[rows, groups] E4M3 scale bytes -> the 128-row x 4-group tile plane."""
+    rows, groups = scale_matrix.shape
+    plane = np.zeros(((rows + 127) // 128) * 128 * groups, dtype=np.uint8)
+    plane[nvfp4_scale_offsets(rows, groups)] = scale_matrix
+    return plane
+
+
+def nvfp4_unswizzle(plane: np.ndarray, rows: int, groups: int) -> np.ndarray:
+    return np.asarray(plane)[nvfp4_scale_offsets(rows, groups)]
+
+
+def nvfp4_reduction_shard(codes: np.ndarray, plane: np.ndarray, k: int, world: int, rank: int):
+    """Row-parallel (reduction) shard of an NVFP4 weight plane: the rank's columns of the code
+    matrix and a scale plane re-tiled for the narrower matrix."""
+    rows = codes.shape[0]
+    ks = k // world
+    assert ks % 64 == 0
+    sc = nvfp4_unswizzle(plane, rows, k // 16)[:, rank * ks // 16:(rank + 1) * ks // 16]
+    return (np.ascontiguousarray(codes[:, rank * ks // 2:(rank + 1) * ks // 2]),
+            nvfp4_swizzle(np.ascontiguousarray(sc)))
+
+
 # --------------------------------------------------------------- numpy builders
 
 def rng_for(seed: int, stream: int) -> np.random.Generator:
