@@ -582,8 +582,29 @@ def run_native(args):
     merged = torch.zeros((m, 2), dtype=torch.int32, device=dev)
     merged_host = torch.zeros((m, 2), dtype=torch.int32).pin_memory()
     op = tk.LmHeadOp(ctx, shard, offset)
+    exchange = "none"
+    peer_addresses = None
+    if world > 1:
+        exchange = "nccl all_gather + merge kernel"
+        if not args.nccl_gather:
+            try:
+                from tuiskollm_b200 import dist as tkd
+                _xbuf, _xhdl, peer_addresses = tkd.alloc_exchange(m, world, torch.device("cuda", local))
+                exchange = "peer stores over NVLink fused with the merge (one kernel)"
+            except Exception as exc:  # symmetric memory unavailable: keep the NCCL route
+                exchange += f" (peer exchange unavailable: {type(exc).__name__}: {exc})"[:300]
+    # all ranks must agree on the route
+    if world > 1:
+        flag = torch.tensor([1 if peer_addresses is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            peer_addresses = None
 
     def step():
+        if peer_addresses is not None:
+            op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, None)
+            op.exchange(None, m, world, rank, scratch, peer_addresses, merged)
+            return
         op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, pairs)
         if world > 1:
             dist.all_gather_into_tensor(gathered.view(-1), pairs.view(-1))
@@ -596,6 +617,14 @@ def run_native(args):
 
     def projection_only():
         op.launch(None, m, None, codes, scales, wc, ws, None, logits, scratch, pairs)
+
+    def local_pairs():
+        """This rank's own (max, index) pairs of the last step, for the sanity check."""
+        if peer_addresses is None:
+            return pairs.cpu().numpy()
+        op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, pairs)
+        torch.cuda.synchronize()
+        return pairs.cpu().numpy()
 
     def barrier():
         if world > 1:
@@ -657,7 +686,7 @@ def run_native(args):
     run_step()
     torch.cuda.synchronize()
     final = (merged if world > 1 else pairs).cpu().numpy()
-    mine = pairs.cpu().numpy()
+    mine = local_pairs()
     rounded = logits.to(torch.bfloat16).float()
     for t in range(m):
         first = int(torch.nonzero(rounded[t] == rounded[t].max())[0, 0]) + offset
@@ -681,7 +710,7 @@ def run_native(args):
             "data": "synthetic",
             "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={vocab} M={m}",
                        "rows": m, "vocab_shard_rows": shard, "parallelism": f"vocab-shard x{world}",
-                       "launch": mode,
+                       "launch": mode, "exchange": exchange,
                        "l2": "weight shard (%.0f MB) larger than L2, streamed once per step"
                              % (shard * HIDDEN / 1e6),
                        "tokens_per_s": m / (per_step * 1e-3), "us_per_step": per_step * 1e3},
@@ -709,8 +738,13 @@ def run_native(args):
             line["extra"] = extra_rows(torch, tk, ctx, peak)
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Graphs that hold NCCL kernels are still alive here and tearing the process group
+        # down under them can block; everything is flushed and synchronised, so leave directly.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
@@ -726,6 +760,8 @@ def main():
     ap.add_argument("--vocab", type=int, default=VOCAB,
                     help="vocabulary rows (a smaller plane makes a small profiling case)")
     ap.add_argument("--eager", action="store_true", help="launch every step from the host")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="N > 1: gather the pairs with NCCL instead of the fused peer exchange")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--case", default="", help="run one side case only: nvfp4:M or fp8:N:M")

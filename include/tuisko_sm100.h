@@ -151,7 +151,8 @@ TK100_API tk100_status tk100_fp8_projection(tk100_ctx* ctx, tk100_stream stream,
  * selection of tuisko-engine/src/sampling.rs:162-173 folded into the same kernel.
  * vocab_rows / vocab_offset describe this rank's contiguous shard of the vocabulary
  * (248320 / 0 on one GPU).  output (BF16 logits [rows, vocab_rows]) is the reference's
- * plane; logits_f32 and pairs are optional (NULL to skip).  argmax_scratch is a
+ * plane; logits_f32 and pairs are optional (NULL to skip; with pairs == NULL and
+ * argmax_scratch != NULL the packed maxima are left in argmax_scratch).  argmax_scratch is a
  * caller-owned array of `rows` 64-bit words that must be zero before the first launch;
  * every launch leaves it zero again.  pairs[i].index is a global vocabulary index. */
 TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,
@@ -164,6 +165,22 @@ TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, in
  * greedy_index (first maximum in total order; lowest global index on ties). */
 TK100_API tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, int shards,
                                 const tk100_argmax_pair* gathered, tk100_argmax_pair* output);
+
+/* Vocabulary-sharded greedy selection fused with its exchange (no reference counterpart: the
+ * reference is single-GPU and selects on the host).  Call tk100_fp8_lm_head with
+ * pairs == NULL so that the packed per-shard maxima stay in argmax_scratch, then this: one
+ * small kernel per rank unpacks them, stores the (max, index) pairs straight into every
+ * peer's exchange buffer over NVLink, raises a step-numbered flag, waits (bounded, ~2 s, then
+ * TK100_DEVICE_WAIT_TIMEOUT) for all peers' flags and merges with the first-maximum rule into
+ * `output` [rows] -- identical on every rank.  No collective library call is involved.
+ * peer_buffers: host array of `world` device addresses, entry i = rank i's exchange buffer as
+ * mapped in THIS process (peer access enabled; e.g. torch symmetric memory), each
+ * TK100_EXCHANGE_BYTES(rows, world) bytes, zero-filled once before the first call.  Every
+ * rank must make the same sequence of calls (the kernels meet by step number). */
+#define TK100_EXCHANGE_BYTES(rows, world) (2u * (world) * (rows) * 8u + 2u * (world) * 4u)
+TK100_API tk100_status tk100_argmax_exchange(tk100_ctx* ctx, tk100_stream stream, int rows, int world,
+                                   int rank, uint64_t* argmax_scratch,
+                                   const uint64_t* peer_buffers, tk100_argmax_pair* output);
 
 /* NVFP4 activation quantiser for the W4A4 tensor-core route.  The reference's NVFP4
  * operators multiply BF16 activations (A16) and have no such step; the definition is this

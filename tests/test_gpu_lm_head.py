@@ -215,3 +215,38 @@ def test_full_vocabulary_properties(tk, ctx, oracle):
     check_close(logits[:, sample], exp, 1 / 16, 0.01, "sampled logits")
     assert max_relative_error(logits[:, sample], exp, 0.25) <= 1e-2
     assert ctx.device_status() == 0
+
+
+def test_peer_exchange_single_rank_and_bounded_wait(tk, ctx, oracle):
+    """The fused exchange kernel with world = 1 (its own buffer is the only peer) must give the
+    same pairs as the finalize route; with a second 'rank' whose flag never arrives the
+    bounded wait runs out and reports TK100_DEVICE_WAIT_TIMEOUT instead of hanging."""
+    from tuiskollm_b200 import _lib, ops, synth
+
+    hidden, vocab, rows = 5120, 1024, 3
+    xb = synth.normal_bf16(15, 1, (rows, hidden))
+    wc, ws = synth.fp8_weights(15, 2, vocab, hidden)
+    x, w, s = dev(xb.view(np.int16)), dev(wc), dev(ws.view(np.int16))
+    op, p, scratch, launch = lm_head(tk, ctx, x, w, s, rows, vocab, 0, rows, hidden, f32=False)
+    launch()
+    torch.cuda.synchronize()
+    expect = pairs_of(p["pairs"], rows)
+    buf = torch.zeros((ops.exchange_bytes(rows, 1) + 7) // 8, dtype=torch.int64, device="cuda")
+    merged = sentinel_plane((rows, 2), torch.int32)
+    for _ in range(3):  # steps alternate parity; the keys are cleared every time
+        op.launch(None, rows, x, p["codes"], p["scales"], w, s, p["out"], None, scratch, None)
+        assert int(scratch.abs().sum()) != 0, "packed maxima must stay in the scratch"
+        op.exchange(None, rows, 1, 0, scratch, [buf.data_ptr()], merged)
+        torch.cuda.synchronize()
+        got = pairs_of(merged, rows)
+        assert np.array_equal(got["index"], expect["index"]) and np.array_equal(got["value"], expect["value"])
+        assert int(scratch.abs().sum()) == 0
+    assert ctx.device_status() == 0
+    # world = 2 on one GPU: rank 1 does not exist, its flag never comes
+    buf2 = torch.zeros((2, (ops.exchange_bytes(rows, 2) + 7) // 8), dtype=torch.int64, device="cuda")
+    op.launch(None, rows, x, p["codes"], p["scales"], w, s, p["out"], None, scratch, None)
+    op.exchange(None, rows, 2, 0, scratch, [buf2[0].data_ptr(), buf2[1].data_ptr()], merged)
+    assert ctx.device_status() & _lib.DEVICE_WAIT_TIMEOUT
+    assert ctx.device_status() == 0
+    with pytest.raises(tk.GpuError):
+        op.exchange(None, rows, 9, 0, scratch, [buf.data_ptr()] * 9, merged)

@@ -50,6 +50,7 @@ SIGNATURES = {
     "tk100_fp8_projection": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_lm_head": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_argmax_merge": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "tk100_argmax_exchange": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(C.c_uint64), _vp]),
     "tk100_nvfp4_quantize_activation": (_i, [_vp, _vp, _i, _i, _vp, C.c_float, _vp, _vp]),
     "tk100_nvfp4_gate_up_swiglu": (_i, [_vp, _vp, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, C.c_float,
                                         _vp]),

@@ -430,6 +430,93 @@ __global__ void argmax_merge_kernel(int rows, int shards, const ArgmaxPair* gath
   out[t] = o;
 }
 
+// Vocabulary-sharded greedy selection without a collective library call: one CTA per rank
+// unpacks its shard's (max, index) pairs, stores them straight into every peer's exchange
+// buffer over NVLink (plain peer stores), raises a per-sender flag carrying the step number,
+// waits -- bounded -- for the flags of all peers and merges with the first-maximum rule.
+// Buffer layout on every rank (same offsets everywhere): [2 parities][world][rows] pairs,
+// then [2 parities][world] 32-bit flags.  Steps alternate parity, so a fast rank's next step
+// never overwrites what a slow rank is still reading.
+__global__ void __launch_bounds__(256)
+    argmax_exchange_kernel(int rows, int world, int rank, unsigned long long* keys,
+                           ExchangePeers peers, unsigned int* step_counter, ArgmaxPair* out,
+                           uint32_t* status) {
+  __shared__ unsigned int s_step;
+  __shared__ unsigned int s_ok;
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    s_step = *step_counter + 1u;
+    *step_counter = s_step;
+    s_ok = 1u;
+  }
+  __syncthreads();
+  const unsigned int step = s_step;
+  const unsigned int parity = step & 1u;
+  const size_t pair_slots = static_cast<size_t>(world) * rows;
+  const size_t flag_base = 2 * pair_slots * sizeof(ArgmaxPair);
+
+  for (int t = threadIdx.x; t < rows; t += blockDim.x) {
+    const unsigned long long packed = keys[t];
+    keys[t] = 0ull;
+    const uint32_t key = static_cast<uint32_t>(packed >> 32);
+    ArgmaxPair mine;
+    mine.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
+    mine.index = packed == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(packed));
+    for (int pr = 0; pr < world; ++pr) {
+      ArgmaxPair* dst = reinterpret_cast<ArgmaxPair*>(peers.base[pr]) + parity * pair_slots +
+                        static_cast<size_t>(rank) * rows + t;
+      *reinterpret_cast<volatile unsigned long long*>(dst) =
+          *reinterpret_cast<const unsigned long long*>(&mine);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) {
+    unsigned int* flag = reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + flag_base) +
+                         parity * world + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+    // wait for the same step from sender `threadIdx.x` in this rank's own buffer
+    const unsigned int* mine_flag =
+        reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_base) + parity * world +
+        threadIdx.x;
+    const uint64_t start = global_timer_ns();
+    unsigned int seen = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine_flag) : "memory");
+      if (static_cast<int>(seen - step) >= 0) break;
+      if (global_timer_ns() - start > 2000000000ull) {
+        atomicOr(status, STATUS_WAIT_TIMEOUT);
+        s_ok = 0u;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const ArgmaxPair* gathered =
+      reinterpret_cast<const ArgmaxPair*>(peers.base[rank]) + parity * pair_slots;
+  for (int t = threadIdx.x; t < rows; t += blockDim.x) {
+    unsigned long long best = 0ull;
+    for (int sdr = 0; sdr < world; ++sdr) {
+      const unsigned long long raw = *reinterpret_cast<const volatile unsigned long long*>(
+          gathered + static_cast<size_t>(sdr) * rows + t);
+      const uint32_t vbits = static_cast<uint32_t>(raw);
+      const int32_t idx = static_cast<int32_t>(raw >> 32);
+      if (idx < 0) continue;
+      const unsigned long long packed =
+          (static_cast<unsigned long long>(total_order_key(vbits)) << 32) |
+          static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(idx));
+      best = packed > best ? packed : best;
+    }
+    const uint32_t key = static_cast<uint32_t>(best >> 32);
+    ArgmaxPair o;
+    o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
+    o.index = best == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(best));
+    out[t] = o;
+  }
+}
+
 template <int BLOCK_TOK>
 cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                        const Fp8ProjParams& p) {
@@ -486,6 +573,13 @@ cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long 
                                    ArgmaxPair* pairs) {
   return launch_kernel(argmax_finalize_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, rows,
                        keys, pairs);
+}
+
+cudaError_t launch_argmax_exchange(cudaStream_t stream, int rows, int world, int rank,
+                                   unsigned long long* keys, const ExchangePeers& peers,
+                                   unsigned int* step_counter, ArgmaxPair* out, uint32_t* status) {
+  return launch_kernel(argmax_exchange_kernel, dim3(1), dim3(256), 0, stream, rows, world, rank,
+                       keys, peers, step_counter, out, status);
 }
 
 cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,

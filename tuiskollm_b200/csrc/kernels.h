@@ -97,6 +97,15 @@ struct ArgmaxPair {
 // keys -> pairs, and clears the keys for the next launch.
 cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long long* keys,
                                    ArgmaxPair* pairs);
+// Peer exchange buffers of the vocabulary-sharded argmax (device addresses, one per rank;
+// entry `rank` is this rank's own buffer).
+constexpr int kMaxExchangeRanks = 8;
+struct ExchangePeers {
+  unsigned char* base[kMaxExchangeRanks];
+};
+cudaError_t launch_argmax_exchange(cudaStream_t stream, int rows, int world, int rank,
+                                   unsigned long long* keys, const ExchangePeers& peers,
+                                   unsigned int* step_counter, ArgmaxPair* out, uint32_t* status);
 // [shards, rows] pairs -> [rows] pairs with the first-maximum rule.
 cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,
                                 const ArgmaxPair* gathered, ArgmaxPair* out);

@@ -124,6 +124,8 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
             cudaMalloc(&ctx->counters_, ctx->counter_count_ * sizeof(unsigned int)) ==
                 cudaSuccess &&
             cudaMalloc(&ctx->status_, sizeof(uint32_t)) == cudaSuccess &&
+            cudaMalloc(&ctx->exchange_step_, sizeof(unsigned int)) == cudaSuccess &&
+            cudaMemset(ctx->exchange_step_, 0, sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->counters_, 0, ctx->counter_count_ * sizeof(unsigned int)) ==
                 cudaSuccess &&
             cudaMemset(ctx->status_, 0, sizeof(uint32_t)) == cudaSuccess &&
@@ -142,6 +144,7 @@ Context::~Context() {
   if (partials_) cudaFree(partials_);
   if (counters_) cudaFree(counters_);
   if (status_) cudaFree(status_);
+  if (exchange_step_) cudaFree(exchange_step_);
 }
 
 Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
@@ -303,7 +306,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   TK100_TRY(check_plane(ctx_, name_, "activation scales", activation_scales, 4));
   TK100_TRY(check_plane(ctx_, name_, "weight codes", weight_codes, 128));
   TK100_TRY(check_plane(ctx_, name_, "weight scales", weight_scales, 2));
-  if (output == nullptr && logits_f32 == nullptr && pairs == nullptr) {
+  if (output == nullptr && logits_f32 == nullptr && argmax_scratch == nullptr) {
     return ctx_.fail(TK100_ERR_LAUNCH,
                      std::string("[gpu.launch] ") + name_ + ": every output plane is null");
   }
@@ -312,6 +315,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     return ctx_.fail(TK100_ERR_LAUNCH,
                      std::string("[gpu.launch] ") + name_ + ": argmax scratch plane is null");
   }
+  if (argmax_scratch) TK100_TRY(check_plane(ctx_, name_, "argmax scratch", argmax_scratch, 8));
 
   if (input) TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
 
@@ -357,7 +361,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.w_scales = weight_scales;
   p.out = output;
   p.logits_f32 = logits_f32;
-  p.argmax_keys = pairs ? argmax_scratch : nullptr;
+  p.argmax_keys = argmax_scratch;  // pairs == null: the keys stay packed for tk100_argmax_exchange
   p.vocab_offset = vocab_offset;
   p.partials = ctx_.partials();
   p.counters = ctx_.counters();
@@ -652,6 +656,34 @@ tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, i
                                  reinterpret_cast<const tk100::ArgmaxPair*>(gathered),
                                  reinterpret_cast<tk100::ArgmaxPair*>(output)),
       "launching the argmax merge");
+}
+
+tk100_status tk100_argmax_exchange(tk100_ctx* ctx, tk100_stream stream, int rows, int world,
+                                   int rank, uint64_t* argmax_scratch,
+                                   const uint64_t* peer_buffers, tk100_argmax_pair* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (rows < 1 || rows > 4096 || world < 1 || world > tk100::kMaxExchangeRanks || rank < 0 ||
+      rank >= world || !argmax_scratch || !peer_buffers || !output) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH,
+                           "[gpu.launch] argmax exchange: bad argument (1 <= world <= 8, "
+                           "0 <= rank < world, non-null planes)");
+  }
+  tk100::ExchangePeers peers{};
+  for (int i = 0; i < world; ++i) {
+    if (peer_buffers[i] == 0 || (peer_buffers[i] & 7) != 0) {
+      return ctx->impl->fail(TK100_ERR_LAUNCH,
+                             "[gpu.launch] argmax exchange: peer buffer is null or misaligned");
+    }
+    peers.base[i] = reinterpret_cast<unsigned char*>(static_cast<uintptr_t>(peer_buffers[i]));
+  }
+  ctx->impl->count_launch();
+  return ctx->impl->check(
+      tk100::launch_argmax_exchange(static_cast<cudaStream_t>(stream), rows, world, rank,
+                                    reinterpret_cast<unsigned long long*>(argmax_scratch), peers,
+                                    ctx->impl->exchange_step(),
+                                    reinterpret_cast<tk100::ArgmaxPair*>(output),
+                                    ctx->impl->status_word()),
+      "launching the argmax exchange");
 }
 
 tk100_status tk100_nvfp4_quantize_activation(tk100_ctx* ctx, tk100_stream stream, int rows,

@@ -44,6 +44,7 @@ class Context {
   unsigned int* counters() const { return counters_; }
   size_t counter_count() const { return counter_count_; }
   uint32_t* status_word() const { return status_; }
+  unsigned int* exchange_step() const { return exchange_step_; }
   int forced_splits() const { return forced_splits_; }
   int forced_block_tok() const { return forced_block_tok_; }
   void count_launch(int n = 1) { launches_ += static_cast<uint64_t>(n); }
@@ -58,6 +59,7 @@ class Context {
   unsigned int* counters_ = nullptr;
   size_t counter_count_ = 0;
   uint32_t* status_ = nullptr;
+  unsigned int* exchange_step_ = nullptr;  // device step counter of the peer argmax exchange
   int forced_splits_ = 0;
   int forced_block_tok_ = 0;
   uint64_t launches_ = 0;

@@ -59,20 +59,55 @@ def gather_pairs(pairs: torch.Tensor, gathered: torch.Tensor, group=None) -> Non
     dist.all_gather_into_tensor(gathered.view(-1), pairs.view(-1), group=group)
 
 
+def alloc_exchange(rows: int, world: int, device, group=None):
+    """Symmetric peer-mapped exchange buffer for the fused argmax exchange: returns
+    ``(buffer, handle, addresses)`` where ``addresses[i]`` is rank i's buffer as mapped in this
+    process (torch symmetric memory over NVLink peer access).  Collective: every rank calls it."""
+    import torch.distributed._symmetric_memory as symm
+
+    from .ops import exchange_bytes
+
+    words = (exchange_bytes(rows, world) + 7) // 8
+    buf = symm.empty(words, dtype=torch.int64, device=device)
+    buf.zero_()
+    torch.cuda.synchronize()
+    grp = group if group is not None else dist.group.WORLD
+    try:
+        handle = symm.rendezvous(buf, grp)
+    except TypeError:
+        handle = symm.rendezvous(buf, grp.group_name)
+    addresses = [int(a) for a in handle.buffer_ptrs]
+    if len(addresses) != world:
+        raise RuntimeError("symmetric memory returned %d peer addresses for %d ranks" % (len(addresses), world))
+    dist.barrier(group=group)
+    return buf, handle, addresses
+
+
 class ShardedLmHead:
     """One rank's part of the vocabulary-sharded LM head with fused greedy selection."""
 
-    def __init__(self, context, vocab: int, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, context, vocab: int, rank: int = 0, world: int = 1, group=None,
+                 peer_addresses=None):
+        """``peer_addresses`` (from :func:`alloc_exchange`) selects the fused peer-store
+        exchange; without it the pairs travel through one NCCL all-gather."""
         from .ops import LmHeadOp
 
         self.shard = vocab_shard(vocab, world, rank)
         self.world = world
+        self.rank = rank
         self.group = group
+        self.peer_addresses = peer_addresses
         self.op = LmHeadOp(context, self.shard.rows, self.shard.offset)
 
     def launch(self, stream, rows, input, activation_codes, activation_scales, weight_codes,
                weight_scales, output, logits_f32, argmax_scratch, pairs, gathered, merged):
         """Projection + per-shard argmax, then (world > 1) all-gather + merge into ``merged``."""
+        if self.world > 1 and self.peer_addresses is not None:
+            self.op.launch(stream, rows, input, activation_codes, activation_scales, weight_codes,
+                           weight_scales, output, logits_f32, argmax_scratch, None)
+            self.op.exchange(stream, rows, self.world, self.rank, argmax_scratch,
+                             self.peer_addresses, merged)
+            return merged
         self.op.launch(stream, rows, input, activation_codes, activation_scales, weight_codes,
                        weight_scales, output, logits_f32, argmax_scratch, pairs)
         if self.world > 1:

@@ -180,6 +180,14 @@ class LmHeadOp:
                                          _ptr(weight_scales), _ptr(output), _ptr(logits_f32),
                                          _ptr(argmax_scratch), _ptr(pairs)))
 
+    def exchange(self, stream, rows, world, rank, argmax_scratch, peer_buffers, output_pairs):
+        """Peer-store exchange + merge of the per-shard maxima (after ``launch`` with
+        ``pairs=None``); ``peer_buffers`` lists every rank's exchange-buffer address."""
+        c = self.ctx
+        arr = (C.c_uint64 * world)(*[int(b) for b in peer_buffers])
+        c.check(c._lib.tk100_argmax_exchange(c.handle, _stream(stream), rows, world, rank,
+                                             _ptr(argmax_scratch), arr, _ptr(output_pairs)))
+
     def merge(self, stream, rows, shards, gathered_pairs, output_pairs):
         c = self.ctx
         c.check(c._lib.tk100_argmax_merge(c.handle, _stream(stream), rows, shards,
@@ -241,6 +249,11 @@ def f32_to_bf16(context: Context, stream, count, input, output):
     """fp32 -> BF16 (nearest even) of `count` values, e.g. after the tensor-parallel all-reduce."""
     context.check(context._lib.tk100_f32_to_bf16(context.handle, _stream(stream), count,
                                                  _ptr(input), _ptr(output)))
+
+
+def exchange_bytes(rows: int, world: int) -> int:
+    """Size of one rank's peer exchange buffer (TK100_EXCHANGE_BYTES)."""
+    return 2 * world * rows * 8 + 2 * world * 4
 
 
 STATIC_MAX_ROWS = 256
