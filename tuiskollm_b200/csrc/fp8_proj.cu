@@ -34,7 +34,10 @@ constexpr int kThreads = 192;    // warp 0: TMA, warp 1: UMMA + TMEM, warps 2-5:
 constexpr int kEpilogueThreads = 128;
 constexpr int kMaxSplits = 8;     // upper bound of gridDim.z (the host never asks for more)
 
-__host__ __device__ constexpr int stages_for(int block_tok) {
+// DEEP: a longer ring for launches that put at most two CTAs on an SM anyway (few tiles):
+// the same bytes in flight per SM with fewer CTAs.
+__host__ __device__ constexpr int stages_for(int block_tok, bool deep = false) {
+  if (deep) return block_tok <= 16 ? 6 : block_tok <= 32 ? 5 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
   // <= 32 tokens: three CTAs share an SM (a third slot lets the next kernel's CTAs start their
   // weight prefetch under this kernel's tail); 64: two; 128 and 256: one.
   return block_tok <= 16 ? 4 : block_tok <= 32 ? 3 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
@@ -42,8 +45,8 @@ __host__ __device__ constexpr int stages_for(int block_tok) {
 
 template <int BLOCK_TOK>
 struct Control {
-  uint64_t full[stages_for(BLOCK_TOK)];
-  uint64_t empty[stages_for(BLOCK_TOK)];
+  uint64_t full[stages_for(BLOCK_TOK, true)];
+  uint64_t empty[stages_for(BLOCK_TOK, true)];
   uint64_t tmem_full;
   unsigned long long red[BLOCK_TOK];  // per-token argmax keys of this CTA
   float a_scale[BLOCK_TOK];
@@ -51,10 +54,10 @@ struct Control {
   uint32_t is_last;
 };
 
-template <int BLOCK_TOK>
+template <int BLOCK_TOK, bool DEEP = false>
 __host__ __device__ constexpr size_t smem_bytes_for() {
   return 1024 /* alignment slack */ +
-         static_cast<size_t>(stages_for(BLOCK_TOK)) * (kWStageBytes + BLOCK_TOK * kTileKBytes) +
+         static_cast<size_t>(stages_for(BLOCK_TOK, DEEP)) * (kWStageBytes + BLOCK_TOK * kTileKBytes) +
          sizeof(Control<BLOCK_TOK>);
 }
 
@@ -67,11 +70,11 @@ __device__ __forceinline__ uint32_t total_order_key(uint32_t bits) {
   return bits ^ ((bits & 0x80000000u) ? 0xffffffffu : 0x80000000u);
 }
 
-template <int BLOCK_TOK>
-__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? 3 : (BLOCK_TOK <= 64 ? 2 : 1))
+template <int BLOCK_TOK, bool DEEP>
+__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP ? 2 : 3) : (BLOCK_TOK <= 64 ? 2 : 1))
     fp8_projection_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_a, const Fp8ProjParams p) {
-  constexpr int STAGES = stages_for(BLOCK_TOK);
+  constexpr int STAGES = stages_for(BLOCK_TOK, DEEP);
   constexpr int A_STAGE_BYTES = BLOCK_TOK * kTileKBytes;
   constexpr int STAGE_BYTES = kWStageBytes + A_STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = BLOCK_TOK < 32 ? 32 : BLOCK_TOK;
@@ -523,15 +526,25 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUt
   dim3 grid((p.out_rows + kTileRows - 1) / kTileRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK,
             p.splits);
   const unsigned int cluster_z = (p.cluster && p.splits > 1) ? static_cast<unsigned int>(p.splits) : 1u;
-  return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK>, grid, dim3(kThreads),
-                               smem_bytes_for<BLOCK_TOK>(), stream, cluster_z, tmap_w, tmap_a, p);
+  if (BLOCK_TOK <= 32 && p.deep_ring) {
+    return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, true>, grid, dim3(kThreads),
+                                 smem_bytes_for<BLOCK_TOK, true>(), stream, cluster_z, tmap_w,
+                                 tmap_a, p);
+  }
+  return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, false>, grid, dim3(kThreads),
+                               smem_bytes_for<BLOCK_TOK, false>(), stream, cluster_z, tmap_w, tmap_a,
+                               p);
 }
 
 template <int BLOCK_TOK>
 cudaError_t prepare_one() {
-  return cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK>,
+  cudaError_t e = cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem_bytes_for<BLOCK_TOK, false>()));
+  if (e != cudaSuccess || BLOCK_TOK > 32) return e;
+  return cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK, true>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(smem_bytes_for<BLOCK_TOK>()));
+                              static_cast<int>(smem_bytes_for<BLOCK_TOK, true>()));
 }
 
 }  // namespace

@@ -69,6 +69,7 @@ struct Fp8ProjParams {
   int out_rows;   // weight rows N (this shard)
   int k;          // reduction length, multiple of 128
   int splits;     // K splits (grid.z)
+  int deep_ring;  // 1: longer ring, two CTAs per SM (launches with few CTAs)
   int cluster;    // 1: the splits of a tile form a thread-block cluster and reduce over
                   // distributed shared memory; 0: fp32 partial tiles in `partials` + tickets
   const float* act_scales;      // [rows]

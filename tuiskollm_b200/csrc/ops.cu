@@ -357,6 +357,12 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.k = columns;
   p.splits = splits;
   p.cluster = cluster_reduce_enabled() ? 1 : 0;
+  {
+    const char* dr = std::getenv("TK100_DEEP_RING");
+    // unsplit launches with at most two CTAs per SM (an LM-head shard on 8 GPUs): measured
+    // 26 us instead of 32 us for a 31 040-row shard; split launches are faster with three
+    p.deep_ring = dr ? (dr[0] != '0') : (splits == 1 && tiles <= 2LL * ctx_.sm_count());
+  }
   p.act_scales = activation_scales;
   p.w_scales = weight_scales;
   p.out = output;
