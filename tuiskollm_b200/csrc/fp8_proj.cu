@@ -39,8 +39,9 @@ constexpr int kMaxSplits = 8;     // upper bound of gridDim.z (the host never as
 __host__ __device__ constexpr int stages_for(int block_tok, bool deep = false) {
   if (deep) return block_tok <= 16 ? 6 : block_tok <= 32 ? 5 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
   // <= 32 tokens: three CTAs share an SM (a third slot lets the next kernel's CTAs start their
-  // weight prefetch under this kernel's tail); 64: two; 128 and 256: one.
-  return block_tok <= 16 ? 4 : block_tok <= 32 ? 3 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
+  // weight prefetch under this kernel's tail); 64 and 128: two (one CTA's epilogue runs under
+  // the other's main loop); 256: one.
+  return block_tok <= 16 ? 4 : block_tok <= 32 ? 3 : block_tok <= 64 ? 4 : block_tok <= 128 ? 3 : 4;
 }
 
 template <int BLOCK_TOK>
@@ -71,7 +72,7 @@ __device__ __forceinline__ uint32_t total_order_key(uint32_t bits) {
 }
 
 template <int BLOCK_TOK, bool DEEP>
-__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP ? 2 : 3) : (BLOCK_TOK <= 64 ? 2 : 1))
+__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP ? 2 : 3) : (BLOCK_TOK <= 128 ? 2 : 1))
     fp8_projection_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_a, const Fp8ProjParams p) {
   constexpr int STAGES = stages_for(BLOCK_TOK, DEEP);

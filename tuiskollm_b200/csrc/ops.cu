@@ -319,7 +319,9 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
 
   if (input) TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
 
-  int block_tok = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+  // token tile: the smallest that holds all rows, 128-token tiles beyond that (two CTAs of
+  // 128 tokens share an SM; a 256-token tile would leave one CTA per SM and no overlap)
+  int block_tok = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
   if (ctx_.forced_block_tok() == 16 || ctx_.forced_block_tok() == 32 ||
       ctx_.forced_block_tok() == 64 || ctx_.forced_block_tok() == 128 ||
       ctx_.forced_block_tok() == 256) {
@@ -331,7 +333,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   const int kb_total = columns / 128;
   // Fill the SMs (two CTAs fit per SM up to 64-token tiles) by splitting K when the
   // plane has few 128-row tiles.
-  const long long slots = static_cast<long long>(ctx_.sm_count()) * (block_tok <= 64 ? 2 : 1);
+  const long long slots = static_cast<long long>(ctx_.sm_count()) * (block_tok <= 128 ? 2 : 1);
   int splits = static_cast<int>(slots / tiles);
   if (ctx_.forced_splits() > 0) splits = ctx_.forced_splits();
   if (splits > 8) splits = 8;
