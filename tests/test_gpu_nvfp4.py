@@ -198,6 +198,56 @@ def test_synthetic_mlp_small_geometry(tk, oracle, rows):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("rows", [256, 300, 512])
+def test_pair_route_small_geometry(tk, oracle, rows, monkeypatch):
+    """The CTA-pair (cta_group::2) prefill route forced on at small sizes: gate_up + SwiGLU
+    (gate CTA / up CTA exchange halves over distributed shared memory) and down, ragged token
+    counts included, against the W4A4 oracle and against the one-CTA route."""
+    from tuiskollm_b200 import synth
+
+    hidden, inter = 1024, 512
+    xb = synth.normal_bf16(14, rows, (rows, hidden))
+    gu_codes, gu_scales, gu_div = synth.nvfp4_weights(14, 1, 2 * inter, hidden)
+    dn_codes, dn_scales, dn_div = synth.nvfp4_weights(14, 2, hidden, inter)
+    a_div = float(np.float32(448.0 * 6.0 / 5.0))
+    results = {}
+    for route, min_rows in (("pair", "1"), ("single", "1000000")):
+        monkeypatch.setenv("TK100_PAIR_MIN_ROWS", min_rows)
+        monkeypatch.setenv("TK100_PAIR", "2")  # gate_up on pairs too (off by default)
+        ctx = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=512)
+        codes, scales = act_planes(tk, rows + 1, hidden)
+        mid = sentinel_plane((rows + 1, inter), torch.int16)
+        tk.Nvfp4SwiGluOp(ctx).launch(None, rows, dev(xb.view(np.int16)), dev(gu_codes), dev(gu_scales),
+                                     float(gu_div), mid, activation_codes=codes,
+                                     activation_scales=scales, input_global_divisor=a_div)
+        torch.cuda.synchronize()
+        got_mid = _u16(mid)[:rows].copy()
+        assert_inactive_untouched(mid, rows)
+        m_div = float(np.float32(448.0 * 6.0 / 8.0))
+        codes2, scales2 = act_planes(tk, rows + 1, inter)
+        out = sentinel_plane((rows + 1, hidden), torch.int16)
+        tk.Nvfp4DownOp(ctx).launch(None, rows, mid, dev(dn_codes), dev(dn_scales), float(dn_div), out,
+                                   activation_codes=codes2, activation_scales=scales2,
+                                   input_global_divisor=m_div)
+        torch.cuda.synchronize()
+        assert_inactive_untouched(out, rows)
+        assert ctx.device_status() == 0, route
+        results[route] = (got_mid, _u16(out)[:rows].copy(), host(codes)[:rows].copy(), host(scales).copy(),
+                          host(codes2)[:rows].copy(), host(scales2).copy())
+    oc, osc = oracle.nvfp4_quantize(xb, a_div)
+    dots = oracle.nvfp4_w4a4_dot(oc, osc, a_div, gu_codes, gu_scales, float(gu_div))
+    exp_mid = oracle.silu_mul(dots[:, :inter], dots[:, inter:])
+    for route in ("pair", "single"):
+        got_mid, got_out, _, _, c2, s2 = results[route]
+        assert max_relative_error(got_mid, exp_mid, 4 * float(np.abs(exp_mid).mean())) <= 1e-2, route
+        oc2, osc2 = oracle.nvfp4_quantize(got_mid, float(np.float32(448.0 * 6.0 / 8.0)))
+        assert np.array_equal(c2, oc2)
+        exp_out = oracle.nvfp4_w4a4_dot(oc2, osc2, float(np.float32(448.0 * 6.0 / 8.0)), dn_codes, dn_scales, float(dn_div))
+        assert max_relative_error(got_out, exp_out, 4 * float(np.abs(exp_out).mean())) <= 1e-2, route
+    # same products, same fp32 accumulation order per output: the two routes agree to the bit
+    assert np.array_equal(results["pair"][0], results["single"][0])
+
+
 @pytest.mark.parametrize("world,rows", [(2, 5), (8, 40), (8, 200)])
 def test_row_parallel_down_shards_sum_to_the_full_projection(tk, oracle, world, rows):
     """Tensor-parallel down projection emulated on one GPU: every rank's reduction shard

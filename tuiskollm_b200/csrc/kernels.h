@@ -135,6 +135,11 @@ cudaError_t nvfp4_prepare();
 cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,
                               const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                               const Nvfp4Params& p);
+// nvfp4_pair.cu: prefill route on CTA pairs (256-row x 256-token pair tiles).
+cudaError_t nvfp4_pair_prepare();
+cudaError_t launch_nvfp4_pair(cudaStream_t stream, bool gate_up, const CUtensorMap& tmap_w,
+                              const CUtensorMap& tmap_a, const CUtensorMap& tmap_wsf,
+                              const CUtensorMap& tmap_asf, const Nvfp4Params& p);
 cudaError_t launch_f32_to_bf16(cudaStream_t stream, long long n, const float* in, uint16_t* out);
 cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const uint16_t* x,
                                   float divisor, uint8_t* codes, uint8_t* scales);

@@ -111,6 +111,11 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
     delete ctx;
     return TK100_ERR_MODULE;
   }
+  if ((e = nvfp4_pair_prepare()) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the NVFP4 pair routes: ") + cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
   if ((e = nvfp4_prepare()) != cudaSuccess) {
     *error = std::string("[gpu.module] preparing the NVFP4 projection routes: ") +
              cudaGetErrorString(e);
@@ -170,6 +175,33 @@ Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, 
   if (r != CUDA_SUCCESS) {
     return fail(TK100_ERR_DRIVER, "[gpu.driver] cuTensorMapEncodeTiled failed with CUresult " +
                                       std::to_string(static_cast<int>(r)));
+  }
+  if (maps_.size() > 4096) maps_.clear();
+  maps_.emplace(key, map);
+  *out = map;
+  return TK100_OK;
+}
+
+Status Context::scale_map(const void* base, uint64_t chunks, CUtensorMap* out) {
+  char key[96];
+  std::snprintf(key, sizeof key, "sf:%p:%llu", base, static_cast<unsigned long long>(chunks));
+  auto it = maps_.find(key);
+  if (it != maps_.end()) {
+    *out = it->second;
+    return TK100_OK;
+  }
+  auto encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(encode_fn_);
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {128, chunks};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128u, 4u};
+  const cuuint32_t elem[2] = {1u, 1u};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims,
+                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(TK100_ERR_DRIVER, "[gpu.driver] cuTensorMapEncodeTiled (scale plane) failed with "
+                                  "CUresult " + std::to_string(static_cast<int>(r)));
   }
   if (maps_.size() > 4096) maps_.clear();
   maps_.emplace(key, map);
@@ -458,6 +490,42 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
                        activation_scales));
   }
 
+  // Prefill shapes: CTA pairs (256-row x 256-token pair tiles) halve the operand bytes per MAC.
+  {
+    const char* pe = std::getenv("TK100_PAIR");
+    const char* pm = std::getenv("TK100_PAIR_MIN_ROWS");
+    const int min_rows = pm ? std::atoi(pm) : 1024;
+    const bool allowed = !(pe && pe[0] == '0');
+    // Measured at M = 2048: down 242 -> 185 us on pairs; gate_up is no faster on pairs (its
+    // gate/up exchange costs what the lighter loads save), so it takes this route only when
+    // TK100_PAIR=2 asks for it.
+    const bool this_op = gate_up ? (pe && pe[0] == '2') : (out_rows % 256 == 0);
+    if (allowed && this_op && rows >= min_rows) {
+      const uint64_t w_rows = static_cast<uint64_t>(out_rows) * (gate_up ? 2 : 1);
+      const uint64_t chunks_per_tile = static_cast<uint64_t>(columns / 64);
+      CUtensorMap map_w, map_a, map_wsf, map_asf;
+      TK100_TRY(ctx_.tensor_map(weight_codes, w_rows, static_cast<uint64_t>(columns / 2), 128, &map_w));
+      TK100_TRY(ctx_.tensor_map(activation_codes, static_cast<uint64_t>(rows),
+                                static_cast<uint64_t>(columns / 2), 128, &map_a));
+      TK100_TRY(ctx_.scale_map(weight_scales, (w_rows / 128) * chunks_per_tile, &map_wsf));
+      TK100_TRY(ctx_.scale_map(activation_scales,
+                               static_cast<uint64_t>((rows + 127) / 128) * chunks_per_tile, &map_asf));
+      Nvfp4Params q{};
+      q.rows = rows;
+      q.out_rows = out_rows;
+      q.k = columns;
+      q.splits = 1;
+      q.up_row_offset = gate_up ? out_rows : 0;
+      q.out_scale = 1.0f / (weight_scale_divisor * input_global_divisor);
+      q.out = output;
+      q.out_f32 = output_f32;
+      q.status = ctx_.status_word();
+      q.debug = debug_flags();
+      ctx_.count_launch();
+      return ctx_.check(launch_nvfp4_pair(stream, gate_up, map_w, map_a, map_wsf, map_asf, q),
+                        "launching the NVFP4 pair projection");
+    }
+  }
   const int block_tok = rows <= 32 ? 32 : 128;
   const int tiles_n = out_rows / 128;
   const int tiles_m = (rows + block_tok - 1) / block_tok;

@@ -37,6 +37,9 @@ class Context {
   Status tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                     CUtensorMap* out);
 
+  // NVFP4 scale plane as rows of one 512-byte chunk (128 x u32), boxes of 4 chunks, unswizzled.
+  Status scale_map(const void* base, uint64_t chunks, CUtensorMap* out);
+
   const tk100_config& config() const { return config_; }
   int sm_count() const { return sm_count_; }
   float* partials() const { return partials_; }

@@ -261,6 +261,77 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---------------------------------------------------- tcgen05 with cta_group::2
+// Two CTAs of a cluster (ranks 2k, 2k+1) work as one UMMA unit: each holds 128 rows of the
+// "A" operand and half of the "B" columns in its own shared memory and 128 lanes of the
+// accumulator in its own TMEM; the even CTA issues the instructions for both.
+
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  return remote;
+}
+
+// Tiled load into this CTA's shared memory whose completion is counted on a barrier that may
+// live in the pair's other CTA (`mbar_cluster_addr` is a shared::cluster address); the data
+// itself goes to this CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t mbar_cluster_addr, int32_t c0, int32_t c1,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(mbar_cluster_addr),
+        "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair when every
+// tcgen05 operation issued so far by this thread has completed: one commit per CTA, the
+// peer's barrier addressed through its shared::cluster address.  Issued by the even CTA.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint32_t mine = smem_u32(bar);
+  const uint32_t peer = mapa_u32(mine, 1);
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   mine)
+               : "memory");
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   peer)
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_nvfp4_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X"
+      " [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb),
+        "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t tmem_dst, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc)
+               : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major operand stored as rows of 128 bytes
 // with the 128-byte swizzle (what a TMA box of 128 bytes x R rows writes): groups of
 // 8 rows are 1024 bytes apart; the tile base must be 1024-byte aligned.  Stepping
