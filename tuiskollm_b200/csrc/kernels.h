@@ -117,6 +117,7 @@ struct Nvfp4Params {
   int out_rows;        // outputs per token (weight rows of one tile family), multiple of 128
   int k;               // reduction length in elements, multiple of 256
   int splits;          // K splits (1 with gate/up fusion)
+  int cluster;         // 1: the splits of a tile reduce over distributed shared memory
   int up_row_offset;   // gate/up fusion: first weight row of the up half (= out_rows)
   const uint8_t* w_scales;  // swizzled E4M3 weight scales
   const uint8_t* a_scales;  // swizzled E4M3 activation scales

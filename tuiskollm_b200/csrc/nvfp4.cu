@@ -38,7 +38,8 @@ constexpr int kSfSlots = 8;          // TMEM scale slots in rotation
 constexpr int kSfSlotCols = 16;      // columns per slot: SFA0 [0,4) SFA1 [4,8) SFB [8,12)
 
 __host__ __device__ constexpr int nv_stages(int block_tok, bool gate_up) {
-  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 8 : 6);
+  // plain projection at <= 32 tokens: 4 stages (98 KB) so that two CTAs share an SM
+  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 4 : 6);
 }
 
 __host__ __device__ constexpr int nv_stage_bytes(int block_tok, bool gate_up) {
@@ -75,7 +76,7 @@ __device__ __forceinline__ float silu_stable(float v) {
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_a, const Nvfp4Params p) {
   constexpr int STAGES = nv_stages(BLOCK_TOK, GATE_UP);
@@ -109,7 +110,16 @@ __global__ void __launch_bounds__(kThreads)
 
   if (threadIdx.x == 0) ctl->flag = *reinterpret_cast<volatile uint32_t*>(p.status);
   __syncthreads();
-  if (ctl->flag & STATUS_WAIT_TIMEOUT) return;
+  const bool clustered = !GATE_UP && p.cluster != 0 && p.splits > 1;
+  if (ctl->flag & STATUS_WAIT_TIMEOUT) {
+    if (clustered) {  // still owed to the cluster: both barriers of the reduction
+      cluster_arrive();
+      cluster_wait();
+      cluster_arrive();
+      cluster_wait();
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -282,6 +292,21 @@ __global__ void __launch_bounds__(kThreads)
           }
         }
       }
+    } else if (clustered) {
+      // split-K inside a thread-block cluster: park the partial tile in this CTA's shared
+      // memory ([token][row] fp32 over the ring, free once tmem_full has fired)
+      float* mine = reinterpret_cast<float*>(smem) + row_in_tile;
+#pragma unroll 1
+      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+        if (c0 >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok) mine[(c0 + j) * kRows] = __uint_as_float(r[j]);
+        }
+      }
     } else {
       // split-K: fixed-order sum of fp32 partial tiles by the last CTA to arrive
       const size_t tile_elems = static_cast<size_t>(BLOCK_TOK) * kRows;
@@ -346,6 +371,44 @@ __global__ void __launch_bounds__(kThreads)
         }
       }
     }
+  }
+
+  if (clustered) {
+    // CTA `rank` of the cluster finishes tokens rank, rank + S, ...: partials come from the
+    // peers' shared memory and are added in split order (fixed => bit-reproducible).
+    cluster_arrive();
+    cluster_wait();
+    if (warp >= 2 && !(p.debug & DBG_NO_EPILOGUE)) {
+      const int quad = warp & 3;
+      const int half = (warp - 2) >> 2;
+      const int row_in_tile = quad * 32 + lane;
+      const int n = tile_n * kRows + row_in_tile;
+      const bool row_ok = n < p.out_rows;
+      const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
+      const uint32_t rank = cluster_cta_rank();
+      const uint32_t my_addr = smem_u32(reinterpret_cast<float*>(smem) + row_in_tile);
+#pragma unroll 1
+      for (int j = static_cast<int>(rank) + half * p.splits; j < valid_tok; j += 2 * p.splits) {
+        float v[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          v[sp] = sp < p.splits ? ld_dsmem_f32(my_addr + j * kRows * 4, static_cast<uint32_t>(sp)) : 0.0f;
+        }
+        float acc = 0.0f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          if (sp < p.splits) acc = __fadd_rn(acc, v[sp]);
+        }
+        if (row_ok) {
+          const size_t o = static_cast<size_t>(tok0 + j) * p.out_rows + n;
+          const float val = __fmul_rn(acc, p.out_scale);
+          if (p.out_f32) p.out_f32[o] = val;
+          else p.out[o] = static_cast<uint16_t>(f32_to_bf16_bits(val));
+        }
+      }
+    }
+    cluster_arrive();  // no CTA's shared memory may go away while a peer still reads it
+    cluster_wait();
   }
 
   tc_fence_before_sync();
@@ -423,8 +486,11 @@ template <int BLOCK_TOK, bool GATE_UP>
 cudaError_t nv_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                       const Nvfp4Params& p) {
   dim3 grid((p.rows + BLOCK_TOK - 1) / BLOCK_TOK, (p.out_rows + kRows - 1) / kRows, p.splits);
-  return launch_kernel(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid, dim3(kThreads),
-                       nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, tmap_w, tmap_a, p);
+  const unsigned int cluster_z =
+      (!GATE_UP && p.cluster && p.splits > 1) ? static_cast<unsigned int>(p.splits) : 1u;
+  return launch_kernel_cluster(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid, dim3(kThreads),
+                               nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, cluster_z, tmap_w, tmap_a,
+                               p);
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
