@@ -380,8 +380,9 @@ def nvfp4_rows(torch, tk, ctx, row_counts=(2048, 256, 32, 8, 1)):
 
 
 def layer_slice_rows(torch, tk, ctx):
-    """Configuration 5, one GPU: residual add + RMSNorm + E4M3 quantise -> FP8 QKV (N = 8192)
-    -> FP8 GDN-input (N = 12288) -> NVFP4 gate_up + SwiGLU -> NVFP4 down, as one CUDA graph."""
+    """Configuration 5, one GPU: residual add + RMSNorm + E4M3 and NVFP4 quantise (one kernel)
+    -> FP8 QKV (N = 8192) -> FP8 GDN-input (N = 12288) -> NVFP4 gate_up + SwiGLU -> NVFP4
+    re-quantise -> NVFP4 down, as one CUDA graph of six kernels."""
     from tuiskollm_b200 import ops, synth
 
     out = []
@@ -406,10 +407,11 @@ def layer_slice_rows(torch, tk, ctx):
         gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
 
         def slice_():
-            norm.launch_quantize(None, m, x, br, nw, res, nrm, codes, scales)
+            norm.launch_quantize_nvfp4(None, m, x, br, nw, res, nrm, codes, scales, pl.a_div,
+                                       pl.a_codes, pl.a_scales)
             qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
             gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
-            gu.launch(None, m, nrm, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+            gu.launch(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
                       activation_codes=pl.a_codes, activation_scales=pl.a_scales,
                       input_global_divisor=pl.a_div)
             dn.launch(None, m, pl.mid, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
@@ -424,7 +426,7 @@ def layer_slice_rows(torch, tk, ctx):
         reps = 50
         ms = time_region(torch, graph.replay, reps) / reps
         flops = 2.0 * m * HIDDEN * (synth.QKV_ROWS + synth.GDN_ROWS + 3 * synth.INTERMEDIATE)
-        out.append({"op": "layer_slice", "M": m, "us": ms * 1e3, "kernels": 7,
+        out.append({"op": "layer_slice", "M": m, "us": ms * 1e3, "kernels": 6,
                     "weight_stream_GBs": weight_bytes / ms / 1e6, "TFLOPs": flops / ms / 1e9,
                     "floor_us_at_measured_hbm": weight_bytes / measured_peak()[0] / 1e3})
         del pl
@@ -469,10 +471,11 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local):
     a_div, m_div = 448.0 * 6.0 / 6.0, 448.0 * 6.0 / 8.0
 
     def slice_():
-        norm.launch_quantize(None, m, x, br, nw, res, nrm, codes, scales)
+        norm.launch_quantize_nvfp4(None, m, x, br, nw, res, nrm, codes, scales, a_div, a_codes,
+                                   a_scales)
         qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
         gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
-        gu.launch(None, m, nrm, gu_codes, gu_scales, gu_div, mid, activation_codes=a_codes,
+        gu.launch(None, m, None, gu_codes, gu_scales, gu_div, mid, activation_codes=a_codes,
                   activation_scales=a_scales, input_global_divisor=a_div)
         dn.launch_partial(None, m, mid, dn_codes, dn_scales, dn_div, partial,
                           activation_codes=m_codes, activation_scales=m_scales,

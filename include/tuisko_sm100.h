@@ -118,6 +118,17 @@ TK100_API tk100_status tk100_residual_rms_norm_quantize(tk100_ctx* ctx, tk100_st
                                               uint8_t* activation_codes,
                                               float* activation_scales);
 
+/* The fused producer with both quantised forms of the normalised row: E4M3 codes + scale for
+ * the FP8 projections (optional: activation_codes / activation_scales may both be NULL) and
+ * NVFP4 codes + block scales for the W4A4 MLP (definition at tk100_nvfp4_quantize_activation;
+ * no reference counterpart), all in the one kernel that reads x (+ branch) once.  The NVFP4
+ * planes then go to tk100_nvfp4_gate_up_swiglu with input == NULL.  hidden % 64 == 0. */
+TK100_API tk100_status tk100_residual_rms_norm_quantize_nvfp4(
+    tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* residual_input,
+    const uint16_t* branch, const uint16_t* weight, uint16_t* residual_output,
+    uint16_t* normalized_output, uint8_t* activation_codes, float* activation_scales,
+    float input_global_divisor, uint8_t* nvfp4_codes, uint8_t* nvfp4_scales);
+
 /* quantize_activation_e4m3 alone (tuisko-kernels-sm120/src/fp8/projection.rs:71-88),
  * for rows of `columns` BF16 values (columns % 8 == 0). */
 TK100_API tk100_status tk100_quantize_activation_e4m3(tk100_ctx* ctx, tk100_stream stream, int rows,

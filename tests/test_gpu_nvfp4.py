@@ -70,6 +70,45 @@ def test_activation_quantiser_is_bit_exact(tk, ctx, oracle, rows, k):
     check_quantiser(oracle, xb, divisor, codes, scales, rows)
 
 
+@pytest.mark.parametrize("rows", [1, 7, 130])
+def test_fused_producer_emits_nvfp4_and_e4m3(tk, ctx, oracle, rows):
+    """Residual add + RMSNorm + E4M3 quantise + NVFP4 quantise in ONE kernel: every output is
+    the oracle's function of the normalised row the kernel itself wrote, bit for bit, and the
+    NVFP4 planes feed the gate_up projection directly (input == NULL)."""
+    from tuiskollm_b200 import synth
+
+    xb = synth.normal_bf16(33, rows, (rows, HIDDEN))
+    bb = synth.normal_bf16(33, rows + 1, (rows, HIDDEN))
+    nb = synth.normal_bf16(33, 3, (HIDDEN,), std=0.1)
+    divisor = float(np.float32(448.0 * 6.0 / 6.0))
+    res = sentinel_plane((rows + 1, HIDDEN), torch.int16)
+    norm = sentinel_plane((rows + 1, HIDDEN), torch.int16)
+    e_codes = sentinel_plane((rows + 1, HIDDEN), torch.uint8)
+    e_scales = sentinel_plane((rows + 1,), torch.float32)
+    codes, scales = act_planes(tk, rows + 1, HIDDEN)
+    tk.ResidualNormOp(ctx).launch_quantize_nvfp4(None, rows, dev(xb.view(np.int16)), dev(bb.view(np.int16)),
+                                                 dev(nb.view(np.int16)), res, norm, e_codes, e_scales,
+                                                 divisor, codes, scales)
+    torch.cuda.synchronize()
+    res_o, _ = oracle.residual_rms_norm(xb, bb, nb, 1e-6)
+    assert np.array_equal(_u16(res)[:rows], res_o)
+    nd = _u16(norm)[:rows]
+    oc, os_ = oracle.quantize_e4m3(nd)
+    assert np.array_equal(host(e_codes)[:rows], oc)
+    assert np.array_equal(host(e_scales)[:rows].view(np.uint32), os_.view(np.uint32))
+    check_quantiser(oracle, nd, divisor, codes, scales, rows)
+    for pl in (res, norm, e_codes, e_scales):
+        assert_inactive_untouched(pl, rows)
+    # E4M3 side optional
+    codes2, scales2 = act_planes(tk, rows + 1, HIDDEN)
+    tk.ResidualNormOp(ctx).launch_quantize_nvfp4(None, rows, dev(xb.view(np.int16)), None,
+                                                 dev(nb.view(np.int16)), None, norm, None, None,
+                                                 divisor, codes2, scales2)
+    torch.cuda.synchronize()
+    check_quantiser(oracle, _u16(norm)[:rows], divisor, codes2, scales2, rows)
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_reference_fixture_gate_up_swiglu(tk, ctx, oracle, batch):
     """qual/src/nvfp4_swiglu.rs: structured fixture at full size, exact batches 1..8; tolerance

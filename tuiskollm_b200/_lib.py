@@ -44,6 +44,8 @@ SIGNATURES = {
     "tk100_rms_norm": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "tk100_residual_rms_norm": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "tk100_residual_rms_norm_quantize": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tk100_residual_rms_norm_quantize_nvfp4": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                    C.c_float, _vp, _vp]),
     "tk100_quantize_activation_e4m3": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "tk100_fp8_qkv": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_gdn_input": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -61,7 +61,9 @@ bool norm_geometry(int hidden, int* threads, int* chunks);
 cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, const uint16_t* x,
                                  const uint16_t* branch, const uint16_t* weight,
                                  uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
-                                 float* scales, float eps, uint32_t* status);
+                                 float* scales, float eps, uint32_t* status,
+                                 uint8_t* nvfp4_codes = nullptr, uint8_t* nvfp4_scales = nullptr,
+                                 float nvfp4_divisor = 0.0f);
 
 // ------------------------------------------------------------------ fp8_proj.cu
 struct Fp8ProjParams {

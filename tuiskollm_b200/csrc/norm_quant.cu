@@ -31,12 +31,20 @@ struct alignas(16) Chunk {
   uint32_t w[4];
 };
 
+// Optional NVFP4 side output of the fused producer (all null/zero when unused).
+struct Nvfp4Out {
+  uint8_t* codes;   // [rows, hidden/2]
+  uint8_t* scales;  // 128-row x 4-group tiles, row = token
+  float divisor;    // input global divisor
+};
+
 template <bool HAS_BRANCH, bool DO_NORM, bool DO_QUANT, int CHUNKS>
 __global__ void __launch_bounds__(1024)
     resnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ branch,
                          const uint16_t* __restrict__ weight, uint16_t* __restrict__ residual_out,
                          uint16_t* __restrict__ normalized_out, uint8_t* __restrict__ codes,
-                         float* __restrict__ scales, int hidden, float eps, uint32_t* status) {
+                         float* __restrict__ scales, int hidden, float eps, uint32_t* status,
+                         const Nvfp4Out nv) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();  // x / branch may be the predecessor's output
@@ -104,6 +112,44 @@ __global__ void __launch_bounds__(1024)
     }
   }
 
+  if (nv.codes != nullptr) {
+    // NVFP4 codes of the (rounded) row for the W4A4 MLP: a 16-column block is the two 8-value
+    // chunks of an even/odd thread pair; same arithmetic as nvfp4_quantize_kernel.
+    const int groups = hidden >> 4;
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;  // chunk index; block g = c / 2
+      float bmax = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bmax = fmaxf(bmax, fabsf(v[i][j]));
+      bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+      if (c < chunks_per_row) {
+        const float raw = __fdiv_rn(__fmul_rn(bmax, nv.divisor), 6.0f);
+        const uint32_t sc = f32x2_to_e4m3x2(raw, 0.0f) & 0xffu;
+        const float sd = e4m3_to_f32(sc);
+        uint32_t packed = 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t byte;
+          if (sd == 0.0f) {
+            byte = (signbit(v[i][2 * j]) ? 0x08u : 0u) | (signbit(v[i][2 * j + 1]) ? 0x80u : 0u);
+          } else {
+            byte = f32x2_to_e2m1x2(__fdiv_rn(__fmul_rn(v[i][2 * j], nv.divisor), sd),
+                                   __fdiv_rn(__fmul_rn(v[i][2 * j + 1], nv.divisor), sd)) & 0xffu;
+          }
+          packed |= byte << (8 * j);
+        }
+        *reinterpret_cast<uint32_t*>(nv.codes + static_cast<size_t>(row) * (hidden >> 1) + c * 4) = packed;
+        if ((c & 1) == 0) {
+          const int g = c >> 1;
+          const size_t off = (static_cast<size_t>(row >> 7) * (groups >> 2) + (g >> 2)) * 512 +
+                             static_cast<size_t>(row & 31) * 16 + ((row & 127) >> 5) * 4 + (g & 3);
+          nv.scales[off] = static_cast<uint8_t>(sc);
+        }
+      }
+    }
+  }
+
   if (DO_QUANT) {
 #pragma unroll
     for (int i = 0; i < CHUNKS; ++i) {
@@ -136,11 +182,11 @@ template <bool HAS_BRANCH, bool DO_NORM, bool DO_QUANT>
 cudaError_t launch_chunks(cudaStream_t stream, int rows, int hidden, int threads, int chunks,
                           const uint16_t* x, const uint16_t* branch, const uint16_t* weight,
                           uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
-                          float* scales, float eps, uint32_t* status) {
+                          float* scales, float eps, uint32_t* status, const Nvfp4Out& nv) {
 #define TK100_LAUNCH(C)                                                                       \
   launch_kernel(resnorm_quant_kernel<HAS_BRANCH, DO_NORM, DO_QUANT, C>, dim3(rows), dim3(threads), \
                 0, stream, x, branch, weight, residual_out, normalized_out, codes, scales, hidden, \
-                eps, status)
+                eps, status, nv)
   switch (chunks) {
     case 1: return TK100_LAUNCH(1);
     case 2: return TK100_LAUNCH(2);
@@ -192,7 +238,9 @@ bool norm_geometry(int hidden, int* threads, int* chunks) {
 cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, const uint16_t* x,
                                  const uint16_t* branch, const uint16_t* weight,
                                  uint16_t* residual_out, uint16_t* normalized_out, uint8_t* codes,
-                                 float* scales, float eps, uint32_t* status) {
+                                 float* scales, float eps, uint32_t* status, uint8_t* nvfp4_codes,
+                                 uint8_t* nvfp4_scales, float nvfp4_divisor) {
+  const Nvfp4Out nv{nvfp4_codes, nvfp4_scales, nvfp4_divisor};
   int threads = 0, chunks = 0;
   if (!norm_geometry(hidden, &threads, &chunks)) return cudaErrorInvalidValue;
   const bool has_branch = branch != nullptr;
@@ -201,7 +249,7 @@ cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, cons
 #define TK100_CASE(B, N, Q)                                                                      \
   if (has_branch == B && do_norm == N && do_quant == Q)                                          \
   return launch_chunks<B, N, Q>(stream, rows, hidden, threads, chunks, x, branch, weight,        \
-                                residual_out, normalized_out, codes, scales, eps, status)
+                                residual_out, normalized_out, codes, scales, eps, status, nv)
   TK100_CASE(true, true, true);
   TK100_CASE(true, true, false);
   TK100_CASE(false, true, true);

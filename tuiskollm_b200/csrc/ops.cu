@@ -273,8 +273,21 @@ Status ResidualNormOp::launch_quantize(cudaStream_t stream, int batch,
                                        const uint16_t* residual_input, const uint16_t* branch,
                                        const uint16_t* weight, uint16_t* residual_output,
                                        uint16_t* normalized_output, uint8_t* activation_codes,
-                                       float* activation_scales) {
+                                       float* activation_scales, float nvfp4_divisor,
+                                       uint8_t* nvfp4_codes, uint8_t* nvfp4_scales) {
   TK100_TRY(check_rows(ctx_, "residual norm", batch));
+  if (nvfp4_codes || nvfp4_scales) {
+    if (ctx_.config().hidden % 64 != 0) {
+      return ctx_.fail(TK100_ERR_LAUNCH,
+                       "[gpu.launch] residual norm: NVFP4 output needs hidden % 64 == 0");
+    }
+    if (!std::isfinite(nvfp4_divisor) || nvfp4_divisor <= 0.0f) {
+      return ctx_.fail(TK100_ERR_LAUNCH,
+                       "[gpu.launch] NVFP4 input scale divisor must be finite and positive");
+    }
+    TK100_TRY(check_plane(ctx_, "residual norm", "NVFP4 activation codes", nvfp4_codes, 128));
+    TK100_TRY(check_plane(ctx_, "residual norm", "NVFP4 activation scales", nvfp4_scales, 128));
+  }
   TK100_TRY(check_plane(ctx_, "residual norm", "residual input", residual_input, 16));
   TK100_TRY(check_plane(ctx_, "residual norm", "weight", weight, 16));
   TK100_TRY(check_plane(ctx_, "residual norm", "normalized output", normalized_output, 16));
@@ -291,7 +304,7 @@ Status ResidualNormOp::launch_quantize(cudaStream_t stream, int batch,
       launch_resnorm_quant(stream, batch, static_cast<int>(ctx_.config().hidden), residual_input,
                            branch, weight, branch ? residual_output : nullptr, normalized_output,
                            activation_codes, activation_scales, ctx_.config().rms_norm_epsilon,
-                           ctx_.status_word()),
+                           ctx_.status_word(), nvfp4_codes, nvfp4_scales, nvfp4_divisor),
       "launching residual RMSNorm");
 }
 
@@ -667,6 +680,22 @@ tk100_status tk100_residual_rms_norm_quantize(tk100_ctx* ctx, tk100_stream strea
   return tk100::ResidualNormOp(*ctx->impl)
       .launch_quantize(static_cast<cudaStream_t>(stream), rows, residual_input, branch, weight,
                        residual_output, normalized_output, activation_codes, activation_scales);
+}
+
+tk100_status tk100_residual_rms_norm_quantize_nvfp4(
+    tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* residual_input,
+    const uint16_t* branch, const uint16_t* weight, uint16_t* residual_output,
+    uint16_t* normalized_output, uint8_t* activation_codes, float* activation_scales,
+    float input_global_divisor, uint8_t* nvfp4_codes, uint8_t* nvfp4_scales) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (!nvfp4_codes || !nvfp4_scales) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH,
+                           "[gpu.launch] residual norm: NVFP4 code/scale plane is null");
+  }
+  return tk100::ResidualNormOp(*ctx->impl)
+      .launch_quantize(static_cast<cudaStream_t>(stream), rows, residual_input, branch, weight,
+                       residual_output, normalized_output, activation_codes, activation_scales,
+                       input_global_divisor, nvfp4_codes, nvfp4_scales);
 }
 
 tk100_status tk100_quantize_activation_e4m3(tk100_ctx* ctx, tk100_stream stream, int rows,

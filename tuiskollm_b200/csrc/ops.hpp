@@ -84,7 +84,9 @@ class ResidualNormOp {
   Status launch_quantize(cudaStream_t stream, int batch, const uint16_t* residual_input,
                          const uint16_t* branch, const uint16_t* weight,
                          uint16_t* residual_output, uint16_t* normalized_output,
-                         uint8_t* activation_codes, float* activation_scales);
+                         uint8_t* activation_codes, float* activation_scales,
+                         float nvfp4_divisor = 0.0f, uint8_t* nvfp4_codes = nullptr,
+                         uint8_t* nvfp4_scales = nullptr);
 
  private:
   Context& ctx_;

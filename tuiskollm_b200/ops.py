@@ -116,6 +116,17 @@ class ResidualNormOp:
             _ptr(activation_scales)))
 
 
+    def launch_quantize_nvfp4(self, stream, batch, residual_input, branch, weight, residual_output,
+                              normalized_output, activation_codes, activation_scales,
+                              input_global_divisor, nvfp4_codes, nvfp4_scales):
+        """Fused producer with both quantised forms: E4M3 (optional) and NVFP4, one kernel."""
+        c = self.ctx
+        c.check(c._lib.tk100_residual_rms_norm_quantize_nvfp4(
+            c.handle, _stream(stream), batch, _ptr(residual_input), _ptr(branch), _ptr(weight),
+            _ptr(residual_output), _ptr(normalized_output), _ptr(activation_codes),
+            _ptr(activation_scales), input_global_divisor, _ptr(nvfp4_codes), _ptr(nvfp4_scales)))
+
+
 class Fp8ProjectionOp:
     """Generic FP8 projection (any reduction length that is a multiple of 128)."""
 
