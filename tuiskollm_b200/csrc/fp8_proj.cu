@@ -529,11 +529,11 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUt
   const unsigned int cluster_z = (p.cluster && p.splits > 1) ? static_cast<unsigned int>(p.splits) : 1u;
   if (BLOCK_TOK <= 32 && p.deep_ring) {
     return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, true>, grid, dim3(kThreads),
-                                 smem_bytes_for<BLOCK_TOK, true>(), stream, cluster_z, tmap_w,
+                                 smem_bytes_for<BLOCK_TOK, true>(), stream, dim3(1, 1, cluster_z), tmap_w,
                                  tmap_a, p);
   }
   return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, false>, grid, dim3(kThreads),
-                               smem_bytes_for<BLOCK_TOK, false>(), stream, cluster_z, tmap_w, tmap_a,
+                               smem_bytes_for<BLOCK_TOK, false>(), stream, dim3(1, 1, cluster_z), tmap_w, tmap_a,
                                p);
 }
 

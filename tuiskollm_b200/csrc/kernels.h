@@ -18,10 +18,10 @@ bool pdl_enabled();
 enum : uint32_t { DBG_NO_EPILOGUE = 1, DBG_NO_MMA = 2, DBG_NO_ACT = 4 };
 uint32_t debug_flags();
 
-// cluster_z > 1 launches thread-block clusters of (1, 1, cluster_z) CTAs.
+// A cluster shape other than (1, 1, 1) launches thread-block clusters of that shape.
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                  cudaStream_t stream, unsigned int cluster_z, Args&&... args) {
+                                  cudaStream_t stream, dim3 cluster, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -34,11 +34,11 @@ cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
-  if (cluster_z > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = 1;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = cluster_z;
+    attr[n].val.clusterDim.x = cluster.x;
+    attr[n].val.clusterDim.y = cluster.y;
+    attr[n].val.clusterDim.z = cluster.z;
     ++n;
   }
   cfg.attrs = attr;
@@ -49,7 +49,8 @@ cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                           cudaStream_t stream, Args&&... args) {
-  return launch_kernel_cluster(kernel, grid, block, smem, stream, 1u, std::forward<Args>(args)...);
+  return launch_kernel_cluster(kernel, grid, block, smem, stream, dim3(1, 1, 1),
+                               std::forward<Args>(args)...);
 }
 
 // ---------------------------------------------------------------- norm_quant.cu
@@ -120,6 +121,8 @@ struct Nvfp4Params {
   int k;               // reduction length in elements, multiple of 256
   int splits;          // K splits (1 with gate/up fusion)
   int cluster;         // 1: the splits of a tile reduce over distributed shared memory
+  int pair_swiglu;     // 1: plain tiles in clusters of two (gate tile, up tile): the up CTA hands
+                       // its accumulator to the gate CTA, which writes bf16(silu(gate) * up)
   int up_row_offset;   // gate/up fusion: first weight row of the up half (= out_rows)
   const uint8_t* w_scales;  // swizzled E4M3 weight scales
   const uint8_t* a_scales;  // swizzled E4M3 activation scales

@@ -101,6 +101,11 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
   // token tiles vary fastest so that the CTAs sharing a weight tile run together (L2 reuse)
   const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
   const int tiles_m = gridDim.x, tiles_n = gridDim.y;
+  // gate/up as a cluster of two plain tiles: CTA 0 = gate tile `pair`, CTA 1 = up tile `pair`
+  const bool pair_swiglu = !GATE_UP && p.pair_swiglu != 0;
+  const uint32_t pair_rank = pair_swiglu ? cluster_cta_rank() : 0u;
+  const int out_tile = pair_swiglu ? tile_n >> 1 : tile_n;
+  const int w_tile = pair_swiglu ? (pair_rank == 0 ? out_tile : p.up_row_offset / kRows + out_tile) : tile_n;
   // K is a multiple of 64 (one UMMA K); the last 256-element stage may hold 1..4 such steps.
   const int kb_total = (p.k + kStageK - 1) / kStageK;
   const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / p.splits);
@@ -112,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
   __syncthreads();
   const bool clustered = !GATE_UP && p.cluster != 0 && p.splits > 1;
   if (ctl->flag & STATUS_WAIT_TIMEOUT) {
-    if (clustered) {  // still owed to the cluster: both barriers of the reduction
+    if (clustered || (!GATE_UP && p.pair_swiglu != 0)) {  // still owed to the cluster: both barriers of the reduction
       cluster_arrive();
       cluster_wait();
       cluster_arrive();
@@ -149,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
       // Scale tiles: chunk (tile, kb) of a plane with G = K/16 groups per row starts at
       // ((tile * G/4) + 4 * kb) * 512 bytes and is 2 KB long (4 consecutive 512-byte chunks).
       const size_t chunks_per_tile = static_cast<size_t>(p.k / 64);
-      const uint8_t* sfa0 = p.w_scales + (static_cast<size_t>(tile_n) * chunks_per_tile) * kSfChunk;
+      const uint8_t* sfa0 = p.w_scales + (static_cast<size_t>(w_tile) * chunks_per_tile) * kSfChunk;
       const uint8_t* sfa1 =
           p.w_scales + (static_cast<size_t>(p.up_row_offset / kRows + tile_n) * chunks_per_tile) * kSfChunk;
       const uint8_t* sfb = p.a_scales + (static_cast<size_t>(tok0 / kRows) * chunks_per_tile) * kSfChunk;
@@ -166,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
                               (p.debug & DBG_NO_ACT)
                                   ? NW * (kWTile + sf_bytes)
                                   : code_bytes + (NW + 1) * sf_bytes);
-        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, tile_n * kRows, pol_w);
+        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, w_tile * kRows, pol_w);
         bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, sf_bytes, &ctl->full[s], pol_w);
         if (GATE_UP) {
           tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
     const int quad = warp & 3;         // TMEM lane quadrant of this warp
     const int half = (warp - 2) >> 2;  // which of the two warps of the quadrant
     const int row_in_tile = quad * 32 + lane;
-    const int n = tile_n * kRows + row_in_tile;
+    const int n = out_tile * kRows + row_in_tile;
     const bool row_ok = n < p.out_rows;
     const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
     const float s = p.out_scale;
@@ -273,6 +278,19 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
             p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
                 static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up)));
           }
+        }
+      }
+    } else if (pair_swiglu) {
+      if (pair_rank == 1) {  // up tile: park the accumulator for the gate CTA
+        float* mine = reinterpret_cast<float*>(smem) + row_in_tile;
+#pragma unroll 1
+        for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+          if (c0 >= valid_tok) break;
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(c0 + j) * kRows] = __uint_as_float(r[j]);
         }
       }
     } else if (p.splits == 1) {
@@ -371,6 +389,42 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
         }
       }
     }
+  }
+
+  if (pair_swiglu) {
+    cluster_arrive();
+    cluster_wait();
+    if (warp >= 2 && pair_rank == 0 && !(p.debug & DBG_NO_EPILOGUE)) {
+      const int quad = warp & 3;
+      const int half = (warp - 2) >> 2;
+      const int row_in_tile = quad * 32 + lane;
+      const int n = out_tile * kRows + row_in_tile;
+      const bool row_ok = n < p.out_rows;
+      const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t up_addr = smem_u32(reinterpret_cast<float*>(smem) + row_in_tile);
+#pragma unroll 1
+      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+        if (c0 >= valid_tok) break;
+        uint32_t g[16];
+        tmem_ld16(taddr + c0, g);
+        float u[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) u[j] = ld_dsmem_f32(up_addr + (c0 + j) * kRows * 4, 1u);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j < valid_tok && row_ok) {
+            const float gate = __fmul_rn(__uint_as_float(g[j]), p.out_scale);
+            const float up = __fmul_rn(u[j], p.out_scale);
+            p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
+                static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up)));
+          }
+        }
+      }
+    }
+    cluster_arrive();  // the up CTA keeps its shared memory until the gate CTA has read it
+    cluster_wait();
   }
 
   if (clustered) {
@@ -485,12 +539,14 @@ __global__ void __launch_bounds__(256)
 template <int BLOCK_TOK, bool GATE_UP>
 cudaError_t nv_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                       const Nvfp4Params& p) {
-  dim3 grid((p.rows + BLOCK_TOK - 1) / BLOCK_TOK, (p.out_rows + kRows - 1) / kRows, p.splits);
-  const unsigned int cluster_z =
-      (!GATE_UP && p.cluster && p.splits > 1) ? static_cast<unsigned int>(p.splits) : 1u;
+  const bool pair_swiglu = !GATE_UP && p.pair_swiglu;
+  dim3 grid((p.rows + BLOCK_TOK - 1) / BLOCK_TOK,
+            (p.out_rows + kRows - 1) / kRows * (pair_swiglu ? 2 : 1), p.splits);
+  dim3 cluster(1, 1, 1);
+  if (pair_swiglu) cluster = dim3(1, 2, 1);
+  else if (!GATE_UP && p.cluster && p.splits > 1) cluster = dim3(1, 1, p.splits);
   return launch_kernel_cluster(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid, dim3(kThreads),
-                               nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, cluster_z, tmap_w, tmap_a,
-                               p);
+                               nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, cluster, tmap_w, tmap_a, p);
 }
 
 template <int BLOCK_TOK, bool GATE_UP>

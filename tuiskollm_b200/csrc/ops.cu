@@ -587,8 +587,19 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
   p.debug = debug_flags();
+  // Decode shapes: gate/up as clusters of two plain tiles (two CTAs per SM, 272 CTAs for the
+  // 34 816-row plane) instead of one fused CTA per output tile (136 CTAs, one per SM).
+  bool as_pairs = false;
+  if (gate_up && block_tok == 32) {
+    const char* ps = std::getenv("TK100_SWIGLU_PAIRS");
+    as_pairs = !(ps && ps[0] == '0');
+  }
+  if (as_pairs) {
+    p.pair_swiglu = 1;
+    p.splits = 1;
+  }
   ctx_.count_launch();
-  return ctx_.check(launch_nvfp4_gemm(stream, block_tok, gate_up, map_w, map_a, p),
+  return ctx_.check(launch_nvfp4_gemm(stream, block_tok, gate_up && !as_pairs, map_w, map_a, p),
                     "launching the NVFP4 projection");
 }
 
