@@ -518,7 +518,9 @@ def run_case(args):
         rows = nvfp4_rows(torch, tk, ctx, (int(parts[1]),))
     elif parts[0] == "fp8":
         n_rows, m = int(parts[1]), int(parts[2])
-        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, "cuda") for c in range(4)]
+        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)  # as in extra_rows: 3 x L2
+        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, "cuda")
+                  for c in range(copies)]
         x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), "cuda")
         codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device="cuda")
         scales = torch.empty((m,), dtype=torch.float32, device="cuda")
@@ -528,14 +530,14 @@ def run_case(args):
         state = {"i": 0}
 
         def proj():
-            w, sc = planes[state["i"] % 4]
+            w, sc = planes[state["i"] % copies]
             state["i"] += 1
             op.launch(None, m, None, codes, scales, w, sc, outp)
 
-        graph = capture(torch, proj, 8)
+        graph = capture(torch, proj, copies)
         for _ in range(3):
             graph.replay()
-        ms = time_region(torch, graph.replay, 20) / 160
+        ms = time_region(torch, graph.replay, 20) / (20 * copies)
         rows = [{"op": "fp8", "N": n_rows, "M": m, "us": ms * 1e3,
                  "GB/s": algorithmic_bytes(m, n_rows, HIDDEN, 2) / ms / 1e6}]
     else:

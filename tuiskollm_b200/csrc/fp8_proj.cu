@@ -93,6 +93,16 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP ? 2 : 3) : (
   const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / p.splits);
   const int nkb = kb_end - kb_begin;
 
+  // A short weight stream is queued at L2 whole, first thing: the weights do not depend on the
+  // predecessor kernel, so HBM keeps working through the predecessor's tail and through this
+  // kernel's own set-up, and the ring below then fills from L2.
+  if (warp == 2 && p.l2_prefetch > 0) {
+    const int ahead = nkb < p.l2_prefetch ? nkb : p.l2_prefetch;
+    for (int i = lane; i < ahead; i += 32) {
+      tma_prefetch_l2_2d(&tmap_w, (kb_begin + i) * kTileKBytes, tile_n * kTileRows);
+    }
+  }
+
   // A wait that timed out earlier in this stream has already made the results invalid:
   // later CTAs leave at once instead of queueing more multi-second waits.  (Under
   // programmatic launch the predecessor may still be running; a fault it raises after this

@@ -73,6 +73,8 @@ struct Fp8ProjParams {
   int k;          // reduction length, multiple of 128
   int splits;     // K splits (grid.z)
   int deep_ring;  // 1: longer ring, two CTAs per SM (launches with few CTAs)
+  int l2_prefetch;  // > 0: before waiting for the predecessor, ask L2 for up to this many weight
+                    // k-blocks beyond the ring (short weight streams that fit L2)
   int cluster;    // 1: the splits of a tile form a thread-block cluster and reduce over
                   // distributed shared memory; 0: fp32 partial tiles in `partials` + tickets
   const float* act_scales;      // [rows]
@@ -124,6 +126,7 @@ struct Nvfp4Params {
   int pair_swiglu;     // 1: plain tiles in clusters of two (gate tile, up tile): the up CTA hands
                        // its accumulator to the gate CTA, which writes bf16(silu(gate) * up)
   int up_row_offset;   // gate/up fusion: first weight row of the up half (= out_rows)
+  int l2_prefetch;     // > 0: queue up to this many weight k-blocks of the CTA's slice at L2 first
   const uint8_t* w_scales;  // swizzled E4M3 weight scales
   const uint8_t* a_scales;  // swizzled E4M3 activation scales
   float out_scale;     // 1 / (weight divisor * activation divisor)

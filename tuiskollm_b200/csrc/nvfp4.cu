@@ -113,6 +113,29 @@ __global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 
   const int nkb = kb_end - kb_begin;
   const int tok0 = tile_m * BLOCK_TOK;
 
+  // A short weight stream (decode shapes) is queued at L2 whole before anything else: it does
+  // not depend on the predecessor kernel, and HBM then works through that kernel's tail and
+  // this one's set-up.
+  if (warp == 2 && p.l2_prefetch > 0) {
+    const int ahead = nkb < p.l2_prefetch ? nkb : p.l2_prefetch;
+    const size_t chunks_per_tile = static_cast<size_t>(p.k / 64);
+    for (int i = lane; i < ahead; i += 32) {
+      const int kb = kb_begin + i;
+      const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
+      tma_prefetch_l2_2d(&tmap_w, kb * kStageKBytes, w_tile * kRows);
+      bulk_prefetch_l2(p.w_scales + (static_cast<size_t>(w_tile) * chunks_per_tile) * kSfChunk +
+                           static_cast<size_t>(kb) * kSfStage,
+                       sf_bytes);
+      if (GATE_UP) {
+        tma_prefetch_l2_2d(&tmap_w, kb * kStageKBytes, p.up_row_offset + tile_n * kRows);
+        bulk_prefetch_l2(p.w_scales +
+                             (static_cast<size_t>(p.up_row_offset / kRows + tile_n) * chunks_per_tile) * kSfChunk +
+                             static_cast<size_t>(kb) * kSfStage,
+                         sf_bytes);
+      }
+    }
+  }
+
   if (threadIdx.x == 0) ctl->flag = *reinterpret_cast<volatile uint32_t*>(p.status);
   __syncthreads();
   const bool clustered = !GATE_UP && p.cluster != 0 && p.splits > 1;

@@ -378,7 +378,12 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   const int kb_total = columns / 128;
   // Fill the SMs (two CTAs fit per SM up to 64-token tiles) by splitting K when the
   // plane has few 128-row tiles.
-  const long long slots = static_cast<long long>(ctx_.sm_count()) * (block_tok <= 128 ? 2 : 1);
+  // CTAs per SM by shared memory and registers: three up to 32-token tiles, two up to 128
+  long long slots =
+      static_cast<long long>(ctx_.sm_count()) * (block_tok <= 32 ? 3 : block_tok <= 128 ? 2 : 1);
+  if (const char* sp = std::getenv("TK100_SLOTS_PER_SM")) {
+    if (std::atoi(sp) > 0) slots = static_cast<long long>(ctx_.sm_count()) * std::atoi(sp);
+  }
   int splits = static_cast<int>(slots / tiles);
   if (ctx_.forced_splits() > 0) splits = ctx_.forced_splits();
   if (splits > 8) splits = 8;
@@ -409,6 +414,13 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     // unsplit launches with at most two CTAs per SM (an LM-head shard on 8 GPUs): measured
     // 26 us instead of 32 us for a 31 040-row shard; split launches are faster with three
     p.deep_ring = dr ? (dr[0] != '0') : (splits == 1 && tiles <= 2LL * ctx_.sm_count());
+  }
+  {
+    // Queueing the CTA's weight slice at L2 before the ring starts looked good only while the
+    // rotating weight copies of the measurement still hit L2; on cold weights it costs
+    // (N = 12288, M = 1: 12.7 -> 14.0 us), so it stays an experiment switch.
+    const char* lp = std::getenv("TK100_L2_PREFETCH");
+    p.l2_prefetch = lp ? std::atoi(lp) : 0;
   }
   p.act_scales = activation_scales;
   p.w_scales = weight_scales;
@@ -577,6 +589,12 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   p.splits = splits;
   p.cluster = cluster_reduce_enabled() ? 1 : 0;
   p.up_row_offset = gate_up ? out_rows : 0;
+  {
+    // Queueing the slice at L2 first does not pay (measured at M = 1: gate/up 20.7 -> 22.0 us,
+    // down 13.4 -> 14.9 us), so only TK100_NVFP4_L2_PREFETCH=n turns it on.
+    const char* lp = std::getenv("TK100_NVFP4_L2_PREFETCH");
+    p.l2_prefetch = lp ? std::atoi(lp) : 0;
+  }
   p.w_scales = weight_scales;
   p.a_scales = activation_scales;
   // the reference passes 1/divisor to its kernel (nvfp4/swiglu.rs:541); both divisors here

@@ -158,6 +158,22 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
 
 // 2-D tiled load, completion counted in bytes on `bar`.  c0 is the innermost
 // coordinate; c0 * element size must be a multiple of 16 bytes.
+// Asks L2 to fetch one box of a tiled tensor; nothing lands in shared memory and nothing is
+// signalled.  Same 16-byte rule for x as a load.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+
+// Asks L2 to fetch `bytes` (a multiple of 16) from a 16-byte aligned global address.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(gptr)),
+               "r"(bytes)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int32_t c0, int32_t c1, uint64_t policy) {
   asm volatile(

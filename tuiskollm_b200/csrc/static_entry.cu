@@ -158,7 +158,8 @@ extern "C" TK100_API tk100_status tk100_fp8_projection_static(
   const int block_tok = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
   const long long tiles_n = (out_rows + 127) / 128;
   const long long tiles = tiles_n * ((rows + block_tok - 1) / block_tok);
-  const long long slots = static_cast<long long>(st->sm_count) * (block_tok <= 128 ? 2 : 1);
+  const long long slots =
+      static_cast<long long>(st->sm_count) * (block_tok <= 32 ? 3 : block_tok <= 128 ? 2 : 1);
   int splits = static_cast<int>(slots / tiles);
   if (splits > 8) splits = 8;
   if (splits > columns / 128) splits = columns / 128;
