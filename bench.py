@@ -38,6 +38,11 @@ sys.path.insert(0, ROOT)
 HIDDEN = 5120
 VOCAB = 248320
 SEED = 20260425
+# DRAM bytes (read + write) that ncu counted for one LM-head projection launch at vocab 248320,
+# M = 1, over that launch's algorithmic bytes (1 272 757 504 / 1 272 893 444): every weight byte
+# crosses HBM once.  The capture is summarised in
+# profiles/fp8_projection_kernel_lm_head_full_m1_traffic.md.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1272757504 / 1272893444
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -664,10 +669,20 @@ def run_native(args):
     launches = (launches_per_step * args.steps if launches_per_step is not None
                 else ctx.launch_count - launches0)
     barrier()
+    # End to end: the same step with the pinned-host -> device copy of the hidden rows in front
+    # and the device -> pinned-host copy of the selected (value, index) pairs behind, recorded
+    # into one graph like the step itself; the host waits for every step's result.
+    run_e2e, e2e_mode = step_e2e, "eager"
+    if mode == "graph":
+        try:
+            graph_e2e = capture(torch, step_e2e, 1)
+            run_e2e, e2e_mode = graph_e2e.replay, "graph"
+        except Exception:  # keep the eager calls
+            torch.cuda.synchronize()
     for _ in range(3):
-        step_e2e()
+        run_e2e()
     barrier()
-    ms_e2e = time_region(torch, step_e2e, args.steps, sync_each=True)
+    ms_e2e = time_region(torch, run_e2e, args.steps, sync_each=True)
     barrier()
     for _ in range(3):
         projection_only()
@@ -720,10 +735,15 @@ def run_native(args):
                              % (shard * HIDDEN / 1e6),
                        "tokens_per_s": m / (per_step * 1e-3), "us_per_step": per_step * 1e3},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
-                    "d2h_bytes_per_step": m * 8, "us_per_step": ms_e2e / args.steps * 1e3},
+                    "d2h_bytes_per_step": m * 8, "us_per_step": ms_e2e / args.steps * 1e3,
+                    "launch": e2e_mode},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak,
+                         "traffic": int(round(shard_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE)),
+                         "traffic_source": "ncu dram read+write bytes of this kernel at vocab "
+                                           "248320, M=1 (1 272 757 504 B), scaled by algorithmic bytes",
+                         "peak_kind": peak_kind,
                          "kernel": "fp8_projection_kernel<16> (+ argmax finalize, < 2 us)",
                          "us_per_launch": proj_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
             "clocks": clocks,
