@@ -38,8 +38,9 @@ constexpr int kSfSlots = 8;          // TMEM scale slots in rotation
 constexpr int kSfSlotCols = 16;      // columns per slot: SFA0 [0,4) SFA1 [4,8) SFB [8,12)
 
 __host__ __device__ constexpr int nv_stages(int block_tok, bool gate_up) {
-  // plain projection at <= 32 tokens: 4 stages (98 KB) so that two CTAs share an SM
-  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 4 : 6);
+  // plain projection: 4 stages (98 KB) at <= 32 tokens and 3 stages (108 KB) at 128, so that
+  // two CTAs share an SM (one runs its epilogue or split reduction under the other's loop)
+  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 4 : 3);
 }
 
 __host__ __device__ constexpr int nv_stage_bytes(int block_tok, bool gate_up) {
@@ -76,7 +77,7 @@ __device__ __forceinline__ float silu_stable(float v) {
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
-__global__ void __launch_bounds__(kThreads, (!GATE_UP && BLOCK_TOK <= 32) ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, GATE_UP ? 1 : 2)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_a, const Nvfp4Params p) {
   constexpr int STAGES = nv_stages(BLOCK_TOK, GATE_UP);

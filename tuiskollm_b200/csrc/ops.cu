@@ -562,7 +562,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
     // Clusters cannot straddle GPCs, so a launch that fills every slot spills into a second
     // wave: aim at ~80 % of the slots (measured on 5120 x 17408, M = 8: 6 splits 13.0 us, 7 splits
     // 20.6 us, 8 splits 19.3 us).
-    const long long slots = static_cast<long long>(ctx_.sm_count()) * (block_tok <= 32 ? 2 : 1);
+    const long long slots = static_cast<long long>(ctx_.sm_count()) * 2;
     splits = static_cast<int>(slots * 82 / 100 / tiles);
     if (ctx_.forced_splits() > 0) splits = ctx_.forced_splits();
     if (splits > 8) splits = 8;
