@@ -33,6 +33,11 @@ constexpr int kWTile = kRows * kStageKBytes;  // 16 KB
 constexpr int kSfChunk = 512;        // scales of 128 rows x 4 groups (one UMMA K = 64)
 constexpr int kSfStage = 4 * kSfChunk;  // 2 KB: 128 rows x 16 groups
 constexpr int kThreads = 320;        // warp 0: TMA, warp 1: UMMA + TMEM, warps 2-9: epilogue
+// The fused gate/up epilogue at 128 tokens is latency-bound math (ex2, rcp) with one CTA per SM:
+// four warps per TMEM lane quadrant instead of two.
+__host__ __device__ constexpr int nv_threads(int block_tok, bool gate_up) {
+  return (gate_up && block_tok >= 128) ? 576 : kThreads;
+}
 constexpr int kEpilogueThreads = 256; // two warps per TMEM lane quadrant, alternate 16-column chunks
 constexpr int kSfSlots = 8;          // TMEM scale slots in rotation
 constexpr int kSfSlotCols = 16;      // columns per slot: SFA0 [0,4) SFA1 [4,8) SFB [8,12)
@@ -71,13 +76,13 @@ __device__ __forceinline__ void nv_epilogue_barrier() {
 // (tuisko-kernels-sm89/src/nvfp4/swiglu.rs:142-155), ex2.approx for the exponential.
 __device__ __forceinline__ float silu_stable(float v) {
   const float e = -fabsf(v) * 1.4426950408889634f;
-  float ex = 0.0f;
-  if (e >= -126.0f) asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(e));
+  float ex;  // .ftz: 2^e below the normal range reads as 0, as the e < -126 cut-off did
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(e));
   return __fdividef(v >= 0.0f ? v : v * ex, 1.0f + ex);
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
-__global__ void __launch_bounds__(kThreads, GATE_UP ? 1 : 2)
+__global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 2)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_a, const Nvfp4Params p) {
   constexpr int STAGES = nv_stages(BLOCK_TOK, GATE_UP);
@@ -272,7 +277,8 @@ __global__ void __launch_bounds__(kThreads, GATE_UP ? 1 : 2)
   } else {
     const int et = threadIdx.x - 64;   // 0..255
     const int quad = warp & 3;         // TMEM lane quadrant of this warp
-    const int half = (warp - 2) >> 2;  // which of the two warps of the quadrant
+    const int half = (warp - 2) >> 2;  // which of the warps of the quadrant
+    constexpr int kChunkStride = 16 * ((nv_threads(BLOCK_TOK, GATE_UP) - 64) / 128);
     const int row_in_tile = quad * 32 + lane;
     const int n = out_tile * kRows + row_in_tile;
     const bool row_ok = n < p.out_rows;
@@ -288,19 +294,25 @@ __global__ void __launch_bounds__(kThreads, GATE_UP ? 1 : 2)
       // experiment: accumulators left unread
     } else if (GATE_UP) {
 #pragma unroll 1
-      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += kChunkStride) {
         if (c0 >= valid_tok) break;
         uint32_t g[16], u[16];
         tmem_ld16(taddr + c0, g);
         tmem_ld16(taddr + BLOCK_TOK + c0, u);
         tmem_ld_wait();
+        // all 16 results first, branch-free, so that their ex2/rcp chains overlap
+        uint32_t bits[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          if (c0 + j < valid_tok && row_ok) {
-            const float gate = __fmul_rn(__uint_as_float(g[j]), s);
-            const float up = __fmul_rn(__uint_as_float(u[j]), s);
-            p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
-                static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up)));
+          const float gate = __fmul_rn(__uint_as_float(g[j]), s);
+          const float up = __fmul_rn(__uint_as_float(u[j]), s);
+          bits[j] = f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up));
+        }
+        uint16_t* dst = p.out + static_cast<size_t>(tok0 + c0) * p.out_rows + n;
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid_tok) dst[static_cast<size_t>(j) * p.out_rows] = static_cast<uint16_t>(bits[j]);
           }
         }
       }
@@ -436,13 +448,19 @@ __global__ void __launch_bounds__(kThreads, GATE_UP ? 1 : 2)
 #pragma unroll
         for (int j = 0; j < 16; ++j) u[j] = ld_dsmem_f32(up_addr + (c0 + j) * kRows * 4, 1u);
         tmem_ld_wait();
+        uint32_t bits[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          if (c0 + j < valid_tok && row_ok) {
-            const float gate = __fmul_rn(__uint_as_float(g[j]), p.out_scale);
-            const float up = __fmul_rn(u[j], p.out_scale);
-            p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] =
-                static_cast<uint16_t>(f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up)));
+          const float gate = __fmul_rn(__uint_as_float(g[j]), p.out_scale);
+          const float up = __fmul_rn(u[j], p.out_scale);
+          bits[j] = f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up));
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid_tok) {
+              p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] = static_cast<uint16_t>(bits[j]);
+            }
           }
         }
       }
@@ -569,7 +587,8 @@ cudaError_t nv_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUte
   dim3 cluster(1, 1, 1);
   if (pair_swiglu) cluster = dim3(1, 2, 1);
   else if (!GATE_UP && p.cluster && p.splits > 1) cluster = dim3(1, 1, p.splits);
-  return launch_kernel_cluster(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid, dim3(kThreads),
+  return launch_kernel_cluster(nvfp4_gemm_kernel<BLOCK_TOK, GATE_UP>, grid,
+                               dim3(nv_threads(BLOCK_TOK, GATE_UP)),
                                nv_smem_bytes<BLOCK_TOK, GATE_UP>(), stream, cluster, tmap_w, tmap_a, p);
 }
 

@@ -57,8 +57,8 @@ constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes 
 
 __device__ __forceinline__ float silu_stable_pair(float v) {
   const float e = -fabsf(v) * 1.4426950408889634f;
-  float ex = 0.0f;
-  if (e >= -126.0f) asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(e));
+  float ex;  // .ftz: 2^e below the normal range reads as 0
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(e));
   return __fdividef(v >= 0.0f ? v : v * ex, 1.0f + ex);
 }
 
