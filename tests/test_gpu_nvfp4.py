@@ -287,6 +287,39 @@ def test_pair_route_small_geometry(tk, oracle, rows, monkeypatch):
     assert np.array_equal(results["pair"][0], results["single"][0])
 
 
+@pytest.mark.parametrize("rows", [1, 7, 32, 33, 130, 256])
+def test_gate_up_cluster_pairs_and_fused_kernel_agree(tk, oracle, rows, monkeypatch):
+    """gate_up + SwiGLU on its two routes, ragged token counts included: clusters of a gate CTA
+    and an up CTA that swap accumulator halves over distributed shared memory (the default), and
+    one CTA that holds both tiles (TK100_SWIGLU_PAIRS=0).  Both against the W4A4 oracle; the
+    two agree to the bit (same products, same fp32 accumulation order per output)."""
+    from tuiskollm_b200 import synth
+
+    hidden, inter = 1024, 512
+    xb = synth.normal_bf16(15, rows, (rows, hidden))
+    gu_codes, gu_scales, gu_div = synth.nvfp4_weights(15, 1, 2 * inter, hidden)
+    a_div = float(np.float32(448.0 * 6.0 / 5.0))
+    results = {}
+    for route, env in (("pairs", "1"), ("fused", "0")):
+        monkeypatch.setenv("TK100_SWIGLU_PAIRS", env)
+        ctx = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=512)
+        codes, scales = act_planes(tk, rows + 1, hidden)
+        mid = sentinel_plane((rows + 1, inter), torch.int16)
+        tk.Nvfp4SwiGluOp(ctx).launch(None, rows, dev(xb.view(np.int16)), dev(gu_codes), dev(gu_scales),
+                                     float(gu_div), mid, activation_codes=codes,
+                                     activation_scales=scales, input_global_divisor=a_div)
+        torch.cuda.synchronize()
+        assert_inactive_untouched(mid, rows)
+        assert ctx.device_status() == 0, route
+        results[route] = _u16(mid)[:rows].copy()
+    oc, osc = oracle.nvfp4_quantize(xb, a_div)
+    dots = oracle.nvfp4_w4a4_dot(oc, osc, a_div, gu_codes, gu_scales, float(gu_div))
+    exp_mid = oracle.silu_mul(dots[:, :inter], dots[:, inter:])
+    for route, got in results.items():
+        assert max_relative_error(got, exp_mid, 4 * float(np.abs(exp_mid).mean())) <= 1e-2, route
+    assert np.array_equal(results["pairs"], results["fused"])
+
+
 @pytest.mark.parametrize("world,rows", [(2, 5), (8, 40), (8, 200)])
 def test_row_parallel_down_shards_sum_to_the_full_projection(tk, oracle, world, rows):
     """Tensor-parallel down projection emulated on one GPU: every rank's reduction shard

@@ -317,17 +317,20 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         }
       }
     } else if (pair_swiglu) {
-      if (pair_rank == 1) {  // up tile: park the accumulator for the gate CTA
-        float* mine = reinterpret_cast<float*>(smem) + row_in_tile;
+      // Each CTA finishes half of the token tile: the gate CTA tokens [0, H), the up CTA
+      // [H, 2H).  Here it parks the other half of its accumulator ([token][row] fp32 over the
+      // ring, free once tmem_full has fired) for the partner.
+      constexpr int H = BLOCK_TOK / 2;
+      const int park0 = pair_rank == 0 ? H : 0;
+      float* mine = reinterpret_cast<float*>(smem) + row_in_tile;
 #pragma unroll 1
-        for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
-          if (c0 >= valid_tok) break;
-          uint32_t r[16];
-          tmem_ld16(taddr + c0, r);
-          tmem_ld_wait();
+      for (int c = half * 16; c < H; c += 32) {
+        if (park0 + c >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + park0 + c, r);
+        tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[(c0 + j) * kRows] = __uint_as_float(r[j]);
-        }
+        for (int j = 0; j < 16; ++j) mine[(c + j) * kRows] = __uint_as_float(r[j]);
       }
     } else if (p.splits == 1) {
 #pragma unroll 1
@@ -430,29 +433,34 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
   if (pair_swiglu) {
     cluster_arrive();
     cluster_wait();
-    if (warp >= 2 && pair_rank == 0 && !(p.debug & DBG_NO_EPILOGUE)) {
+    if (warp >= 2 && !(p.debug & DBG_NO_EPILOGUE)) {
+      constexpr int H = BLOCK_TOK / 2;
       const int quad = warp & 3;
       const int half = (warp - 2) >> 2;
       const int row_in_tile = quad * 32 + lane;
       const int n = out_tile * kRows + row_in_tile;
       const bool row_ok = n < p.out_rows;
       const int valid_tok = min(BLOCK_TOK, p.rows - tok0);
+      const int keep0 = pair_rank == 0 ? 0 : H;
       const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
-      const uint32_t up_addr = smem_u32(reinterpret_cast<float*>(smem) + row_in_tile);
+      const uint32_t other_addr = smem_u32(reinterpret_cast<float*>(smem) + row_in_tile);
 #pragma unroll 1
-      for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+      for (int c = half * 16; c < H; c += 32) {
+        const int c0 = keep0 + c;
         if (c0 >= valid_tok) break;
-        uint32_t g[16];
-        tmem_ld16(taddr + c0, g);
-        float u[16];
+        uint32_t own[16];
+        tmem_ld16(taddr + c0, own);
+        float oth[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) u[j] = ld_dsmem_f32(up_addr + (c0 + j) * kRows * 4, 1u);
+        for (int j = 0; j < 16; ++j) oth[j] = ld_dsmem_f32(other_addr + (c + j) * kRows * 4, pair_rank ^ 1u);
         tmem_ld_wait();
         uint32_t bits[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float gate = __fmul_rn(__uint_as_float(g[j]), p.out_scale);
-          const float up = __fmul_rn(u[j], p.out_scale);
+          const float mine_v = __fmul_rn(__uint_as_float(own[j]), p.out_scale);
+          const float oth_v = __fmul_rn(oth[j], p.out_scale);
+          const float gate = pair_rank == 0 ? mine_v : oth_v;
+          const float up = pair_rank == 0 ? oth_v : mine_v;
           bits[j] = f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up));
         }
         if (row_ok) {
@@ -465,7 +473,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         }
       }
     }
-    cluster_arrive();  // the up CTA keeps its shared memory until the gate CTA has read it
+    cluster_arrive();  // both CTAs keep their shared memory until the partner has read it
     cluster_wait();
   }
 

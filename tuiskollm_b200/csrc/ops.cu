@@ -520,10 +520,10 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
     const char* pe = std::getenv("TK100_PAIR");
     const char* pm = std::getenv("TK100_PAIR_MIN_ROWS");
     const int min_rows = pm ? std::atoi(pm) : 1024;
-    const bool allowed = !(pe && pe[0] == '0');
-    // Measured at M = 2048: down 242 -> 185 us on pairs; gate_up is no faster on pairs (its
-    // gate/up exchange costs what the lighter loads save), so it takes this route only when
-    // TK100_PAIR=2 asks for it.
+    // Off unless TK100_PAIR=1 (down) or 2 (gate_up too): with two CTAs per SM the 128 x 128
+    // tiles of the plain kernel overlap one CTA's epilogue with the other's loop and lose less
+    // to the last wave (down at M = 2048: 149 us, CTA pairs 191 us).
+    const bool allowed = pe && (pe[0] == '1' || pe[0] == '2');
     const bool this_op = gate_up ? (pe && pe[0] == '2') : (out_rows % 256 == 0);
     if (allowed && this_op && rows >= min_rows) {
       const uint64_t w_rows = static_cast<uint64_t>(out_rows) * (gate_up ? 2 : 1);
@@ -605,10 +605,13 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
   p.debug = debug_flags();
-  // Decode shapes: gate/up as clusters of two plain tiles (two CTAs per SM, 272 CTAs for the
-  // 34 816-row plane) instead of one fused CTA per output tile (136 CTAs, one per SM).
+  // gate/up runs as clusters of two plain tiles (gate CTA, up CTA; two CTAs per SM) that swap
+  // half of their accumulators over distributed shared memory, each finishing half of the
+  // tokens.  Measured against the fused kernel (one CTA holds both tiles, one CTA per SM):
+  // M = 1 24.4 -> 20.7 us, M = 256 51.6 -> 45.2 us, M = 2048 368 -> 318 us.  TK100_SWIGLU_PAIRS=0
+  // selects the fused kernel.
   bool as_pairs = false;
-  if (gate_up && block_tok == 32) {
+  if (gate_up) {
     const char* ps = std::getenv("TK100_SWIGLU_PAIRS");
     as_pairs = !(ps && ps[0] == '0');
   }
