@@ -112,6 +112,36 @@ def test_synthetic_configs_match_oracle(tk, ctx, oracle, kind, out_rows, rows):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("out_rows,rows", [(512, 512), (768, 700), (256, 1030), (5120, 600)])
+def test_pair_route_matches_oracle_and_one_cta_route(tk, oracle, out_rows, rows, monkeypatch):
+    """Prefill token counts take the CTA-pair kernel (cta_group::2, 256-row x 256-token pair
+    tiles); ragged token counts exercise the zero-filled tails.  Against the oracle, and against
+    the one-CTA kernel, which splits K at these small sizes: the two may differ by one BF16
+    rounding step, no more."""
+    from tuiskollm_b200 import synth
+
+    hidden = 1024
+    xb = synth.normal_bf16(43, rows, (rows, hidden))
+    wc, ws = synth.fp8_weights(43, out_rows, out_rows, hidden)
+    outs = {}
+    for route, env in (("pair", "1"), ("single", "0")):
+        monkeypatch.setenv("TK100_FP8_PAIR", env)
+        ctx = tk.Context(device=0, hidden=hidden, max_rows=2048)
+        planes = Planes(rows + 2, hidden, out_rows)
+        launches = ctx.launch_count
+        tk.GdnInputProjectionOp(ctx, out_rows).launch(
+            None, rows, dev(xb.view(np.int16)), planes.codes, planes.scales, dev(wc),
+            dev(ws.view(np.int16)), planes.out)
+        torch.cuda.synchronize()
+        assert ctx.launch_count - launches == 2, route  # quantiser + one projection kernel
+        check_projection(oracle, xb, wc, ws, planes, rows, floor=0.25 * (hidden / 5120) ** 0.5)
+        assert ctx.device_status() == 0, route
+        outs[route] = _u16(planes.out)[:rows].copy()
+    a = (outs["pair"].astype(np.uint32) << 16).view(np.float32)
+    b = (outs["single"].astype(np.uint32) << 16).view(np.float32)
+    assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-4)
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 8])
 @pytest.mark.parametrize("block_tok", [0, 64])
 def test_split_k_is_exact_and_deterministic(tk, oracle, splits, block_tok):

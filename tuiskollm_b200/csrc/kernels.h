@@ -95,6 +95,11 @@ cudaError_t launch_fp8_projection(cudaStream_t stream, int block_tok, const CUte
 size_t fp8_projection_smem_bytes(int block_tok);
 int fp8_projection_stages(int block_tok);
 cudaError_t fp8_projection_prepare();  // sets the dynamic shared-memory attributes once
+// fp8_pair.cu: prefill route on CTA pairs (256-row x 256-token pair tiles, BF16 output only,
+// unsplit K; out_rows must be a multiple of 256).
+cudaError_t fp8_pair_prepare();
+cudaError_t launch_fp8_pair(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
+                            const Fp8ProjParams& p);
 
 struct ArgmaxPair {
   float value;

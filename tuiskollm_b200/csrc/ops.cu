@@ -111,6 +111,11 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
     delete ctx;
     return TK100_ERR_MODULE;
   }
+  if ((e = fp8_pair_prepare()) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the FP8 pair route: ") + cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
   if ((e = nvfp4_pair_prepare()) != cudaSuccess) {
     *error = std::string("[gpu.module] preparing the NVFP4 pair routes: ") + cudaGetErrorString(e);
     delete ctx;
@@ -363,6 +368,37 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   if (argmax_scratch) TK100_TRY(check_plane(ctx_, name_, "argmax scratch", argmax_scratch, 8));
 
   if (input) TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
+
+  // Prefill shapes with a plain BF16 output: CTA pairs (256-row x 256-token pair tiles) halve
+  // the operand bytes per MAC, which is what bounds the one-CTA kernel there.
+  {
+    const char* pe = std::getenv("TK100_FP8_PAIR");
+    const char* pm = std::getenv("TK100_FP8_PAIR_MIN_ROWS");
+    const int min_rows = pm ? std::atoi(pm) : 256;
+    if (!(pe && pe[0] == '0') && rows >= min_rows && out_rows % 256 == 0 && output &&
+        !logits_f32 && !argmax_scratch && ctx_.forced_block_tok() == 0 && ctx_.forced_splits() == 0) {
+      CUtensorMap map_w, map_a;
+      TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(out_rows),
+                                static_cast<uint64_t>(columns), 128, &map_w));
+      TK100_TRY(ctx_.tensor_map(activation_codes, static_cast<uint64_t>(rows),
+                                static_cast<uint64_t>(columns), 128, &map_a));
+      Fp8ProjParams q{};
+      q.rows = rows;
+      q.out_rows = out_rows;
+      q.k = columns;
+      q.splits = 1;
+      // at most one CTA per SM: the longer ring
+      q.deep_ring = 2LL * ((rows + 255) / 256) * (out_rows / 256) <= ctx_.sm_count() ? 1 : 0;
+      if (const char* dr = std::getenv("TK100_DEEP_RING")) q.deep_ring = dr[0] != '0';
+      q.act_scales = activation_scales;
+      q.w_scales = weight_scales;
+      q.out = output;
+      q.status = ctx_.status_word();
+      q.debug = debug_flags();
+      ctx_.count_launch();
+      return ctx_.check(launch_fp8_pair(stream, map_w, map_a, q), "launching the FP8 pair projection");
+    }
+  }
 
   // token tile: the smallest that holds all rows, 128-token tiles beyond that (two CTAs of
   // 128 tokens share an SM; a 256-token tile would leave one CTA per SM and no overlap)
