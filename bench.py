@@ -252,6 +252,26 @@ def extra_rows(torch, tk, ctx, peak_gbs):
                         "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs,
                         "frac_of_8TBs": b / ms / 1e6 / 8000.0, "weight_copies": copies})
         del planes
+    # prefill-shaped FP8 projections (tensor-bound): one weight plane, graph of 8 launches
+    burst, _sustained, tkind = measured_tensor_peaks()
+    for name, n_rows in (("fp8_qkv", synth.QKV_ROWS), ("fp8_gdn_input", synth.GDN_ROWS)):
+        w, s = synth.torch_fp8_weights(SEED, 60, n_rows, HIDDEN, dev)
+        for m in (256, 512, 2048):
+            x = synth.torch_normal_bf16(SEED, 8, (m, HIDDEN), dev)
+            codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+            scales = torch.empty((m,), dtype=torch.float32, device=dev)
+            outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device=dev)
+            op = tk.GdnInputProjectionOp(ctx, n_rows)
+            op.launch(None, m, x, codes, scales, w, s, outp)
+            graph = capture(torch, lambda: op.launch(None, m, None, codes, scales, w, s, outp), 8)
+            for _ in range(3):
+                graph.replay()
+            ms = time_region(torch, graph.replay, 10) / 80
+            tf = 2.0 * m * n_rows * HIDDEN / ms / 1e9
+            out.append({"op": name, "M": m, "N": n_rows, "us": ms * 1e3, "TFLOPs": tf,
+                        "frac_of_4.5PF": tf / 4500.0, "frac_of_2x_measured_bf16": tf / (2 * burst),
+                        "tensor_peak_kind": tkind})
+        del w, s
     # fused residual + RMSNorm + quantise
     normop = tk.ResidualNormOp(ctx)
     for m in (1, 256, 512):
