@@ -367,15 +367,22 @@ def nvfp4_rows(torch, tk, ctx, row_counts=(2048, 256, 32, 8, 1)):
                       activation_codes=pl.m_codes, activation_scales=pl.m_scales,
                       input_global_divisor=pl.m_div)
 
+        def gate_up_q():  # the same projection also leaving the NVFP4 form of its output
+            gu.launch_quantize(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+                               activation_codes=pl.a_codes, activation_scales=pl.a_scales,
+                               input_global_divisor=pl.a_div, output_global_divisor=pl.m_div,
+                               output_codes=pl.m_codes, output_scales=pl.m_scales)
+
         def mlp():
-            quant_in(); gate_up(); quant_mid(); down()
+            quant_in(); gate_up_q(); down()
 
         for fn in (quant_in, gate_up, quant_mid, down):
             fn()
         torch.cuda.synchronize()
         times = {}
         for name, fn in (("quant_in", quant_in), ("gate_up_swiglu", gate_up),
-                         ("quant_mid", quant_mid), ("down", down), ("mlp_total", mlp)):
+                         ("quant_mid", quant_mid), ("gate_up_swiglu_quantize", gate_up_q),
+                         ("down", down), ("mlp_total", mlp)):
             graph = capture(torch, fn, 4)
             for _ in range(3):
                 graph.replay()
@@ -406,8 +413,9 @@ def nvfp4_rows(torch, tk, ctx, row_counts=(2048, 256, 32, 8, 1)):
 
 def layer_slice_rows(torch, tk, ctx):
     """Configuration 5, one GPU: residual add + RMSNorm + E4M3 and NVFP4 quantise (one kernel)
-    -> FP8 QKV (N = 8192) -> FP8 GDN-input (N = 12288) -> NVFP4 gate_up + SwiGLU -> NVFP4
-    re-quantise -> NVFP4 down, as one CUDA graph of six kernels."""
+    -> FP8 QKV (N = 8192) -> FP8 GDN-input (N = 12288) -> NVFP4 gate_up + SwiGLU (its epilogue
+    leaves the NVFP4 form of the intermediate at decode sizes, a quantiser launch otherwise) ->
+    NVFP4 down, as one CUDA graph of five or six kernels."""
     from tuiskollm_b200 import ops, synth
 
     out = []
@@ -436,10 +444,11 @@ def layer_slice_rows(torch, tk, ctx):
                                        pl.a_codes, pl.a_scales)
             qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
             gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
-            gu.launch(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
-                      activation_codes=pl.a_codes, activation_scales=pl.a_scales,
-                      input_global_divisor=pl.a_div)
-            dn.launch(None, m, pl.mid, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
+            gu.launch_quantize(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+                               activation_codes=pl.a_codes, activation_scales=pl.a_scales,
+                               input_global_divisor=pl.a_div, output_global_divisor=pl.m_div,
+                               output_codes=pl.m_codes, output_scales=pl.m_scales)
+            dn.launch(None, m, None, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
                       activation_codes=pl.m_codes, activation_scales=pl.m_scales,
                       input_global_divisor=pl.m_div)
 
@@ -451,7 +460,7 @@ def layer_slice_rows(torch, tk, ctx):
         reps = 50
         ms = time_region(torch, graph.replay, reps) / reps
         flops = 2.0 * m * HIDDEN * (synth.QKV_ROWS + synth.GDN_ROWS + 3 * synth.INTERMEDIATE)
-        out.append({"op": "layer_slice", "M": m, "us": ms * 1e3, "kernels": 6,
+        out.append({"op": "layer_slice", "M": m, "us": ms * 1e3, "kernels": 5 if m <= 32 else 6,
                     "weight_stream_GBs": weight_bytes / ms / 1e6, "TFLOPs": flops / ms / 1e9,
                     "floor_us_at_measured_hbm": weight_bytes / measured_peak()[0] / 1e3})
         del pl
@@ -500,9 +509,11 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local):
                                    a_scales)
         qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
         gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
-        gu.launch(None, m, None, gu_codes, gu_scales, gu_div, mid, activation_codes=a_codes,
-                  activation_scales=a_scales, input_global_divisor=a_div)
-        dn.launch_partial(None, m, mid, dn_codes, dn_scales, dn_div, partial,
+        gu.launch_quantize(None, m, None, gu_codes, gu_scales, gu_div, mid,
+                           activation_codes=a_codes, activation_scales=a_scales,
+                           input_global_divisor=a_div, output_global_divisor=m_div,
+                           output_codes=m_codes, output_scales=m_scales)
+        dn.launch_partial(None, m, None, dn_codes, dn_scales, dn_div, partial,
                           activation_codes=m_codes, activation_scales=m_scales,
                           input_global_divisor=m_div)
         if world > 1:

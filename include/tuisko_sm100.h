@@ -220,6 +220,18 @@ TK100_API tk100_status tk100_nvfp4_gate_up_swiglu(tk100_ctx* ctx, tk100_stream s
                                         const uint8_t* weight_codes, const uint8_t* weight_scales,
                                         float weight_scale_divisor, uint16_t* output);
 
+/* tk100_nvfp4_gate_up_swiglu that also leaves the NVFP4 form of its output (codes
+ * [rows, intermediate/2], swizzled block scales, definition at tk100_nvfp4_quantize_activation
+ * with output_global_divisor) for tk100_nvfp4_down(input == NULL).  Up to 32 rows the
+ * quantisation runs in the projection's epilogue instead of a launch of its own; beyond that
+ * the call launches the quantiser after the projection.  Both planes are always written.  No
+ * counterpart in the reference (its down kernel reads BF16). */
+TK100_API tk100_status tk100_nvfp4_gate_up_swiglu_quantize(
+    tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input, uint8_t* activation_codes,
+    uint8_t* activation_scales, float input_global_divisor, const uint8_t* weight_codes,
+    const uint8_t* weight_scales, float weight_scale_divisor, uint16_t* output,
+    float output_global_divisor, uint8_t* output_codes, uint8_t* output_scales);
+
 /* Nvfp4DownOp::launch (tuisko-kernels-sm89/src/nvfp4/down.rs:510-556): weight_codes
  * [hidden, intermediate/2], weight_scales swizzled [hidden, intermediate/16];
  * input / activation planes are [rows, intermediate]; output [rows, hidden]. */

@@ -320,6 +320,73 @@ def test_gate_up_cluster_pairs_and_fused_kernel_agree(tk, oracle, rows, monkeypa
     assert np.array_equal(results["pairs"], results["fused"])
 
 
+def test_activation_quantiser_rounding_ties(tk, oracle):
+    """The quantiser decides each E2M1 code by comparing x * divisor with midpoint * scale instead
+    of dividing; values that sit exactly on the rounding midpoints (ties to the even code), one
+    BF16 step beside them, and beyond the largest magnitude must come out as the oracle's
+    divide-then-round does."""
+    k = 64
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    mid_bits = mids.view(np.uint32) >> 16
+    above = ((mid_bits + 1) << 16).astype(np.uint32).view(np.float32)  # next BF16 value up
+    below = ((mid_bits - 1) << 16).astype(np.uint32).view(np.float32)  # next BF16 value down
+    g0 = np.concatenate([[6.0], mids, -mids, [-6.0]]).astype(np.float32)            # scale 1
+    g1 = (2.0 * g0).astype(np.float32)                                               # scale 2
+    g2 = (1.5 * g0).astype(np.float32)                                               # scale 1.5
+    g3 = np.concatenate([[6.0], above, -below, [7.0]]).astype(np.float32)  # beside the ties
+    rows = np.stack([np.concatenate([g0, g1, g2, g3]),
+                     np.concatenate([g3, -g2, g1 * np.float32(0.5), -g0]),
+                     np.concatenate([g0 * np.float32(2.0 ** -12), np.zeros(16, np.float32), -np.zeros(16, np.float32) - 0.0, g0 * np.float32(40.0)])])
+    bits = (rows.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    assert np.array_equal((bits.astype(np.uint32) << 16).view(np.float32), rows), "values must be BF16-exact"
+    ctx = tk.Context(device=0, hidden=1024, intermediate=512, max_rows=512)
+    for divisor in (1.0, 2.0, 0.5):
+        codes, scales = act_planes(tk, rows.shape[0] + 1, k)
+        tk.Nvfp4DownOp(ctx).quantize(None, rows.shape[0], k, dev(bits.view(np.int16)), divisor, codes, scales)
+        torch.cuda.synchronize()
+        check_quantiser(oracle, bits, divisor, codes, scales, rows.shape[0])
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 20, 33, 129, 300])
+def test_gate_up_epilogue_quantisation_equals_the_quantiser(tk, oracle, rows, monkeypatch):
+    """tk100_nvfp4_gate_up_swiglu_quantize: the codes and block scales it leaves for the down
+    projection equal, bit for bit, what the stand-alone quantiser (and the oracle) make of its
+    BF16 output, whether they come from the projection's epilogue (up to 32 rows on the cluster
+    route) or from the quantiser launch behind it; inactive rows stay untouched."""
+    from tuiskollm_b200 import ops, synth
+
+    hidden, inter = 1024, 512
+    xb = synth.normal_bf16(16, rows, (rows, hidden))
+    gu_codes, gu_scales, gu_div = synth.nvfp4_weights(16, 1, 2 * inter, hidden)
+    a_div = float(np.float32(448.0 * 6.0 / 5.0))
+    m_div = float(np.float32(448.0 * 6.0 / 8.0))
+    planes = {}
+    for route, env in (("pairs", "1"), ("fused", "0")):
+        monkeypatch.setenv("TK100_SWIGLU_PAIRS", env)
+        ctx = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=512)
+        codes, scales = act_planes(tk, rows + 1, hidden)
+        mid = sentinel_plane((rows + 1, inter), torch.int16)
+        q_codes = sentinel_plane((rows + 1, inter // 2), torch.uint8)
+        q_scales = sentinel_plane((ops.nvfp4_scale_plane_bytes(rows, inter),), torch.uint8)
+        launches = ctx.launch_count
+        tk.Nvfp4SwiGluOp(ctx).launch_quantize(
+            None, rows, dev(xb.view(np.int16)), dev(gu_codes), dev(gu_scales), float(gu_div), mid,
+            activation_codes=codes, activation_scales=scales, input_global_divisor=a_div,
+            output_global_divisor=m_div, output_codes=q_codes, output_scales=q_scales)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0, route
+        # input quantiser + projection, + the output quantiser where the epilogue does not do it
+        in_epilogue = route == "pairs" and rows <= 32
+        assert ctx.launch_count - launches == (2 if in_epilogue else 3), route
+        assert_inactive_untouched(mid, rows)
+        got_mid = _u16(mid)[:rows].copy()
+        check_quantiser(oracle, got_mid, m_div, q_codes, q_scales, rows)
+        planes[route] = (host(q_codes)[:rows].copy(), got_mid)
+    assert np.array_equal(planes["pairs"][1], planes["fused"][1])
+    assert np.array_equal(planes["pairs"][0], planes["fused"][0])
+
+
 @pytest.mark.parametrize("world,rows", [(2, 5), (8, 40), (8, 200)])
 def test_row_parallel_down_shards_sum_to_the_full_projection(tk, oracle, world, rows):
     """Tensor-parallel down projection emulated on one GPU: every rank's reduction shard

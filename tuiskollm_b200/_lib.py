@@ -56,6 +56,8 @@ SIGNATURES = {
     "tk100_nvfp4_quantize_activation": (_i, [_vp, _vp, _i, _i, _vp, C.c_float, _vp, _vp]),
     "tk100_nvfp4_gate_up_swiglu": (_i, [_vp, _vp, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, C.c_float,
                                         _vp]),
+    "tk100_nvfp4_gate_up_swiglu_quantize": (_i, [_vp, _vp, _i, _vp, _vp, _vp, C.c_float, _vp, _vp,
+                                                 C.c_float, _vp, C.c_float, _vp, _vp]),
     "tk100_nvfp4_down": (_i, [_vp, _vp, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, C.c_float, _vp]),
     "tk100_nvfp4_down_partial": (_i, [_vp, _vp, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, C.c_float,
                                       _vp]),

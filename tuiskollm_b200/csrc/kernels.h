@@ -137,6 +137,11 @@ struct Nvfp4Params {
   float out_scale;     // 1 / (weight divisor * activation divisor)
   uint16_t* out;       // [rows, out_rows] BF16
   float* out_f32;      // when set (plain projection only): unrounded fp32 output instead
+  // gate/up on cluster pairs at <= 32 tokens: also quantise the rounded outputs to NVFP4 for
+  // the next projection (codes [rows, out_rows / 2], swizzled block scales, row = token)
+  uint8_t* q_codes;
+  uint8_t* q_scales;
+  float q_divisor;
   float* partials;
   unsigned int* counters;
   uint32_t* status;

@@ -463,11 +463,47 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
           const float up = pair_rank == 0 ? oth_v : mine_v;
           bits[j] = f32_to_bf16_bits(__fmul_rn(silu_stable(gate), up));
         }
-        if (row_ok) {
+        if (row_ok && p.out) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (c0 + j < valid_tok) {
               p.out[static_cast<size_t>(tok0 + c0 + j) * p.out_rows + n] = static_cast<uint16_t>(bits[j]);
+            }
+          }
+        }
+        if (p.q_codes) {
+          // NVFP4 form of the rounded outputs, as nvfp4_quantize_kernel defines it: a block is 16
+          // consecutive outputs of a token = 16 lanes of this warp (out_rows is a multiple of
+          // 128, so every lane holds a valid row).
+          const int groups = p.out_rows >> 4;
+          const int g = n >> 4;
+          auto store_q = [&](int j, uint32_t nib, uint32_t other, uint32_t scale_code) {
+            const int r = tok0 + c0 + j;
+            if (!(lane & 1)) {
+              p.q_codes[static_cast<size_t>(r) * (p.out_rows >> 1) + (n >> 1)] =
+                  static_cast<uint8_t>(nib | (other << 4));
+            }
+            if (!(lane & 15)) {
+              const size_t off = (static_cast<size_t>(r >> 7) * (groups >> 2) + (g >> 2)) * 512 +
+                                 static_cast<size_t>(r & 31) * 16 + ((r & 127) >> 5) * 4 + (g & 3);
+              p.q_scales[off] = static_cast<uint8_t>(scale_code);
+            }
+          };
+          // decode shapes only (the operator sends larger launches through the quantiser
+          // kernel, which is faster there): the valid tokens one after the other
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid_tok) {  // warp-uniform
+              const float v = __uint_as_float(bits[j] << 16);
+              float amax = fmaxf(0.0f, fabsf(v));
+#pragma unroll
+              for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+              const uint32_t sc = f32x2_to_e4m3x2(__fdiv_rn(__fmul_rn(amax, p.q_divisor), 6.0f), 0.0f) & 0xffu;
+              const float sf = e4m3_to_f32(sc);
+              const uint32_t nib =
+                  sf == 0.0f ? (signbit(v) ? 0x8u : 0u)
+                             : (f32x2_to_e2m1x2(__fdiv_rn(__fmul_rn(v, p.q_divisor), sf), 0.0f) & 0xfu);
+              store_q(j, nib, __shfl_xor_sync(0xffffffffu, nib, 1), sc);
             }
           }
         }

@@ -123,6 +123,13 @@ struct LmHeadOp : Fp8ProjectionOp {
 // tuisko-kernels-sm89/src/nvfp4/swiglu.rs:470-571 and nvfp4/down.rs:455-556, with the
 // activation side quantised to NVFP4 as well (caller-owned code / scale planes, like the FP8
 // operators' activation planes) so that both operands feed the block-scaled tensor cores.
+// Where gate_up + SwiGLU also leaves the NVFP4 form of its output for the down projection.
+struct Nvfp4NextQuant {
+  float divisor;    // input_global_divisor of the consumer
+  uint8_t* codes;   // [rows, out_rows / 2]
+  uint8_t* scales;  // swizzled [ceil(rows / 128) * 128, out_rows / 16]
+};
+
 class Nvfp4MlpOp {
  public:
   explicit Nvfp4MlpOp(Context& ctx) : ctx_(ctx) {}
@@ -135,7 +142,7 @@ class Nvfp4MlpOp {
                 const uint16_t* input, uint8_t* activation_codes, uint8_t* activation_scales,
                 float input_global_divisor, const uint8_t* weight_codes,
                 const uint8_t* weight_scales, float weight_scale_divisor, uint16_t* output,
-                float* output_f32 = nullptr);
+                float* output_f32 = nullptr, const Nvfp4NextQuant* next = nullptr);
 
  private:
   Context& ctx_;

@@ -239,6 +239,18 @@ class Nvfp4SwiGluOp(_Nvfp4Op):
 
     _entry = "tk100_nvfp4_gate_up_swiglu"
 
+    def launch_quantize(self, stream, batch, input, weight_codes, weight_scales,
+                        weight_scale_divisor, output, *, activation_codes, activation_scales,
+                        input_global_divisor, output_global_divisor, output_codes, output_scales):
+        """The same projection, also leaving the NVFP4 codes and block scales of its output for
+        ``Nvfp4DownOp.launch(input=None, ...)`` (in the projection's epilogue up to 32 rows)."""
+        c = self.ctx
+        c.check(c._lib.tk100_nvfp4_gate_up_swiglu_quantize(
+            c.handle, _stream(stream), batch, _ptr(input), _ptr(activation_codes),
+            _ptr(activation_scales), input_global_divisor, _ptr(weight_codes),
+            _ptr(weight_scales), weight_scale_divisor, _ptr(output), output_global_divisor,
+            _ptr(output_codes), _ptr(output_scales)))
+
 
 class Nvfp4DownOp(_Nvfp4Op):
     """tuisko-kernels-sm89/src/nvfp4/down.rs:455-556."""
