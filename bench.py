@@ -467,10 +467,12 @@ def layer_slice_rows(torch, tk, ctx):
     return out
 
 
-def tp_layer_slice(torch, tk, dist, rank, world, m, local):
+def tp_layer_slice(torch, tk, dist, rank, world, m, local, nccl_reduce=False):
     """Configuration 5 on `world` GPUs: norm + quantise replicated; QKV / GDN-input / gate-up
-    column-parallel; down row-parallel with fp32 partial sums, one NCCL all-reduce of
-    [m, hidden] fp32 and one rounding to BF16.  Returns the device time per replay (ms)."""
+    column-parallel; down row-parallel with fp32 partial sums, which the library's peer-memory
+    kernel adds over NVLink and rounds to BF16 once (`nccl_reduce`: an NCCL all-reduce of
+    [m, hidden] fp32 and a rounding kernel instead).  Before timing, the two routes are compared.
+    Returns (device time per replay in ms, launch mode, reduce route)."""
     from tuiskollm_b200 import dist as tkd, ops, synth
 
     dev = "cuda"
@@ -503,6 +505,26 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local):
     gdn_op = tk.GdnInputProjectionOp(ctx, gdn_rows)
     gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
     a_div, m_div = 448.0 * 6.0 / 6.0, 448.0 * 6.0 / 8.0
+    route = "nccl all_reduce + rounding kernel"
+    peer_addrs = None
+    if world > 1 and not nccl_reduce:
+        try:
+            _rbuf, _rhdl, peer_addrs = tkd.alloc_peer_sum(m * HIDDEN, world, torch.device("cuda", local))
+            route = "peer-memory sum kernel over NVLink (one launch)"
+        except Exception as exc:  # symmetric memory unavailable: keep the NCCL route
+            route += f" (peer sum unavailable: {type(exc).__name__}: {exc})"[:200]
+        flag = torch.tensor([1 if peer_addrs is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # all ranks must agree on the route
+        if int(flag.item()) == 0:
+            peer_addrs = None
+
+    def reduce_():
+        if peer_addrs is not None:
+            ops.peer_sum_bf16(ctx, None, m * HIDDEN, m * HIDDEN, world, rank, partial, peer_addrs, out)
+            return
+        if world > 1:
+            dist.all_reduce(partial)
+        ops.f32_to_bf16(ctx, None, m * HIDDEN, partial, out)
 
     def slice_():
         norm.launch_quantize_nvfp4(None, m, x, br, nw, res, nrm, codes, scales, a_div, a_codes,
@@ -516,12 +538,24 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local):
         dn.launch_partial(None, m, None, dn_codes, dn_scales, dn_div, partial,
                           activation_codes=m_codes, activation_scales=m_scales,
                           input_global_divisor=m_div)
-        if world > 1:
-            dist.all_reduce(partial)
-        ops.f32_to_bf16(ctx, None, m * HIDDEN, partial, out)
+        reduce_()
 
     slice_()
     torch.cuda.synchronize()
+    if peer_addrs is not None:
+        # the peer sum against NCCL on the same partials: same values up to the order of the
+        # fp32 additions, i.e. at most one BF16 step apart, and identical on every rank
+        mine = out.clone()
+        check = partial.clone()
+        dist.all_reduce(check)
+        want = check.to(torch.bfloat16).float()
+        got = mine.float()
+        tol = want.abs() * 2.0 ** -7 + 1e-6
+        bad = int(((got - want).abs() > tol).sum())
+        assert bad == 0, f"peer sum differs from the NCCL all-reduce in {bad} values"
+        ref = mine.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(ref.view(torch.int16), mine.view(torch.int16)), "ranks hold different sums"
     mode = "graph"
     try:
         graph = capture(torch, slice_, 1)
@@ -537,7 +571,7 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local):
     reps = 50
     ms = time_region(torch, run, reps) / reps
     assert ctx.device_status() == 0
-    return ms, mode
+    return ms, mode, route
 
 
 def run_case(args):
@@ -723,8 +757,9 @@ def run_native(args):
     tp = []
     if world > 1 and not args.no_extra:
         for m_tp in (256, 1):
-            t_ms, t_mode = tp_layer_slice(torch, tk, dist, rank, world, m_tp, local)
-            tp.append([m_tp, t_ms, t_mode])
+            t_ms, t_mode, t_route = tp_layer_slice(torch, tk, dist, rank, world, m_tp, local,
+                                                   nccl_reduce=args.nccl_reduce)
+            tp.append([m_tp, t_ms, t_mode, t_route])
     times = torch.tensor([ms, ms_e2e, ms_proj] + [t[1] for t in tp], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -782,8 +817,9 @@ def run_native(args):
         }
         if tp:
             line["tp_layer_slice"] = [
-                {"M": t[0], "us": t[1] * 1e3, "launch": t[2], "all_reduce_bytes": t[0] * HIDDEN * 4,
-                 "parallelism": f"column(QKV,GDN-in,gate_up) + row(down) x{world}, fp32 all-reduce"}
+                {"M": t[0], "us": t[1] * 1e3, "launch": t[2], "partial_bytes": t[0] * HIDDEN * 4,
+                 "reduce": t[3],
+                 "parallelism": f"column(QKV,GDN-in,gate_up) + row(down) x{world}, fp32 partial sums"}
                 for t in tp]
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, note, _ = cpu_lm_head(m, 3, 1, budget_s=15.0,
@@ -816,6 +852,8 @@ def main():
     ap.add_argument("--vocab", type=int, default=VOCAB,
                     help="vocabulary rows (a smaller plane makes a small profiling case)")
     ap.add_argument("--eager", action="store_true", help="launch every step from the host")
+    ap.add_argument("--nccl-reduce", action="store_true",
+                    help="tensor-parallel slice: NCCL all-reduce + rounding kernel instead of the peer sum")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="N > 1: gather the pairs with NCCL instead of the fused peer exchange")
     ap.add_argument("--no-cpu", action="store_true")

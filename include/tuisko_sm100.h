@@ -220,6 +220,24 @@ TK100_API tk100_status tk100_nvfp4_gate_up_swiglu(tk100_ctx* ctx, tk100_stream s
                                         const uint8_t* weight_codes, const uint8_t* weight_scales,
                                         float weight_scale_divisor, uint16_t* output);
 
+/* Tensor-parallel layer: sum of every rank's fp32 partial output (tk100_nvfp4_down_partial),
+ * rounded to BF16 once, by one kernel per rank over NVLink peer memory instead of a collective
+ * library call plus tk100_f32_to_bf16.  peer_buffers[i] is the device address, valid on this
+ * rank, of rank i's exchange buffer (entry `rank` is this rank's own): tk100_peer_sum_bytes
+ * (capacity_values, world) bytes each, 256-byte aligned, zeroed once, the same capacity on every
+ * rank and in every call.  values % 8 == 0, values <= capacity_values.  Up to 16 384 values every
+ * rank receives the whole partials (one NVLink latency); beyond that rank d adds chunk d of all
+ * partials and sends the BF16 chunk to everyone.  The partials are added in rank order on every
+ * rank, so all ranks end with identical bits.  All ranks must call it the same number of
+ * times; a peer that does not arrive within 2 s sets TK100_DEVICE_WAIT_TIMEOUT.  Ranks are
+ * processes on different GPUs (the kernel waits for its peers).  No counterpart in the
+ * reference (single GPU). */
+TK100_API size_t tk100_peer_sum_bytes(size_t capacity_values, int world);
+TK100_API tk100_status tk100_peer_sum_bf16(tk100_ctx* ctx, tk100_stream stream, size_t values,
+                                           size_t capacity_values, int world, int rank,
+                                           const float* partial, const uint64_t* peer_buffers,
+                                           uint16_t* output);
+
 /* tk100_nvfp4_gate_up_swiglu that also leaves the NVFP4 form of its output (codes
  * [rows, intermediate/2], swizzled block scales, definition at tk100_nvfp4_quantize_activation
  * with output_global_divisor) for tk100_nvfp4_down(input == NULL).  Up to 32 rows the

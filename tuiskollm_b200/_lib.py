@@ -62,6 +62,9 @@ SIGNATURES = {
     "tk100_nvfp4_down_partial": (_i, [_vp, _vp, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, C.c_float,
                                       _vp]),
     "tk100_f32_to_bf16": (_i, [_vp, _vp, C.c_size_t, _vp, _vp]),
+    "tk100_peer_sum_bytes": (C.c_size_t, [C.c_size_t, _i]),
+    "tk100_peer_sum_bf16": (_i, [_vp, _vp, C.c_size_t, C.c_size_t, _i, _i, _vp,
+                                 C.POINTER(C.c_uint64), _vp]),
     "tk100_fp8_projection_static": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, C.c_char_p,
                                          C.c_size_t]),
 }

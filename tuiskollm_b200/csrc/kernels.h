@@ -117,6 +117,23 @@ struct ExchangePeers {
 cudaError_t launch_argmax_exchange(cudaStream_t stream, int rows, int world, int rank,
                                    unsigned long long* keys, const ExchangePeers& peers,
                                    unsigned int* step_counter, ArgmaxPair* out, uint32_t* status);
+// peer_reduce.cu: sum of the ranks' fp32 partials over peer memory, rounded to BF16 once.
+constexpr long long kPeerSumOneShotElems = 16384;  // up to here every rank receives whole partials
+struct PeerSumParams {
+  long long elems;        // values per rank, multiple of 8
+  long long chunk;        // two-shot: values of one rank's chunk (multiple of 8); world * chunk >= elems
+  int world, rank;
+  int one_shot;
+  const float* partial;   // this rank's [elems] fp32
+  uint16_t* output;       // this rank's [elems] BF16 sum
+  size_t result_offset;   // byte offsets inside every rank's exchange buffer
+  size_t flag_offset;
+  unsigned int* tickets;  // 3 zeroed counters of this rank
+  unsigned int* step_counter;
+  uint32_t* status;
+};
+cudaError_t launch_peer_sum(cudaStream_t stream, int ctas, const PeerSumParams& q,
+                            const ExchangePeers& peers);
 // [shards, rows] pairs -> [rows] pairs with the first-maximum rule.
 cudaError_t launch_argmax_merge(cudaStream_t stream, int rows, int shards,
                                 const ArgmaxPair* gathered, ArgmaxPair* out);

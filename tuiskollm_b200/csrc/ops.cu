@@ -136,6 +136,8 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
             cudaMalloc(&ctx->status_, sizeof(uint32_t)) == cudaSuccess &&
             cudaMalloc(&ctx->exchange_step_, sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->exchange_step_, 0, sizeof(unsigned int)) == cudaSuccess &&
+            cudaMalloc(&ctx->peer_sum_state_, 4 * sizeof(unsigned int)) == cudaSuccess &&
+            cudaMemset(ctx->peer_sum_state_, 0, 4 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->counters_, 0, ctx->counter_count_ * sizeof(unsigned int)) ==
                 cudaSuccess &&
             cudaMemset(ctx->status_, 0, sizeof(uint32_t)) == cudaSuccess &&
@@ -155,6 +157,7 @@ Context::~Context() {
   if (counters_) cudaFree(counters_);
   if (status_) cudaFree(status_);
   if (exchange_step_) cudaFree(exchange_step_);
+  if (peer_sum_state_) cudaFree(peer_sum_state_);
 }
 
 Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
@@ -895,6 +898,78 @@ tk100_status tk100_argmax_exchange(tk100_ctx* ctx, tk100_stream stream, int rows
                                     reinterpret_cast<tk100::ArgmaxPair*>(output),
                                     ctx->impl->status_word()),
       "launching the argmax exchange");
+}
+
+namespace {
+struct PeerSumLayout {
+  long long chunk;       // two-shot chunk for `capacity` values
+  size_t result_offset, flag_offset, bytes;
+};
+// Layout of a peer-sum exchange buffer sized for `capacity` values on `world` ranks.
+PeerSumLayout peer_sum_layout(long long capacity, int world) {
+  auto up = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
+  PeerSumLayout l{};
+  l.chunk = static_cast<long long>(up(static_cast<size_t>((capacity + world - 1) / world), 8));
+  const long long one_shot = capacity < tk100::kPeerSumOneShotElems ? capacity : tk100::kPeerSumOneShotElems;
+  const size_t slots_two = static_cast<size_t>(world) * l.chunk * sizeof(float);
+  const size_t slots_one = 2 * static_cast<size_t>(world) * one_shot * sizeof(float);
+  l.result_offset = up(slots_two > slots_one ? slots_two : slots_one, 256);
+  l.flag_offset = l.result_offset + up(2 * static_cast<size_t>(world) * l.chunk * sizeof(uint16_t), 256);
+  l.bytes = l.flag_offset + 256;
+  return l;
+}
+}  // namespace
+
+size_t tk100_peer_sum_bytes(size_t capacity_values, int world) {
+  if (world < 1 || world > tk100::kMaxExchangeRanks || capacity_values == 0) return 0;
+  return peer_sum_layout(static_cast<long long>(capacity_values), world).bytes;
+}
+
+tk100_status tk100_peer_sum_bf16(tk100_ctx* ctx, tk100_stream stream, size_t values,
+                                 size_t capacity_values, int world, int rank, const float* partial,
+                                 const uint64_t* peer_buffers, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (values == 0 || values % 8 != 0 || values > capacity_values || world < 1 ||
+      world > tk100::kMaxExchangeRanks || rank < 0 || rank >= world || !partial || !peer_buffers ||
+      !output || (reinterpret_cast<uintptr_t>(partial) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(output) & 7) != 0) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH,
+                           "[gpu.launch] peer sum: bad argument (values a multiple of 8 within the "
+                           "capacity, 1 <= world <= 8, 0 <= rank < world, aligned non-null planes)");
+  }
+  tk100::ExchangePeers peers{};
+  for (int i = 0; i < world; ++i) {
+    if (peer_buffers[i] == 0 || (peer_buffers[i] & 255) != 0) {
+      return ctx->impl->fail(TK100_ERR_LAUNCH,
+                             "[gpu.launch] peer sum: peer buffer is null or not 256-byte aligned");
+    }
+    peers.base[i] = reinterpret_cast<unsigned char*>(static_cast<uintptr_t>(peer_buffers[i]));
+  }
+  const PeerSumLayout l = peer_sum_layout(static_cast<long long>(capacity_values), world);
+  tk100::PeerSumParams q{};
+  q.elems = static_cast<long long>(values);
+  q.world = world;
+  q.rank = rank;
+  q.one_shot = q.elems <= tk100::kPeerSumOneShotElems ? 1 : 0;
+  // the chunk follows this call's size (a smaller sum still spreads over all ranks); it never
+  // exceeds the chunk the buffer was sized for
+  q.chunk = ((q.elems + world - 1) / world + 7) / 8 * 8;
+  q.partial = partial;
+  q.output = output;
+  q.result_offset = l.result_offset;
+  q.flag_offset = l.flag_offset;
+  q.step_counter = ctx->impl->peer_sum_state();
+  q.tickets = ctx->impl->peer_sum_state() + 1;
+  q.status = ctx->impl->status_word();
+  // all CTAs of the launch must be resident together (they wait for peers, never for each other)
+  const long long vec = q.elems / 4;
+  long long ctas = (vec + 256 * 4 - 1) / (256 * 4);
+  if (ctas > ctx->impl->sm_count()) ctas = ctx->impl->sm_count();
+  if (ctas < 1) ctas = 1;
+  ctx->impl->count_launch();
+  return ctx->impl->check(
+      tk100::launch_peer_sum(static_cast<cudaStream_t>(stream), static_cast<int>(ctas), q, peers),
+      "launching the peer sum");
 }
 
 tk100_status tk100_nvfp4_quantize_activation(tk100_ctx* ctx, tk100_stream stream, int rows,

@@ -48,6 +48,7 @@ class Context {
   size_t counter_count() const { return counter_count_; }
   uint32_t* status_word() const { return status_; }
   unsigned int* exchange_step() const { return exchange_step_; }
+  unsigned int* peer_sum_state() const { return peer_sum_state_; }
   int forced_splits() const { return forced_splits_; }
   int forced_block_tok() const { return forced_block_tok_; }
   void count_launch(int n = 1) { launches_ += static_cast<uint64_t>(n); }
@@ -63,6 +64,7 @@ class Context {
   size_t counter_count_ = 0;
   uint32_t* status_ = nullptr;
   unsigned int* exchange_step_ = nullptr;  // device step counter of the peer argmax exchange
+  unsigned int* peer_sum_state_ = nullptr;  // peer sum: [0] step counter, [1..3] phase tickets
   int forced_splits_ = 0;
   int forced_block_tok_ = 0;
   uint64_t launches_ = 0;

@@ -83,6 +83,29 @@ def alloc_exchange(rows: int, world: int, device, group=None):
     return buf, handle, addresses
 
 
+def alloc_peer_sum(capacity_values: int, world: int, device, group=None):
+    """Symmetric peer-mapped exchange buffer for :func:`tuiskollm_b200.ops.peer_sum_bf16`:
+    returns ``(buffer, handle, addresses)`` as :func:`alloc_exchange` does.  Collective."""
+    import torch.distributed._symmetric_memory as symm
+
+    from .ops import peer_sum_bytes
+
+    words = (peer_sum_bytes(capacity_values, world) + 7) // 8
+    buf = symm.empty(words, dtype=torch.int64, device=device)
+    buf.zero_()
+    torch.cuda.synchronize()
+    grp = group if group is not None else dist.group.WORLD
+    try:
+        handle = symm.rendezvous(buf, grp)
+    except TypeError:
+        handle = symm.rendezvous(buf, grp.group_name)
+    addresses = [int(a) for a in handle.buffer_ptrs]
+    if len(addresses) != world:
+        raise RuntimeError("symmetric memory returned %d peer addresses for %d ranks" % (len(addresses), world))
+    dist.barrier(group=group)
+    return buf, handle, addresses
+
+
 class ShardedLmHead:
     """One rank's part of the vocabulary-sharded LM head with fused greedy selection."""
 

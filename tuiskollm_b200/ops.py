@@ -274,6 +274,23 @@ def f32_to_bf16(context: Context, stream, count, input, output):
                                                  _ptr(input), _ptr(output)))
 
 
+def peer_sum_bytes(capacity_values: int, world: int) -> int:
+    """Size of one rank's exchange buffer for :func:`peer_sum_bf16` (tk100_peer_sum_bytes)."""
+    return int(_lib.load().tk100_peer_sum_bytes(capacity_values, world))
+
+
+def peer_sum_bf16(context: Context, stream, values, capacity_values, world, rank, partial,
+                  peer_buffers, output):
+    """BF16 sum over ranks of the fp32 ``partial`` (``values`` numbers, a multiple of 8) through
+    the ranks' peer-mapped exchange buffers (``peer_buffers[i]`` = rank i's buffer address in this
+    process, each ``peer_sum_bytes(capacity_values, world)`` bytes, zeroed once).  Every rank
+    calls it; all ranks get identical bits."""
+    arr = (C.c_uint64 * world)(*[int(b) for b in peer_buffers])
+    context.check(context._lib.tk100_peer_sum_bf16(context.handle, _stream(stream), values,
+                                                   capacity_values, world, rank, _ptr(partial), arr,
+                                                   _ptr(output)))
+
+
 def exchange_bytes(rows: int, world: int) -> int:
     """Size of one rank's peer exchange buffer (TK100_EXCHANGE_BYTES)."""
     return 2 * world * rows * 8 + 2 * world * 4
