@@ -378,11 +378,12 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     const char* pe = std::getenv("TK100_FP8_PAIR");
     const char* pm = std::getenv("TK100_FP8_PAIR_MIN_ROWS");
     const int min_rows = pm ? std::atoi(pm) : 256;
-    // a launch of fewer than 64 pair CTAs (a tensor-parallel shard of the plane) leaves most SMs
-    // idle: the one-CTA kernel splits K instead (TK100_FP8_PAIR=2 takes the pair route anyway)
+    // a launch of fewer than 32 pair CTAs (a small tensor-parallel shard of the plane) leaves
+    // most SMs idle: the one-CTA kernel splits K instead (TK100_FP8_PAIR=2 takes the pair route
+    // anyway).  Shards of 32-48 pair CTAs were measured faster on pairs than split.
     const long long pair_ctas = 2LL * ((rows + 255) / 256) * (out_rows / 256);
     if (!(pe && pe[0] == '0') && rows >= min_rows && out_rows % 256 == 0 &&
-        (pair_ctas >= 64 || (pe && pe[0] == '2')) && output &&
+        (pair_ctas >= 32 || (pe && pe[0] == '2')) && output &&
         !logits_f32 && !argmax_scratch && ctx_.forced_block_tok() == 0 && ctx_.forced_splits() == 0) {
       CUtensorMap map_w, map_a;
       TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(out_rows),
