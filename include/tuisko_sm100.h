@@ -181,14 +181,15 @@ TK100_API tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, i
  * reference is single-GPU and selects on the host).  Call tk100_fp8_lm_head with
  * pairs == NULL so that the packed per-shard maxima stay in argmax_scratch, then this: one
  * small kernel per rank unpacks them, stores the (max, index) pairs straight into every
- * peer's exchange buffer over NVLink, raises a step-numbered flag, waits (bounded, ~2 s, then
- * TK100_DEVICE_WAIT_TIMEOUT) for all peers' flags and merges with the first-maximum rule into
- * `output` [rows] -- identical on every rank.  No collective library call is involved.
+ * peer's exchange buffer over NVLink as 8-byte words tagged with the step number (no fence, no
+ * separate flag), waits (bounded, ~2 s, then TK100_DEVICE_WAIT_TIMEOUT) for all peers' words of
+ * the step and merges with the first-maximum rule into `output` [rows] -- identical on every
+ * rank.  No collective library call is involved.
  * peer_buffers: host array of `world` device addresses, entry i = rank i's exchange buffer as
  * mapped in THIS process (peer access enabled; e.g. torch symmetric memory), each
  * TK100_EXCHANGE_BYTES(rows, world) bytes, zero-filled once before the first call.  Every
  * rank must make the same sequence of calls (the kernels meet by step number). */
-#define TK100_EXCHANGE_BYTES(rows, world) (2u * (world) * (rows) * 8u + 2u * (world) * 4u)
+#define TK100_EXCHANGE_BYTES(rows, world) (2u * (world) * (rows) * 16u)
 TK100_API tk100_status tk100_argmax_exchange(tk100_ctx* ctx, tk100_stream stream, int rows, int world,
                                    int rank, uint64_t* argmax_scratch,
                                    const uint64_t* peer_buffers, tk100_argmax_pair* output);

@@ -445,84 +445,78 @@ __global__ void argmax_merge_kernel(int rows, int shards, const ArgmaxPair* gath
 }
 
 // Vocabulary-sharded greedy selection without a collective library call: one CTA per rank
-// unpacks its shard's (max, index) pairs, stores them straight into every peer's exchange
-// buffer over NVLink (plain peer stores), raises a per-sender flag carrying the step number,
-// waits -- bounded -- for the flags of all peers and merges with the first-maximum rule.
-// Buffer layout on every rank (same offsets everywhere): [2 parities][world][rows] pairs,
-// then [2 parities][world] 32-bit flags.  Steps alternate parity, so a fast rank's next step
-// never overwrites what a slow rank is still reading.
+// unpacks its shard's (max, index) pairs and stores them straight into every peer's exchange
+// buffer over NVLink (plain peer stores), then waits -- bounded -- for the pairs of all peers
+// in its own buffer and merges with the first-maximum rule.
+// Every pair travels as two 8-byte words that carry the step number in their upper half:
+// {step, value bits} and {step, index}.  An aligned 8-byte store is indivisible, so a word
+// whose tag equals the current step IS the sender's data of this step: no fence, no separate
+// flag and no second round trip (one NVLink write latency per exchange).
+// Buffer layout on every rank (same offsets everywhere): [2 parities][world][rows][2] words.
+// Steps alternate parity, and a rank can be at most one step ahead of its peers (finishing a
+// step needs every peer's words of that step), so a fast rank's next step never overwrites what
+// a slow rank is still waiting for.
 __global__ void __launch_bounds__(256)
     argmax_exchange_kernel(int rows, int world, int rank, unsigned long long* keys,
                            ExchangePeers peers, unsigned int* step_counter, ArgmaxPair* out,
                            uint32_t* status) {
   __shared__ unsigned int s_step;
-  __shared__ unsigned int s_ok;
   pdl_trigger();
   pdl_wait();
   if (threadIdx.x == 0) {
     s_step = *step_counter + 1u;
+    if (s_step == 0u) s_step = 1u;  // 0 is what a zero-filled buffer holds
     *step_counter = s_step;
-    s_ok = 1u;
   }
   __syncthreads();
   const unsigned int step = s_step;
-  const unsigned int parity = step & 1u;
-  const size_t pair_slots = static_cast<size_t>(world) * rows;
-  const size_t flag_base = 2 * pair_slots * sizeof(ArgmaxPair);
+  const unsigned long long tag = static_cast<unsigned long long>(step) << 32;
+  const size_t parity_words = 2 * static_cast<size_t>(world) * rows;
+  const size_t base = (step & 1u) * parity_words;
 
   for (int t = threadIdx.x; t < rows; t += blockDim.x) {
     const unsigned long long packed = keys[t];
     keys[t] = 0ull;
     const uint32_t key = static_cast<uint32_t>(packed >> 32);
-    ArgmaxPair mine;
-    mine.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
-    mine.index = packed == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(packed));
+    const uint32_t value_bits = key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu);
+    const uint32_t index = packed == 0ull ? 0xffffffffu : 0xffffffffu - static_cast<uint32_t>(packed);
     for (int pr = 0; pr < world; ++pr) {
-      ArgmaxPair* dst = reinterpret_cast<ArgmaxPair*>(peers.base[pr]) + parity * pair_slots +
-                        static_cast<size_t>(rank) * rows + t;
-      *reinterpret_cast<volatile unsigned long long*>(dst) =
-          *reinterpret_cast<const unsigned long long*>(&mine);
+      volatile unsigned long long* dst = reinterpret_cast<volatile unsigned long long*>(peers.base[pr]) +
+                                         base + 2 * (static_cast<size_t>(rank) * rows + t);
+      dst[0] = tag | value_bits;
+      dst[1] = tag | index;
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < world) {
-    unsigned int* flag = reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + flag_base) +
-                         parity * world + rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
-    // wait for the same step from sender `threadIdx.x` in this rank's own buffer
-    const unsigned int* mine_flag =
-        reinterpret_cast<const unsigned int*>(peers.base[rank] + flag_base) + parity * world +
-        threadIdx.x;
-    const uint64_t start = global_timer_ns();
-    unsigned int seen = 0;
-    for (;;) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine_flag) : "memory");
-      if (static_cast<int>(seen - step) >= 0) break;
-      if (global_timer_ns() - start > 2000000000ull) {
-        atomicOr(status, STATUS_WAIT_TIMEOUT);
-        s_ok = 0u;
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (!s_ok) return;
-  const ArgmaxPair* gathered =
-      reinterpret_cast<const ArgmaxPair*>(peers.base[rank]) + parity * pair_slots;
+  // every row: wait for each sender's two words of this step, merge as they are read
+  const volatile unsigned long long* mine =
+      reinterpret_cast<const volatile unsigned long long*>(peers.base[rank]) + base;
+  const uint64_t start = global_timer_ns();
   for (int t = threadIdx.x; t < rows; t += blockDim.x) {
     unsigned long long best = 0ull;
-    for (int sdr = 0; sdr < world; ++sdr) {
-      const unsigned long long raw = *reinterpret_cast<const volatile unsigned long long*>(
-          gathered + static_cast<size_t>(sdr) * rows + t);
-      const uint32_t vbits = static_cast<uint32_t>(raw);
-      const int32_t idx = static_cast<int32_t>(raw >> 32);
-      if (idx < 0) continue;
+    bool ok = true;
+    for (int sdr = 0; sdr < world && ok; ++sdr) {
+      const volatile unsigned long long* slot = mine + 2 * (static_cast<size_t>(sdr) * rows + t);
+      unsigned long long w0, w1;
+      for (;;) {
+        w0 = slot[0];
+        w1 = slot[1];
+        if ((w0 >> 32) == step && (w1 >> 32) == step) break;
+        if (global_timer_ns() - start > 2000000000ull) {
+          atomicOr(status, STATUS_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+      const uint32_t vbits = static_cast<uint32_t>(w0);
+      const uint32_t idx = static_cast<uint32_t>(w1);
+      if (idx == 0xffffffffu) continue;  // the sender had no candidate
       const unsigned long long packed =
           (static_cast<unsigned long long>(total_order_key(vbits)) << 32) |
-          static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(idx));
+          static_cast<unsigned long long>(0xffffffffu - idx);
       best = packed > best ? packed : best;
     }
+    if (!ok) continue;  // results are invalid; the status word says so
     const uint32_t key = static_cast<uint32_t>(best >> 32);
     ArgmaxPair o;
     o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));

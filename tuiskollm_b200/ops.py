@@ -293,7 +293,7 @@ def peer_sum_bf16(context: Context, stream, values, capacity_values, world, rank
 
 def exchange_bytes(rows: int, world: int) -> int:
     """Size of one rank's peer exchange buffer (TK100_EXCHANGE_BYTES)."""
-    return 2 * world * rows * 8 + 2 * world * 4
+    return 2 * world * rows * 16
 
 
 STATIC_MAX_ROWS = 256
