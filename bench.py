@@ -729,6 +729,9 @@ def run_native(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    # rank 0 alone just spent host time starting the sampler; the exchange kernels of the other
+    # ranks give a late peer 2 s, so the ranks meet again before the timed region
+    barrier()
     launches0 = ctx.launch_count
     ms = time_region(torch, run_step, args.steps)
     launches = (launches_per_step * args.steps if launches_per_step is not None
