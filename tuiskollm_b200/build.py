@@ -29,14 +29,31 @@ def is_stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles the library when it is absent or older than its sources.  Several processes may
+    call this at once (one rank per GPU): an exclusive file lock lets one of them compile, into a
+    temporary file that is renamed into place, and the others then find the library fresh."""
     if not force and not is_stale():
         return LIB
+    import fcntl
+
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale():  # another process built it while this one waited
+                return LIB
+            return _compile(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _compile(verbose: bool) -> str:
+    tmp = "%s.%d.tmp" % (LIB, os.getpid())
     cmd = [
         nvcc_path(), "-std=c++17", "-O3", "-lineinfo",
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
         "-Xptxas", "-v" if verbose else "-warn-spills",
-        "-o", LIB,
+        "-o", tmp,
     ] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a private gcc; nvcc wants the system one
@@ -46,7 +63,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
         raise RuntimeError("nvcc failed building libtuisko_sm100.so")
+    os.replace(tmp, LIB)  # atomic: a concurrent loader sees the old file or the new one, whole
     return LIB
 
 
