@@ -263,9 +263,65 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP ? 2 : 3) : (
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
         tmem_ld_wait();
+        if constexpr (BLOCK_TOK >= 32) {
+          // Many tokens per tile: the 16 tokens of a chunk go through scaling, rounding, stores
+          // and the warp maxima side by side (one dependent chain per token would leave the few
+          // epilogue warps waiting on latencies).  Same values, same order of comparisons.
+          uint32_t b[16];
+          float v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (c0 + j < valid_tok) emit(c0 + j, __uint_as_float(r[j]));
+          for (int j = 0; j < 16; ++j) {
+            v[j] = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), ctl->a_scale[c0 + j]), w_scale);
+            b[j] = f32_to_bf16_bits(v[j]);
+          }
+          if (row_ok) {
+            const size_t o0 = static_cast<size_t>(tok0 + c0) * p.out_rows + n;
+            if (p.out) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < valid_tok) p.out[o0 + static_cast<size_t>(j) * p.out_rows] = static_cast<uint16_t>(b[j]);
+              }
+            }
+            if (p.logits_f32) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < valid_tok) p.logits_f32[o0 + static_cast<size_t>(j) * p.out_rows] = v[j];
+              }
+            }
+          }
+          if (want_argmax) {
+            unsigned long long pk[16];
+            uint32_t nonfinite = 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const bool live = row_ok && c0 + j < valid_tok;
+              nonfinite |= (live && (b[j] & 0x7f80u) == 0x7f80u) ? 1u : 0u;
+              pk[j] = live ? ((static_cast<unsigned long long>(total_order_key(b[j] << 16)) << 32) |
+                              static_cast<unsigned long long>(0xffffffffu -
+                                                              static_cast<uint32_t>(p.vocab_offset + n)))
+                           : 0ull;
+            }
+            if (nonfinite) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, pk[j], o2);
+                pk[j] = other > pk[j] ? other : pk[j];
+              }
+            }
+            if (lane == 0) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < valid_tok) atomicMax(&ctl->red[c0 + j], pk[j]);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid_tok) emit(c0 + j, __uint_as_float(r[j]));
+          }
         }
       }
     } else if (clustered) {
