@@ -40,8 +40,7 @@ VOCAB = 248320
 SEED = 20260425
 # DRAM bytes (read + write) that ncu counted for one LM-head projection launch at vocab 248320,
 # M = 1, over that launch's algorithmic bytes (1 272 757 504 / 1 272 893 444): every weight byte
-# crosses HBM once.  The capture is summarised in
-# profiles/fp8_projection_kernel_lm_head_full_m1_traffic.md.
+# crosses HBM once (ncu: dram__bytes_read.sum + dram__bytes_write.sum of one captured launch).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1272757504 / 1272893444
 FALLBACK_HBM_GBS = 6650.0
 
