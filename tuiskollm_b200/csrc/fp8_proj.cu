@@ -36,8 +36,12 @@ constexpr int kMaxSplits = 8;     // upper bound of gridDim.z (the host never as
 
 // DEEP: a longer ring for launches that put at most two CTAs on an SM anyway (few tiles):
 // the same bytes in flight per SM with fewer CTAs.
-__host__ __device__ constexpr int stages_for(int block_tok, bool deep = false) {
-  if (deep) return block_tok <= 16 ? 6 : block_tok <= 32 ? 5 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
+// WIDE (ring 2, 16-token tiles only): a 3-stage ring so that four CTAs share an SM, for unsplit
+// launches whose tile count lies between three and four CTAs per SM (a 4-way LM-head shard:
+// 485 tiles) and would otherwise leave a short second wave.
+__host__ __device__ constexpr int stages_for(int block_tok, int ring = 0) {
+  if (ring == 2) return 3;
+  if (ring == 1) return block_tok <= 16 ? 6 : block_tok <= 32 ? 5 : block_tok <= 64 ? 4 : block_tok <= 128 ? 6 : 4;
   // <= 32 tokens: three CTAs share an SM (a third slot lets the next kernel's CTAs start their
   // weight prefetch under this kernel's tail); 64 and 128: two (one CTA's epilogue runs under
   // the other's main loop); 256: one.
@@ -46,8 +50,8 @@ __host__ __device__ constexpr int stages_for(int block_tok, bool deep = false) {
 
 template <int BLOCK_TOK>
 struct Control {
-  uint64_t full[stages_for(BLOCK_TOK, true)];
-  uint64_t empty[stages_for(BLOCK_TOK, true)];
+  uint64_t full[stages_for(BLOCK_TOK, 1)];
+  uint64_t empty[stages_for(BLOCK_TOK, 1)];
   uint64_t tmem_full;
   unsigned long long red[BLOCK_TOK];  // per-token argmax keys of this CTA
   float a_scale[BLOCK_TOK];
@@ -55,7 +59,7 @@ struct Control {
   uint32_t is_last;
 };
 
-template <int BLOCK_TOK, bool DEEP = false>
+template <int BLOCK_TOK, int DEEP = 0>
 __host__ __device__ constexpr size_t smem_bytes_for() {
   return 1024 /* alignment slack */ +
          static_cast<size_t>(stages_for(BLOCK_TOK, DEEP)) * (kWStageBytes + BLOCK_TOK * kTileKBytes) +
@@ -71,8 +75,9 @@ __device__ __forceinline__ uint32_t total_order_key(uint32_t bits) {
   return bits ^ ((bits & 0x80000000u) ? 0xffffffffu : 0x80000000u);
 }
 
-template <int BLOCK_TOK, bool DEEP>
-__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP ? 2 : 3) : (BLOCK_TOK <= 128 ? 2 : 1))
+template <int BLOCK_TOK, int DEEP>  // DEEP: 0 normal ring, 1 deep, 2 wide
+__global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (DEEP == 2 ? 4 : 3))
+                                                            : (BLOCK_TOK <= 128 ? 2 : 1))
     fp8_projection_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_a, const Fp8ProjParams p) {
   constexpr int STAGES = stages_for(BLOCK_TOK, DEEP);
@@ -587,25 +592,34 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& tmap_w, const CUt
   dim3 grid((p.out_rows + kTileRows - 1) / kTileRows, (p.rows + BLOCK_TOK - 1) / BLOCK_TOK,
             p.splits);
   const unsigned int cluster_z = (p.cluster && p.splits > 1) ? static_cast<unsigned int>(p.splits) : 1u;
-  if (BLOCK_TOK <= 32 && p.deep_ring) {
-    return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, true>, grid, dim3(kThreads),
-                                 smem_bytes_for<BLOCK_TOK, true>(), stream, dim3(1, 1, cluster_z), tmap_w,
+  if (BLOCK_TOK <= 32 && p.deep_ring == 1) {
+    return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, 1>, grid, dim3(kThreads),
+                                 smem_bytes_for<BLOCK_TOK, 1>(), stream, dim3(1, 1, cluster_z), tmap_w,
                                  tmap_a, p);
   }
-  return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, false>, grid, dim3(kThreads),
-                               smem_bytes_for<BLOCK_TOK, false>(), stream, dim3(1, 1, cluster_z), tmap_w, tmap_a,
+  if (BLOCK_TOK <= 16 && p.deep_ring == 2) {
+    constexpr int BT = BLOCK_TOK <= 16 ? BLOCK_TOK : 16;  // only the 16-token tile has this variant
+    return launch_kernel_cluster(fp8_projection_kernel<BT, 2>, grid, dim3(kThreads),
+                                 smem_bytes_for<BT, 2>(), stream, dim3(1, 1, cluster_z), tmap_w, tmap_a, p);
+  }
+  return launch_kernel_cluster(fp8_projection_kernel<BLOCK_TOK, 0>, grid, dim3(kThreads),
+                               smem_bytes_for<BLOCK_TOK, 0>(), stream, dim3(1, 1, cluster_z), tmap_w, tmap_a,
                                p);
 }
 
 template <int BLOCK_TOK>
 cudaError_t prepare_one() {
-  cudaError_t e = cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK, false>,
+  cudaError_t e = cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK, 0>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem_bytes_for<BLOCK_TOK, false>()));
+                                       static_cast<int>(smem_bytes_for<BLOCK_TOK, 0>()));
   if (e != cudaSuccess || BLOCK_TOK > 32) return e;
-  return cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK, true>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(smem_bytes_for<BLOCK_TOK, true>()));
+  e = cudaFuncSetAttribute(fp8_projection_kernel<BLOCK_TOK, 1>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem_bytes_for<BLOCK_TOK, 1>()));
+  if (e != cudaSuccess || BLOCK_TOK > 16) return e;
+  constexpr int BT = BLOCK_TOK <= 16 ? BLOCK_TOK : 16;
+  return cudaFuncSetAttribute(fp8_projection_kernel<BT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(smem_bytes_for<BT, 2>()));
 }
 
 }  // namespace

@@ -72,7 +72,8 @@ struct Fp8ProjParams {
   int out_rows;   // weight rows N (this shard)
   int k;          // reduction length, multiple of 128
   int splits;     // K splits (grid.z)
-  int deep_ring;  // 1: longer ring, two CTAs per SM (launches with few CTAs)
+  int deep_ring;  // 1: longer ring, two CTAs per SM (launches with few CTAs); 2: 3-stage ring, four
+                  // CTAs per SM (16-token tiles, tile counts between 3 and 4 per SM)
   int l2_prefetch;  // > 0: before waiting for the predecessor, ask L2 for up to this many weight
                     // k-blocks beyond the ring (short weight streams that fit L2)
   int cluster;    // 1: the splits of a tile form a thread-block cluster and reduce over

@@ -457,7 +457,13 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     const char* dr = std::getenv("TK100_DEEP_RING");
     // unsplit launches with at most two CTAs per SM (an LM-head shard on 8 GPUs): measured
     // 26 us instead of 32 us for a 31 040-row shard; split launches are faster with three
-    p.deep_ring = dr ? (dr[0] != '0') : (splits == 1 && tiles <= 2LL * ctx_.sm_count());
+    p.deep_ring = dr ? (dr[0] - '0') : (splits == 1 && tiles <= 2LL * ctx_.sm_count());
+    // between three and four CTAs per SM worth of tiles: the 3-stage ring, four CTAs per SM, one
+    // wave (a 4-way LM-head shard: 485 tiles on 148 SMs)
+    if (!dr && splits == 1 && block_tok == 16 && tiles > 3LL * ctx_.sm_count() &&
+        tiles <= 4LL * ctx_.sm_count()) {
+      p.deep_ring = 2;
+    }
   }
   {
     // Queueing the CTA's weight slice at L2 before the ring starts looked good only while the
