@@ -1,21 +1,27 @@
 #!/usr/bin/env python
 """Benchmark of the quantized projection hot path on B200.
 
-Workload (all N): the FP8 LM head with fused greedy argmax of the third benchmark
+Headline workload (all N): the FP8 LM head with fused greedy argmax of the third benchmark
 configuration -- K = 5120, vocabulary 248320, M decode tokens (default 1), E4M3 weights
 ~N(0, 0.02) with one BF16 scale per row, BF16 hidden ~N(0, 1), fp32 logits + int32 argmax
 out -- the largest single-GPU configuration of the path and the one that shards: the
 vocabulary is split contiguously over the N ranks, every rank streams its shard once per
-step and the per-shard (max, index) pairs are gathered with NCCL and merged.
+step and the per-shard (max, index) pairs are exchanged over NVLink and merged.
 
 One step = quantise the hidden rows + stream the weight shard through the tcgen05
-projection kernel + argmax finalize (+ all-gather + merge when N > 1).
+projection kernel + argmax finalize (N = 1) or the fused peer exchange + merge (N > 1).
 
-  value   whole-job algorithmic GB/s with the hidden rows resident in HBM
-  e2e     the same through the public operator call with HOST buffers: pinned-host ->
-          device copy of the hidden rows and device -> host read of the argmax pairs
-          inside the timed region, one stream synchronisation per step
+  value     whole-job algorithmic GB/s with the hidden rows resident in HBM, from EXACTLY
+            `--steps` graph replays between two barriers (max over ranks)
+  protocol  the same step timed the way the reference times its operators
+            (qual/src/device_benchmark.rs:993-1101): 40 samples, median / p10 / p90
+  e2e       the same through the public operator call with HOST buffers: pinned-host ->
+            device copy of the hidden rows and device -> host read of the argmax pairs
+            inside the timed region, one stream synchronisation per step (graph replay, and
+            `e2e.eager` with every operator call made from the host)
   roofline  the projection kernel alone against the measured HBM copy bandwidth
+  configs   (N = 1) every other benchmark configuration as its own measured row with its
+            roofline and the CPU oracle beside it
 
 `--impl reference` times the CPU restatement of the reference's qualification oracle for
 the same workload on the host cores (the reference is Rust + cuda-oxide for sm_120 and can
@@ -38,11 +44,15 @@ sys.path.insert(0, ROOT)
 HIDDEN = 5120
 VOCAB = 248320
 SEED = 20260425
+SAMPLES = 40  # qual/src/device_benchmark.rs: 40 samples per case
 # DRAM bytes (read + write) that ncu counted for one LM-head projection launch at vocab 248320,
 # M = 1, over that launch's algorithmic bytes (1 272 757 504 / 1 272 893 444): every weight byte
 # crosses HBM once (ncu: dram__bytes_read.sum + dram__bytes_write.sum of one captured launch).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1272757504 / 1272893444
 FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_FP4_TFLOPS = 9000.0
 
 
 def algorithmic_bytes(rows: int, out_rows: int, k: int, out_bytes: int) -> int:
@@ -59,8 +69,34 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def workload_config(rows: int, vocab: int, world: int) -> dict:
+    """The `config` object: the same keys and values in the GPU arm and the reference arm."""
+    return {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={vocab} M={rows}",
+            "rows": rows, "vocab": vocab, "hidden": HIDDEN,
+            "parallelism": f"vocab-shard x{world}",
+            "l2": "weight shard (%.0f MB) larger than L2, streamed once per step"
+                  % (vocab // world * HIDDEN / 1e6)}
+
+
 class ClockSampler:
-    """Polls nvidia-smi for SM clocks and throttle reasons while the timed region runs."""
+    """Polls nvidia-smi for SM clocks and throttle reasons from before the warm-up until the
+    last timed region ends (the GPU is under load for the whole span)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -90,7 +126,15 @@ class ClockSampler:
             if len(parts) >= 6:
                 self.samples.append(parts)
 
-    def stop(self):
+    def wait_for_first_sample(self, limit_s: float = 3.0):
+        t0 = time.time()
+        while self.proc is not None and not self.samples and time.time() - t0 < limit_s:
+            time.sleep(0.01)
+
+    def mark(self) -> int:
+        return len(self.samples)
+
+    def stop(self, first: int = 0):
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -98,7 +142,7 @@ class ClockSampler:
             except Exception:
                 self.proc.kill()
         sm, mx, reasons = [], 0.0, set()
-        for p in self.samples:
+        for p in self.samples[first:]:
             try:
                 sm.append(float(p[0]))
                 mx = max(mx, float(p[1]))
@@ -114,16 +158,25 @@ class ClockSampler:
 
 # ----------------------------------------------------------------- CPU arm
 
+def cpu_threads_all() -> int:
+    """Gives the oracle's OpenMP loops every online core, whatever OMP_NUM_THREADS a launcher
+    exported to its ranks (torch.distributed.run sets it to 1)."""
+    from oracle import tuisko_oracle as O
+
+    O.lib()
+    return O.set_num_threads(host_cores())
+
+
 def cpu_lm_head(rows: int, steps: int, warmup: int, budget_s: float, sample_rows: int = 0):
     """Times the oracle's LM-head formula (quantise + f64 FP8 dot + greedy pick) on a
     bounded sample of vocabulary rows sized so that all steps take about `budget_s` seconds;
-    returns (GB/s, seconds/step, threads, note)."""
+    returns (GB/s, seconds/step, threads, note, sampled rows)."""
     import numpy as np
 
     from oracle import tuisko_oracle as O
     from tuiskollm_b200 import synth
 
-    O.lib()
+    threads = cpu_threads_all()
     x = synth.normal_bf16(SEED, 2, (rows, HIDDEN))
 
     def make_step(wc, ws):
@@ -153,7 +206,113 @@ def cpu_lm_head(rows: int, steps: int, warmup: int, budget_s: float, sample_rows
     nbytes = algorithmic_bytes(rows, sample_rows, HIDDEN, 4)
     note = (f"{sample_rows} of {VOCAB} vocabulary rows x {HIDDEN}, M={rows}: per-token E4M3 "
             f"quantise, f64 dot of decoded codes, greedy pick; OpenMP over rows")
-    return nbytes / dt / 1e9, dt, O.num_threads(), note, sample_rows
+    return nbytes / dt / 1e9, dt, threads, note, sample_rows
+
+
+def cpu_time(fn, budget_s: float = 1.0) -> float:
+    """Seconds per call of fn: one warm-up call, then repeats for about `budget_s`."""
+    fn()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        fn()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or n >= 50:
+            return dt / n
+
+
+_CPU_PLANES = {}
+
+
+def cpu_fp8_plane(k: int):
+    """One 8192-row E4M3 plane per reduction length, drawn once and sliced by the CPU rows."""
+    import numpy as np
+    import torch
+
+    from tuiskollm_b200 import synth
+
+    if k not in _CPU_PLANES:
+        if torch.cuda.is_available():  # same recipe, drawn on the device and copied back: seconds faster
+            c, sc = synth.torch_fp8_weights(SEED, 3, 8192, k, "cuda")
+            _CPU_PLANES[k] = (c.cpu().numpy(), sc.view(torch.int16).cpu().numpy().view(np.uint16))
+        else:
+            _CPU_PLANES[k] = synth.fp8_weights(SEED, 3, 8192, k)
+    return _CPU_PLANES[k]
+
+
+def cpu_fp8_projection(rows: int, out_rows: int, k: int, gpu_us: float, out_bytes: int = 2):
+    """Oracle port of one FP8 projection on a bounded sample of the weight rows (all tokens),
+    extrapolated linearly in the row count."""
+    from oracle import tuisko_oracle as O
+    from tuiskollm_b200 import synth
+
+    threads = cpu_threads_all()
+    sample = min(out_rows, 8192, max(256, int(4.0e8 / (rows * k)) // 128 * 128))
+    x = synth.normal_bf16(SEED, 2, (rows, k))
+    wc, ws = cpu_fp8_plane(k)
+    wc, ws = wc[:sample], ws[:sample]
+    codes, scales = O.quantize_e4m3(x)
+    dt = cpu_time(lambda: O.fp8_projection(codes, scales, wc, ws), 0.6) * out_rows / sample
+    b = algorithmic_bytes(rows, out_rows, k, out_bytes)
+    return {"value": b / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "us_full_shape": dt * 1e6, "gpu_speedup": dt * 1e6 / gpu_us,
+            "sample": f"{sample} of {out_rows} weight rows x {k}, M={rows}, f64 dot of decoded "
+                      f"codes" + ("" if sample == out_rows else "; extrapolated to the full plane")}
+
+
+def cpu_norm_quant(rows: int, gpu_us: float):
+    from oracle import tuisko_oracle as O
+    from tuiskollm_b200 import synth
+
+    threads = cpu_threads_all()
+    sample = min(rows, 64)
+    x = synth.normal_bf16(SEED, 90, (sample, HIDDEN))
+    b = synth.normal_bf16(SEED, 190, (sample, HIDDEN))
+    w = synth.normal_bf16(SEED, 5, (HIDDEN,), std=0.1)
+
+    def fn():
+        _res, nrm = O.residual_rms_norm(x, b, w, 1e-6)
+        O.quantize_e4m3(nrm)
+
+    dt = cpu_time(fn, 0.4) * rows / sample
+    nbytes = 11 * rows * HIDDEN + 4 * rows
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "us_full_shape": dt * 1e6, "gpu_speedup": dt * 1e6 / gpu_us,
+            "sample": f"{sample} of {rows} rows x {HIDDEN}: residual add, f64 RMSNorm, E4M3 quantise"
+                      + ("" if sample == rows else "; extrapolated")}
+
+
+def cpu_nvfp4(rows: int, out_rows: int, k: int, gate_up: bool, gpu_us: float):
+    """Oracle port of one NVFP4 projection on a stratified sample (64 tokens x 512 weight rows),
+    reported per output element and extrapolated to the full shape, labelled as such."""
+    from oracle import tuisko_oracle as O
+    from tuiskollm_b200 import synth
+
+    threads = cpu_threads_all()
+    st, sr = min(rows, 64), min(out_rows, 512)
+    n_w = sr * (2 if gate_up else 1)
+    x = synth.normal_bf16(SEED, 310, (st, k))
+    if ("nvfp4", n_w, k) not in _CPU_PLANES:
+        _CPU_PLANES[("nvfp4", n_w, k)] = synth.nvfp4_weights(SEED, 320, n_w, k)
+    wc, ws, wd = _CPU_PLANES[("nvfp4", n_w, k)]
+    a_div = 448.0
+    oc, osc = O.nvfp4_quantize(x, a_div)
+
+    def fn():
+        d = O.nvfp4_w4a4_dot(oc, osc, a_div, wc, ws, float(wd))
+        if gate_up:
+            O.silu_mul(d[:, :sr], d[:, sr:])
+
+    dt_sample = cpu_time(fn, 0.6)
+    per_elem = dt_sample / (st * sr)
+    dt = per_elem * rows * out_rows
+    flops = 2.0 * rows * out_rows * k * (2 if gate_up else 1)
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "us_per_output_element": per_elem * 1e6, "us_full_shape": dt * 1e6,
+            "gpu_speedup": dt * 1e6 / gpu_us,
+            "sample": f"{st} tokens x {sr} outputs of {rows} x {out_rows}, K={k}: integer dot of "
+                      f"E2M1 codes per 16-block, f64 scale product; extrapolated to the full shape"}
 
 
 def run_reference(args):
@@ -167,10 +326,9 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3",
         "data": "synthetic",
-        "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={VOCAB} M={args.rows}",
-                   "rows": args.rows, "sampled_vocab_rows": sample},
+        "config": workload_config(args.rows, args.vocab, args.gpus),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": note},
+                         "sample": note, "sampled_vocab_rows": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -210,118 +368,89 @@ def capture(torch, fn, reps=1):
     return graph
 
 
-def extra_rows(torch, tk, ctx, peak_gbs):
-    """Other configurations of the path on one GPU: decode projections with the weight plane
-    rotated over several copies so that every launch streams from HBM, not from L2."""
-    import numpy as np
-
-    from tuiskollm_b200 import synth
-
-    out = []
-    dev = "cuda"
-    for name, n_rows in (("fp8_qkv", synth.QKV_ROWS), ("fp8_gdn_input", synth.GDN_ROWS),
-                         ("fp8_qkv_refN", synth.QKV_ROWS_REF),
-                         ("fp8_gdn_input_refN", synth.GDN_ROWS_REF)):
-        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)
-        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, dev) for c in range(copies)]
-        for m in (1, 8, 32):
-            if name.endswith("refN") and m != 1:
-                continue
-            x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), dev)
-            codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
-            scales = torch.empty((m,), dtype=torch.float32, device=dev)
-            outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device=dev)
-            op = tk.GdnInputProjectionOp(ctx, n_rows)
-            op.launch(None, m, x, codes, scales, planes[0][0], planes[0][1], outp)
-            state = {"i": 0}
-
-            def proj():
-                w, s = planes[state["i"] % copies]
-                state["i"] += 1
-                op.launch(None, m, None, codes, scales, w, s, outp)
-
-            state["i"] = 0
-            graph = capture(torch, proj, copies)  # one launch per weight copy, in rotation
-            for _ in range(3):
-                graph.replay()
-            reps = 20
-            ms = time_region(torch, graph.replay, reps) / (reps * copies)
-            b = algorithmic_bytes(m, n_rows, HIDDEN, 2)
-            out.append({"op": name, "M": m, "N": n_rows, "us": ms * 1e3, "GB/s": b / ms / 1e6,
-                        "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs,
-                        "frac_of_8TBs": b / ms / 1e6 / 8000.0, "weight_copies": copies})
-        del planes
-    # prefill-shaped FP8 projections (tensor-bound): one weight plane, graph of 8 launches
-    burst, _sustained, tkind = measured_tensor_peaks()
-    for name, n_rows in (("fp8_qkv", synth.QKV_ROWS), ("fp8_gdn_input", synth.GDN_ROWS)):
-        w, s = synth.torch_fp8_weights(SEED, 60, n_rows, HIDDEN, dev)
-        for m in (256, 512, 2048):
-            x = synth.torch_normal_bf16(SEED, 8, (m, HIDDEN), dev)
-            codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
-            scales = torch.empty((m,), dtype=torch.float32, device=dev)
-            outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device=dev)
-            op = tk.GdnInputProjectionOp(ctx, n_rows)
-            op.launch(None, m, x, codes, scales, w, s, outp)
-            graph = capture(torch, lambda: op.launch(None, m, None, codes, scales, w, s, outp), 8)
-            for _ in range(3):
-                graph.replay()
-            ms = time_region(torch, graph.replay, 10) / 80
-            tf = 2.0 * m * n_rows * HIDDEN / ms / 1e9
-            out.append({"op": name, "M": m, "N": n_rows, "us": ms * 1e3, "TFLOPs": tf,
-                        "frac_of_4.5PF": tf / 4500.0, "frac_of_2x_measured_bf16": tf / (2 * burst),
-                        "tensor_peak_kind": tkind})
-        del w, s
-    # fused residual + RMSNorm + quantise
-    normop = tk.ResidualNormOp(ctx)
-    for m in (1, 256, 512):
-        copies = 1 if m == 1 else max(2, int(2 * 126e6 / (m * HIDDEN * 11)) + 1)
-        xs = [synth.torch_normal_bf16(SEED, 90 + c, (m, HIDDEN), dev) for c in range(copies)]
-        bs = [synth.torch_normal_bf16(SEED, 190 + c, (m, HIDDEN), dev) for c in range(copies)]
-        w = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)
-        res = [torch.empty_like(xs[0]) for _ in range(copies)]
-        nrm = [torch.empty_like(xs[0]) for _ in range(copies)]
-        codes = [torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev) for _ in range(copies)]
-        scales = torch.empty((m,), dtype=torch.float32, device=dev)
-        state = {"i": 0}
-
-        def norm():
-            i = state["i"] % copies
-            state["i"] += 1
-            normop.launch_quantize(None, m, xs[i], bs[i], w, res[i], nrm[i], codes[i], scales)
-
-        state["i"] = 0
-        graph = capture(torch, norm, copies * 4)
-        for _ in range(3):
-            graph.replay()
-        reps = 20
-        ms = time_region(torch, graph.replay, reps) / (reps * copies * 4)
-        b = 10 * m * HIDDEN + m * HIDDEN + 4 * m
-        out.append({"op": "residual_rmsnorm_quant_e4m3", "M": m, "us": ms * 1e3,
-                    "GB/s": b / ms / 1e6, "frac_of_measured_hbm": b / ms / 1e6 / peak_gbs})
-    out.extend(nvfp4_rows(torch, tk, ctx))
-    out.extend(layer_slice_rows(torch, tk, ctx))
-    return out
+def percentile(sorted_values, q):
+    if not sorted_values:
+        return None
+    i = min(len(sorted_values) - 1, max(0, int(round(q * (len(sorted_values) - 1)))))
+    return sorted_values[i]
 
 
-def measured_tensor_peaks():
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            d = json.load(f)
-        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
-    except Exception:
-        return 1590.0, 1400.0, "fallback"
+class Protocol:
+    """The reference's measurement loop (qual/src/device_benchmark.rs:993-1101, order
+    :1228-1239): every case is a CUDA graph of `ops` operations; each of the 40 samples times
+    every case once with CUDA events, visiting the cases in an order that reverses on odd samples
+    and rotates by the sample number; a case reports median / p10 / p90 microseconds per
+    operation."""
+
+    def __init__(self, torch):
+        self.torch = torch
+        self.cases = []  # (name, replay, ops, replays per sample)
+
+    def add(self, name, replay, ops, inner=1):
+        self.cases.append((name, replay, ops, inner))
+
+    @staticmethod
+    def order(sample, count):
+        order = list(range(count))
+        if sample % 2 == 1:
+            order.reverse()
+        r = sample % count
+        return order[r:] + order[:r]
+
+    def run(self, samples=SAMPLES, warmup=3):
+        torch = self.torch
+        times = {name: [] for name, *_ in self.cases}
+        for _name, replay, _ops, inner in self.cases:
+            for _ in range(warmup):
+                replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for s in range(samples):
+            for i in self.order(s, len(self.cases)):
+                name, replay, ops, inner = self.cases[i]
+                start.record()
+                for _ in range(inner):
+                    replay()
+                stop.record()
+                stop.synchronize()
+                times[name].append(start.elapsed_time(stop) * 1e3 / (ops * inner))
+        out = {}
+        for name, v in times.items():
+            v.sort()
+            out[name] = {"median": statistics.median(v), "p10": percentile(v, 0.1),
+                         "p90": percentile(v, 0.9), "samples": len(v)}
+        return out
+
+
+def hbm_roofline(kernel, nbytes, us, peak, peak_kind):
+    gbs = nbytes / us / 1e3
+    return {"bound": "hbm", "kernel": kernel, "algorithmic_bytes": int(nbytes), "us": us,
+            "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+            "peak_kind": peak_kind, "frac_of_8TBs": gbs / NOMINAL_HBM_GBS}
+
+
+def tensor_roofline(kernel, flops, nbytes, us, nominal_tflops, proxy_factor, hbm_peak):
+    burst, sustained, kind = measured_tensor_peaks()
+    tf = flops / us / 1e6
+    proxy = proxy_factor * burst
+    # near the ridge the bound is the slower of the byte stream and the flops
+    bound_us = max(nbytes / hbm_peak / 1e3, flops / (proxy * 1e6))
+    return {"bound": "tensor", "kernel": kernel, "algorithmic_flops": flops,
+            "algorithmic_bytes": int(nbytes), "us": us, "achieved": tf, "peak": proxy,
+            "unit": "TFLOP/s", "frac": tf / proxy,
+            "peak_kind": f"{proxy_factor} x {kind} bf16 burst ({burst:.0f} TFLOP/s)",
+            "frac_of_nominal": tf / nominal_tflops, "nominal_tflops": nominal_tflops,
+            "frac_of_sustained_proxy": tf / (proxy_factor * sustained),
+            "bound_us_max_of_bytes_and_flops": bound_us, "frac_of_bound": bound_us / us}
 
 
 class MlpPlanes:
-    """Synthetic NVFP4 MLP weights + activation planes for `m` tokens."""
+    """Synthetic NVFP4 MLP weights (shared between token counts) + activation planes."""
 
-    def __init__(self, torch, ops, synth, m, dev="cuda"):
+    def __init__(self, torch, ops, synth, m, weights, dev="cuda"):
         inter = synth.INTERMEDIATE
         self.m = m
-        self.gu_codes, self.gu_scales, self.gu_div = synth.torch_nvfp4_weights(
-            SEED, 300, 2 * inter, HIDDEN, dev)
-        self.dn_codes, self.dn_scales, self.dn_div = synth.torch_nvfp4_weights(
-            SEED, 301, HIDDEN, inter, dev)
+        (self.gu_codes, self.gu_scales, self.gu_div), (self.dn_codes, self.dn_scales, self.dn_div) = weights
         self.a_codes = torch.empty((m, HIDDEN // 2), dtype=torch.uint8, device=dev)
         self.a_scales = torch.zeros((ops.nvfp4_scale_plane_bytes(m, HIDDEN),), dtype=torch.uint8,
                                     device=dev)
@@ -336,111 +465,264 @@ class MlpPlanes:
         self.m_div = 448.0 * 6.0 / 8.0
 
 
-def nvfp4_rows(torch, tk, ctx, row_counts=(2048, 256, 32, 8, 1)):
-    """NVFP4 MLP (configuration 4 at M = 2048, and decode shapes): each kernel as graph
-    replays; prefill in TFLOP/s against the block-scaled FP4 peak, decode in GB/s."""
-    from tuiskollm_b200 import ops, synth
+def mlp_weights(synth):
+    inter = synth.INTERMEDIATE
+    return (synth.torch_nvfp4_weights(SEED, 300, 2 * inter, HIDDEN, "cuda"),
+            synth.torch_nvfp4_weights(SEED, 301, HIDDEN, inter, "cuda"))
+
+
+def w4a4_vs_a16(torch, pl, x):
+    """How far the W4A4 result lies from the reference's A16 definition
+    (tuisko-kernels-sm89/src/nvfp4/swiglu.rs:166-320: BF16 activations times decoded NVFP4
+    weights) on the benchmark's own inputs: max and mean relative deviation of sampled tiles of
+    the gate_up + SwiGLU output and of the down output (its input being the BF16 intermediate the
+    device wrote).  A reported fact, not a gate."""
+    import numpy as np
+
+    from oracle import tuisko_oracle as O
+    from tuiskollm_b200 import synth
 
     inter = synth.INTERMEDIATE
-    burst, sustained, kind = measured_tensor_peaks()
-    hbm, _ = measured_peak()
-    out = []
-    for m in row_counts:
-        pl = MlpPlanes(torch, ops, synth, m)
-        x = synth.torch_normal_bf16(SEED, 310, (m, HIDDEN), "cuda")
-        gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
+    host16 = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+    tok = slice(0, 64)
+    xs = host16(x[tok])
+    out = {}
+    g_w = HIDDEN // 16
+    devs = []
+    sc_all = pl.gu_scales.cpu().numpy()
+    tile = lambda t: sc_all[t * 128 * g_w:(t + 1) * 128 * g_w]
+    for wt in (0, 77):
+        rows_g = slice(wt * 128, (wt + 1) * 128)
+        rows_u = slice(inter + wt * 128, inter + (wt + 1) * 128)
+        wc = np.concatenate([pl.gu_codes[rows_g].cpu().numpy(), pl.gu_codes[rows_u].cpu().numpy()])
+        ws = np.concatenate([tile(wt), tile(inter // 128 + wt)])
+        dots = O.nvfp4_a16_dot(xs, wc, ws, float(pl.gu_div))
+        exp = O.silu_mul(dots[:, :128], dots[:, 128:])
+        got = O.bf16_to_f32(host16(pl.mid[tok])[:, rows_g]).astype(np.float64)
+        devs.append(np.abs(got - exp) / np.maximum(np.abs(exp), 4 * np.abs(exp).mean()))
+    d = np.concatenate([v.reshape(-1) for v in devs])
+    out["gate_up_swiglu"] = {"max_rel": float(d.max()), "mean_rel": float(d.mean()),
+                             "sample": "64 tokens x 2 tiles of 128 outputs"}
+    mids = host16(pl.mid[tok])
+    g_d = inter // 16
+    dsc = pl.dn_scales.cpu().numpy()
+    devs = []
+    for wt in (0, 31):
+        rows_w = slice(wt * 128, (wt + 1) * 128)
+        wc = pl.dn_codes[rows_w].cpu().numpy()
+        ws = dsc[wt * 128 * g_d:(wt + 1) * 128 * g_d]
+        exp = O.nvfp4_a16_dot(mids, wc, ws, float(pl.dn_div))
+        got = O.bf16_to_f32(host16(pl.out[tok])[:, rows_w]).astype(np.float64)
+        devs.append(np.abs(got - exp) / np.maximum(np.abs(exp), 4 * np.abs(exp).mean()))
+    d = np.concatenate([v.reshape(-1) for v in devs])
+    out["down"] = {"max_rel": float(d.max()), "mean_rel": float(d.mean()),
+                   "sample": "64 tokens x 2 tiles of 128 outputs"}
+    out["definition"] = ("|w4a4 - a16| / max(|a16|, 4 x mean|a16|); a16 = the reference's BF16-"
+                         "activation product in f64 on the same inputs")
+    return out
 
-        def quant_in():
+
+def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
+    """Configurations 1, 2, 4 and 5 (and the other LM-head token counts of 3) on one GPU, each
+    operator as a graph of several launches timed with the 40-sample protocol.  Decode planes
+    rotate over enough weight copies (> 3 x L2) that every launch streams from HBM."""
+    from tuiskollm_b200 import ops, synth
+
+    dev = "cuda"
+    proto = Protocol(torch)
+    meta = {}   # case name -> dict(describing the row)
+    keep = []   # tensors that must outlive the graphs
+    inter = synth.INTERMEDIATE
+
+    # ---- configurations 1 and 2: FP8 decode projections, weights rotated over > 3 x L2
+    for name, n_rows, cfg in (("fp8_qkv", synth.QKV_ROWS, 1), ("fp8_gdn_input", synth.GDN_ROWS, 2),
+                              ("fp8_qkv_refN", synth.QKV_ROWS_REF, 1),
+                              ("fp8_gdn_input_refN", synth.GDN_ROWS_REF, 2)):
+        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)
+        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, dev) for c in range(copies)]
+        keep.append(planes)
+        for m in (1, 8, 32):
+            if name.endswith("refN") and m != 1:
+                continue
+            x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), dev)
+            codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+            scales = torch.empty((m,), dtype=torch.float32, device=dev)
+            outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device=dev)
+            op = tk.GdnInputProjectionOp(ctx, n_rows)
+            op.launch(None, m, x, codes, scales, planes[0][0], planes[0][1], outp)
+            state = {"i": 0}
+
+            def proj(op=op, m=m, codes=codes, scales=scales, outp=outp, planes=planes, state=state,
+                     copies=copies):
+                w, s = planes[state["i"] % copies]
+                state["i"] += 1
+                op.launch(None, m, None, codes, scales, w, s, outp)
+
+            graph = capture(torch, proj, copies)  # one launch per weight copy, in rotation
+            case = f"{name}:M{m}"
+            proto.add(case, graph.replay, copies)
+            meta[case] = {"config": cfg, "op": name, "M": m, "N": n_rows, "K": HIDDEN,
+                          "kernel": ctx.last_kernel, "weight_copies": copies,
+                          "bytes": algorithmic_bytes(m, n_rows, HIDDEN, 2), "kind": "hbm",
+                          "cpu": ("fp8", m, n_rows, HIDDEN)}
+            keep.append((graph, x, codes, scales, outp))
+
+    # ---- FP8 prefill shapes (tensor-bound): one weight plane, graph of 8 launches
+    for name, n_rows in (("fp8_qkv", synth.QKV_ROWS), ("fp8_gdn_input", synth.GDN_ROWS)):
+        w, s = synth.torch_fp8_weights(SEED, 60, n_rows, HIDDEN, dev)
+        for m in (256, 512, 2048):
+            x = synth.torch_normal_bf16(SEED, 8, (m, HIDDEN), dev)
+            codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+            scales = torch.empty((m,), dtype=torch.float32, device=dev)
+            outp = torch.empty((m, n_rows), dtype=torch.bfloat16, device=dev)
+            op = tk.GdnInputProjectionOp(ctx, n_rows)
+            op.launch(None, m, x, codes, scales, w, s, outp)
+            graph = capture(torch, lambda op=op, m=m, codes=codes, scales=scales, outp=outp, w=w, s=s:
+                            op.launch(None, m, None, codes, scales, w, s, outp), 8)
+            case = f"{name}:M{m}"
+            proto.add(case, graph.replay, 8)
+            meta[case] = {"config": 5 if m == 256 else "metric", "op": name, "M": m, "N": n_rows,
+                          "K": HIDDEN, "kernel": ctx.last_kernel, "kind": "fp8_tensor",
+                          "flops": 2.0 * m * n_rows * HIDDEN,
+                          "bytes": algorithmic_bytes(m, n_rows, HIDDEN, 2),
+                          "cpu": ("fp8", m, n_rows, HIDDEN)}
+            keep.append((graph, x, codes, scales, outp, w, s))
+
+    # ---- fused residual + RMSNorm + quantise (configurations 1 and 5, and the metric's M = 512)
+    normop = tk.ResidualNormOp(ctx)
+    nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)
+    for m in (1, 256, 512):
+        copies = 1 if m == 1 else max(2, int(2 * 126e6 / (m * HIDDEN * 11)) + 1)
+        xs = [synth.torch_normal_bf16(SEED, 90 + c, (m, HIDDEN), dev) for c in range(copies)]
+        bs = [synth.torch_normal_bf16(SEED, 190 + c, (m, HIDDEN), dev) for c in range(copies)]
+        res = [torch.empty_like(xs[0]) for _ in range(copies)]
+        nrm = [torch.empty_like(xs[0]) for _ in range(copies)]
+        codes = [torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev) for _ in range(copies)]
+        scales = torch.empty((m,), dtype=torch.float32, device=dev)
+        state = {"i": 0}
+
+        def norm(m=m, xs=xs, bs=bs, res=res, nrm=nrm, codes=codes, scales=scales, state=state,
+                 copies=copies):
+            i = state["i"] % copies
+            state["i"] += 1
+            normop.launch_quantize(None, m, xs[i], bs[i], nw, res[i], nrm[i], codes[i], scales)
+
+        graph = capture(torch, norm, copies * 4)
+        case = f"residual_rmsnorm_quant_e4m3:M{m}"
+        proto.add(case, graph.replay, copies * 4)
+        meta[case] = {"config": 1 if m == 1 else 5 if m == 256 else "metric",
+                      "op": "residual_rmsnorm_quant_e4m3", "M": m, "kind": "hbm",
+                      "kernel": "resnorm_quant_kernel<1,1,1,1>",
+                      "bytes": 11 * m * HIDDEN + 4 * m, "cpu": ("norm", m)}
+        keep.append((graph, xs, bs, res, nrm, codes, scales))
+
+    # ---- configuration 3 at the other token counts (the headline run has M = lm['m'])
+    for m in (1, 4, 32):
+        if m == lm["m"]:
+            continue
+        x = synth.torch_normal_bf16(SEED, 2, (m, HIDDEN), dev)
+        codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+        scales = torch.empty((m,), dtype=torch.float32, device=dev)
+        logits = torch.empty((m, lm["vocab"]), dtype=torch.float32, device=dev)
+        scratch = torch.zeros((m,), dtype=torch.int64, device=dev)
+        pairs = torch.zeros((m, 2), dtype=torch.int32, device=dev)
+        op = tk.LmHeadOp(ctx, lm["vocab"], 0)
+        op.launch(None, m, x, codes, scales, lm["wc"], lm["ws"], None, logits, scratch, pairs)
+        graph = capture(torch, lambda op=op, m=m, codes=codes, scales=scales, logits=logits,
+                        scratch=scratch, pairs=pairs:
+                        op.launch(None, m, None, codes, scales, lm["wc"], lm["ws"], None, logits,
+                                  scratch, pairs), 1)
+        case = f"fp8_lm_head_argmax:M{m}"
+        proto.add(case, graph.replay, 1)
+        meta[case] = {"config": 3, "op": "fp8_lm_head_argmax", "M": m, "N": lm["vocab"], "K": HIDDEN,
+                      "kernel": ctx.last_kernel + " + argmax_finalize_kernel", "kind": "hbm",
+                      "bytes": algorithmic_bytes(m, lm["vocab"], HIDDEN, 4),
+                      "cpu": ("fp8", m, lm["vocab"], HIDDEN, 4)}
+        keep.append((graph, x, codes, scales, logits, scratch, pairs))
+
+    # ---- configuration 4 (M = 2048) and the decode / batched-decode shapes of the NVFP4 MLP
+    weights = mlp_weights(synth)
+    gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
+    mlp_planes = {}
+    for m in (2048, 256, 32, 8, 1):
+        pl = MlpPlanes(torch, ops, synth, m, weights)
+        mlp_planes[m] = pl
+        x = synth.torch_normal_bf16(SEED, 310, (m, HIDDEN), dev)
+        pl.x = x
+
+        def quant_in(pl=pl, m=m, x=x):
             gu.quantize(None, m, HIDDEN, x, pl.a_div, pl.a_codes, pl.a_scales)
 
-        def gate_up():
+        def gate_up(pl=pl, m=m):
             gu.launch(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
                       activation_codes=pl.a_codes, activation_scales=pl.a_scales,
                       input_global_divisor=pl.a_div)
 
-        def quant_mid():
+        def quant_mid(pl=pl, m=m):
             dn.quantize(None, m, inter, pl.mid, pl.m_div, pl.m_codes, pl.m_scales)
 
-        def down():
+        def down(pl=pl, m=m):
             dn.launch(None, m, None, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
                       activation_codes=pl.m_codes, activation_scales=pl.m_scales,
                       input_global_divisor=pl.m_div)
 
-        def gate_up_q():  # the same projection also leaving the NVFP4 form of its output
+        def gate_up_q(pl=pl, m=m):  # the same projection also leaving the NVFP4 form of its output
             gu.launch_quantize(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
                                activation_codes=pl.a_codes, activation_scales=pl.a_scales,
                                input_global_divisor=pl.a_div, output_global_divisor=pl.m_div,
                                output_codes=pl.m_codes, output_scales=pl.m_scales)
 
-        def mlp():
+        def mlp(quant_in=quant_in, gate_up_q=gate_up_q, down=down):
             quant_in(); gate_up_q(); down()
 
         for fn in (quant_in, gate_up, quant_mid, down):
             fn()
         torch.cuda.synchronize()
-        times = {}
-        for name, fn in (("quant_in", quant_in), ("gate_up_swiglu", gate_up),
-                         ("quant_mid", quant_mid), ("gate_up_swiglu_quantize", gate_up_q),
-                         ("down", down), ("mlp_total", mlp)):
-            graph = capture(torch, fn, 4)
-            for _ in range(3):
-                graph.replay()
-            reps = 10
-            times[name] = time_region(torch, graph.replay, reps) / (reps * 4)
         f_gu = 2.0 * m * 2 * inter * HIDDEN
         f_dn = 2.0 * m * HIDDEN * inter
         b_gu = 2 * inter * HIDDEN // 2 + 2 * inter * HIDDEN // 16 + m * HIDDEN // 2 + m * HIDDEN // 16 + 2 * m * inter
         b_dn = HIDDEN * inter // 2 + HIDDEN * inter // 16 + m * inter // 2 + m * inter // 16 + 2 * m * HIDDEN
-        row = {"op": "nvfp4_mlp", "M": m, "us": {k: v * 1e3 for k, v in times.items()},
-               "gate_up_TFLOPs": f_gu / times["gate_up_swiglu"] / 1e9,
-               "down_TFLOPs": f_dn / times["down"] / 1e9,
-               "mlp_TFLOPs": (f_gu + f_dn) / times["mlp_total"] / 1e9,
-               "gate_up_GBs": b_gu / times["gate_up_swiglu"] / 1e6,
-               "down_GBs": b_dn / times["down"] / 1e6}
-        if m >= 256:
-            row["gemm_frac_of_9PF"] = (f_gu + f_dn) / (times["gate_up_swiglu"] + times["down"]) / 1e9 / 9000.0
-            row["gemm_frac_of_4x_measured_bf16"] = ((f_gu + f_dn) / (times["gate_up_swiglu"] + times["down"])
-                                                    / 1e9 / (4 * burst))
-            row["tensor_peak_kind"] = kind
-        else:
-            row["gate_up_frac_of_measured_hbm"] = row["gate_up_GBs"] / hbm
-            row["down_frac_of_measured_hbm"] = row["down_GBs"] / hbm
-        out.append(row)
-        del pl
-    return out
+        for nm, fn, fl, by, cpu in (("quant_in", quant_in, 0.0, m * HIDDEN * (2 + 9 / 16), None),
+                                    ("gate_up_swiglu", gate_up, f_gu, b_gu, ("nvfp4", m, inter, HIDDEN, True)),
+                                    ("quant_mid", quant_mid, 0.0, m * inter * (2 + 9 / 16), None),
+                                    ("gate_up_swiglu_quantize", gate_up_q, f_gu, b_gu + m * inter * 9 // 16, None),
+                                    ("down", down, f_dn, b_dn, ("nvfp4", m, HIDDEN, inter, False)),
+                                    ("mlp_total", mlp, f_gu + f_dn, b_gu + b_dn, None)):
+            fn()
+            kernel = ctx.last_kernel if nm in ("gate_up_swiglu", "down") else nm
+            graph = capture(torch, fn, 4)
+            case = f"nvfp4_{nm}:M{m}"
+            proto.add(case, graph.replay, 4)
+            meta[case] = {"config": 4 if m == 2048 else 5 if m == 256 else "decode",
+                          "op": f"nvfp4_{nm}", "M": m, "kernel": kernel,
+                          "kind": "fp4_tensor" if (m >= 256 and fl > 0) else "hbm",
+                          "flops": fl, "bytes": by, "cpu": cpu}
+            keep.append(graph)
 
-
-def layer_slice_rows(torch, tk, ctx):
-    """Configuration 5, one GPU: residual add + RMSNorm + E4M3 and NVFP4 quantise (one kernel)
-    -> FP8 QKV (N = 8192) -> FP8 GDN-input (N = 12288) -> NVFP4 gate_up + SwiGLU (its epilogue
-    leaves the NVFP4 form of the intermediate at decode sizes, a quantiser launch otherwise) ->
-    NVFP4 down, as one CUDA graph of five or six kernels."""
-    from tuiskollm_b200 import ops, synth
-
-    out = []
-    dev = "cuda"
+    # ---- configuration 5: the layer slice on one GPU (M = 1 decode slice of configuration 1 too)
     qkv_w = synth.torch_fp8_weights(SEED, 400, synth.QKV_ROWS, HIDDEN, dev)
     gdn_w = synth.torch_fp8_weights(SEED, 401, synth.GDN_ROWS, HIDDEN, dev)
-    nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)
-    weight_bytes = (synth.QKV_ROWS + synth.GDN_ROWS) * HIDDEN + 3 * synth.INTERMEDIATE * HIDDEN * 9 // 16
+    weight_bytes = (synth.QKV_ROWS + synth.GDN_ROWS) * HIDDEN + 3 * inter * HIDDEN * 9 // 16
+    slice_e2e = {}
     for m in (1, 256, 512):
-        pl = MlpPlanes(torch, ops, synth, m)
+        pl = MlpPlanes(torch, ops, synth, m, weights)
         x = synth.torch_normal_bf16(SEED, 410, (m, HIDDEN), dev)
         br = synth.torch_normal_bf16(SEED, 411, (m, HIDDEN), dev)
+        x_host, br_host = x.cpu().pin_memory(), br.cpu().pin_memory()
+        out_host = torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
         res = torch.empty_like(x)
         nrm = torch.empty_like(x)
         codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
         scales = torch.empty((m,), dtype=torch.float32, device=dev)
         qkv = torch.empty((m, synth.QKV_ROWS), dtype=torch.bfloat16, device=dev)
         gdn = torch.empty((m, synth.GDN_ROWS), dtype=torch.bfloat16, device=dev)
-        norm = tk.ResidualNormOp(ctx)
         qkv_op = tk.FullAttentionQkvOp(ctx, synth.QKV_ROWS)
         gdn_op = tk.GdnInputProjectionOp(ctx, synth.GDN_ROWS)
-        gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
 
-        def slice_():
-            norm.launch_quantize_nvfp4(None, m, x, br, nw, res, nrm, codes, scales, pl.a_div,
-                                       pl.a_codes, pl.a_scales)
+        def slice_(m=m, pl=pl, x=x, br=br, res=res, nrm=nrm, codes=codes, scales=scales, qkv=qkv,
+                   gdn=gdn, qkv_op=qkv_op, gdn_op=gdn_op):
+            normop.launch_quantize_nvfp4(None, m, x, br, nw, res, nrm, codes, scales, pl.a_div,
+                                         pl.a_codes, pl.a_scales)
             qkv_op.launch(None, m, None, codes, scales, qkv_w[0], qkv_w[1], qkv)
             gdn_op.launch(None, m, None, codes, scales, gdn_w[0], gdn_w[1], gdn)
             gu.launch_quantize(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
@@ -451,19 +733,111 @@ def layer_slice_rows(torch, tk, ctx):
                       activation_codes=pl.m_codes, activation_scales=pl.m_scales,
                       input_global_divisor=pl.m_div)
 
+        def slice_e2e_(slice_=slice_, x=x, br=br, x_host=x_host, br_host=br_host, pl=pl,
+                       out_host=out_host):
+            x.copy_(x_host, non_blocking=True)
+            br.copy_(br_host, non_blocking=True)
+            slice_()
+            out_host.copy_(pl.out, non_blocking=True)
+
         slice_()
         torch.cuda.synchronize()
         graph = capture(torch, slice_, 1)
-        for _ in range(5):
-            graph.replay()
-        reps = 50
-        ms = time_region(torch, graph.replay, reps) / reps
-        flops = 2.0 * m * HIDDEN * (synth.QKV_ROWS + synth.GDN_ROWS + 3 * synth.INTERMEDIATE)
-        out.append({"op": "layer_slice", "M": m, "us": ms * 1e3, "kernels": 5 if m <= 32 else 6,
-                    "weight_stream_GBs": weight_bytes / ms / 1e6, "TFLOPs": flops / ms / 1e9,
-                    "floor_us_at_measured_hbm": weight_bytes / measured_peak()[0] / 1e3})
-        del pl
-    return out
+        case = f"layer_slice:M{m}"
+        proto.add(case, graph.replay, 1)
+        flops = 2.0 * m * HIDDEN * (synth.QKV_ROWS + synth.GDN_ROWS + 3 * inter)
+        meta[case] = {"config": 1 if m == 1 else 5 if m == 256 else "metric", "op": "layer_slice",
+                      "M": m, "kernel": "5 kernels" if m <= 32 else "6 kernels",
+                      "kind": "slice", "flops": flops, "bytes": weight_bytes, "cpu": ("slice", m)}
+        graph_e2e = capture(torch, slice_e2e_, 1)
+        for _ in range(3):
+            graph_e2e.replay()
+        reps = 40
+        ms = time_region(torch, graph_e2e.replay, reps, sync_each=True) / reps
+        slice_e2e[case] = {"us": ms * 1e3, "h2d_bytes_per_step": 2 * m * HIDDEN * 2,
+                           "d2h_bytes_per_step": m * HIDDEN * 2, "launch": "graph",
+                           "note": "host x and branch in, BF16 down output out, one sync per step"}
+        keep.append((graph, graph_e2e, pl, x, br, res, nrm, codes, scales, qkv, gdn))
+
+    results = proto.run()
+
+    rows = []
+    for case, r in results.items():
+        md = meta[case]
+        us = r["median"]
+        row = {"config": md["config"], "op": md["op"], "M": md["M"],
+               "us": {"median": us, "p10": r["p10"], "p90": r["p90"], "samples": r["samples"]}}
+        for key in ("N", "K", "weight_copies"):
+            if key in md:
+                row[key] = md[key]
+        if md["kind"] == "hbm":
+            row["roofline"] = hbm_roofline(md["kernel"], md["bytes"], us, peak_gbs, peak_kind)
+        elif md["kind"] == "fp8_tensor":
+            row["roofline"] = tensor_roofline(md["kernel"], md["flops"], md["bytes"], us,
+                                              NOMINAL_FP8_TFLOPS, 2, peak_gbs)
+        elif md["kind"] == "fp4_tensor":
+            row["roofline"] = tensor_roofline(md["kernel"], md["flops"], md["bytes"], us,
+                                              NOMINAL_FP4_TFLOPS, 4, peak_gbs)
+        else:  # the slice: bounded by its weight stream at decode, by its flops at 256 and more
+            floor_us = md["bytes"] / peak_gbs / 1e3
+            row["roofline"] = {"bound": "hbm" if md["M"] <= 32 else "tensor",
+                               "kernel": md["kernel"], "weight_bytes": md["bytes"],
+                               "algorithmic_flops": md["flops"], "us": us,
+                               "weight_stream_GBs": md["bytes"] / us / 1e3,
+                               "TFLOPs": md["flops"] / us / 1e6,
+                               "floor_us_at_measured_hbm": floor_us, "frac": floor_us / us,
+                               "peak_kind": peak_kind}
+            row["e2e"] = slice_e2e[case]
+        if with_cpu and md.get("cpu"):
+            c = md["cpu"]
+            try:
+                if c[0] == "fp8":
+                    row["cpu_baseline"] = cpu_fp8_projection(c[1], c[2], c[3], us, *(c[4:5] or (2,)))
+                elif c[0] == "norm":
+                    row["cpu_baseline"] = cpu_norm_quant(c[1], us)
+                elif c[0] == "nvfp4":
+                    row["cpu_baseline"] = cpu_nvfp4(c[1], c[2], c[3], c[4], us)
+                elif c[0] == "slice":
+                    row["cpu_baseline"] = None  # filled below from the operators' own rows
+            except Exception as exc:  # the row stays, the baseline says why it is absent
+                row["cpu_baseline"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        rows.append(row)
+    # the slice's CPU figure = the sum of its operators' extrapolated CPU times
+    by_key = {(r["op"], r["M"]): r for r in rows}
+    for r in rows:
+        if r["op"] != "layer_slice" or not with_cpu:
+            continue
+        m = r["M"]
+        parts = [by_key.get(("residual_rmsnorm_quant_e4m3", m)), by_key.get(("fp8_qkv", m)),
+                 by_key.get(("fp8_gdn_input", m)), by_key.get(("nvfp4_gate_up_swiglu", m)),
+                 by_key.get(("nvfp4_down", m))]
+        if all(p and isinstance(p.get("cpu_baseline"), dict) and "us_full_shape" in p["cpu_baseline"]
+               for p in parts):
+            total = sum(p["cpu_baseline"]["us_full_shape"] for p in parts)
+            r["cpu_baseline"] = {"value": total, "unit": "us per slice", "kind": "port",
+                                 "cores": parts[0]["cpu_baseline"]["cores"],
+                                 "gpu_speedup": total / r["us"]["median"],
+                                 "sample": "sum of the five operators' CPU rows (extrapolated)"}
+        else:
+            r.pop("cpu_baseline", None)
+    deviation = None
+    if with_cpu:
+        try:
+            pl = mlp_planes[2048]
+            gu.quantize(None, 2048, HIDDEN, pl.x, pl.a_div, pl.a_codes, pl.a_scales)
+            gu.launch_quantize(None, 2048, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+                               activation_codes=pl.a_codes, activation_scales=pl.a_scales,
+                               input_global_divisor=pl.a_div, output_global_divisor=pl.m_div,
+                               output_codes=pl.m_codes, output_scales=pl.m_scales)
+            dn.launch(None, 2048, None, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
+                      activation_codes=pl.m_codes, activation_scales=pl.m_scales,
+                      input_global_divisor=pl.m_div)
+            torch.cuda.synchronize()
+            deviation = w4a4_vs_a16(torch, pl, pl.x)
+        except Exception as exc:
+            deviation = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    del keep
+    return rows, deviation
 
 
 def tp_layer_slice(torch, tk, dist, rank, world, m, local, nccl_reduce=False):
@@ -574,20 +948,62 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local, nccl_reduce=False):
 
 
 def run_case(args):
-    """One small side case on one GPU (for profiling): `nvfp4:M` or `fp8:N:M`."""
+    """One small side case on one GPU (for profiling): `nvfp4:M`, `fp8:N:M`, `norm:M`,
+    `exchange`, or `issue` (the tcgen05 issue-rate micro-benchmark beside this file)."""
+    if args.case == "issue":
+        src = os.path.join(ROOT, "bench_tcgen05_issue.cu")
+        exe = os.path.join(ROOT, "bench_tcgen05_issue")
+        if not os.path.exists(exe) or os.path.getmtime(exe) < os.path.getmtime(src):
+            cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
+                   "-I", ROOT, "-o", exe, src]
+            if os.path.exists("/usr/bin/g++"):
+                cmd[1:1] = ["-ccbin", "/usr/bin/g++"]
+            subprocess.run(cmd, check=True)
+        return subprocess.run([exe]).returncode
+
     import torch
 
     import tuiskollm_b200 as tk
-    from tuiskollm_b200 import synth
+    from tuiskollm_b200 import ops, synth
 
     torch.cuda.set_device(0)
     ctx = tk.Context(device=0)
     parts = args.case.split(":")
+    reps = args.case_reps
     if parts[0] == "nvfp4":
-        rows = nvfp4_rows(torch, tk, ctx, (int(parts[1]),))
+        m = int(parts[1])
+        which = parts[2] if len(parts) > 2 else "all"
+        pl = MlpPlanes(torch, ops, synth, m, mlp_weights(synth))
+        x = synth.torch_normal_bf16(SEED, 310, (m, HIDDEN), "cuda")
+        gu, dn = tk.Nvfp4SwiGluOp(ctx), tk.Nvfp4DownOp(ctx)
+        gu.quantize(None, m, HIDDEN, x, pl.a_div, pl.a_codes, pl.a_scales)
+        rows = []
+
+        def gate_up():
+            gu.launch(None, m, None, pl.gu_codes, pl.gu_scales, pl.gu_div, pl.mid,
+                      activation_codes=pl.a_codes, activation_scales=pl.a_scales,
+                      input_global_divisor=pl.a_div)
+
+        def quant_mid():
+            dn.quantize(None, m, synth.INTERMEDIATE, pl.mid, pl.m_div, pl.m_codes, pl.m_scales)
+
+        def down():
+            dn.launch(None, m, None, pl.dn_codes, pl.dn_scales, pl.dn_div, pl.out,
+                      activation_codes=pl.m_codes, activation_scales=pl.m_scales,
+                      input_global_divisor=pl.m_div)
+
+        gate_up(); quant_mid(); down()
+        torch.cuda.synchronize()
+        for nm, fn in (("gate_up", gate_up), ("down", down)):
+            if which not in ("all", nm):
+                continue
+            for _ in range(2):
+                fn()
+            ms = time_region(torch, fn, reps) / reps
+            rows.append({"op": nm, "M": m, "us": ms * 1e3, "kernel": ctx.last_kernel})
     elif parts[0] == "fp8":
         n_rows, m = int(parts[1]), int(parts[2])
-        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)  # as in extra_rows: 3 x L2
+        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)  # as in config_rows: 3 x L2
         planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, "cuda")
                   for c in range(copies)]
         x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), "cuda")
@@ -606,14 +1022,68 @@ def run_case(args):
         graph = capture(torch, proj, copies)
         for _ in range(3):
             graph.replay()
-        ms = time_region(torch, graph.replay, 20) / (20 * copies)
-        rows = [{"op": "fp8", "N": n_rows, "M": m, "us": ms * 1e3,
+        ms = time_region(torch, graph.replay, reps) / (reps * copies)
+        rows = [{"op": "fp8", "N": n_rows, "M": m, "us": ms * 1e3, "kernel": ctx.last_kernel,
                  "GB/s": algorithmic_bytes(m, n_rows, HIDDEN, 2) / ms / 1e6}]
+    elif parts[0] == "norm":
+        m = int(parts[1])
+        copies = max(2, int(2 * 126e6 / (m * HIDDEN * 11)) + 1)
+        xs = [synth.torch_normal_bf16(SEED, 90 + c, (m, HIDDEN), "cuda") for c in range(copies)]
+        bs = [synth.torch_normal_bf16(SEED, 190 + c, (m, HIDDEN), "cuda") for c in range(copies)]
+        nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), "cuda", std=0.1)
+        res, nrm = torch.empty_like(xs[0]), torch.empty_like(xs[0])
+        codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device="cuda")
+        scales = torch.empty((m,), dtype=torch.float32, device="cuda")
+        normop = tk.ResidualNormOp(ctx)
+        state = {"i": 0}
+
+        def norm():
+            i = state["i"] % copies
+            state["i"] += 1
+            normop.launch_quantize(None, m, xs[i], bs[i], nw, res, nrm, codes, scales)
+
+        for _ in range(3):
+            norm()
+        ms = time_region(torch, norm, reps) / reps
+        rows = [{"op": "norm", "M": m, "us": ms * 1e3, "GB/s": (11 * m * HIDDEN + 4 * m) / ms / 1e6}]
+    elif parts[0] == "exchange":
+        # the fused exchange kernel with world = 1: its fixed cost without NVLink or rank skew
+        m = 1
+        buf = torch.zeros((ops.exchange_bytes(m, 1) + 7) // 8, dtype=torch.int64, device="cuda")
+        scratch = torch.zeros((m,), dtype=torch.int64, device="cuda")
+        merged = torch.zeros((m, 2), dtype=torch.int32, device="cuda")
+        op = tk.LmHeadOp(ctx, 4096, 0)
+        fn = lambda: op.exchange(None, m, 1, 0, scratch, [buf.data_ptr()], merged)
+        for _ in range(3):
+            fn()
+        ms = time_region(torch, fn, reps) / reps
+        rows = [{"op": "argmax_exchange world=1", "us": ms * 1e3}]
     else:
         raise SystemExit(f"unknown case {args.case}")
     status = ctx.device_status()
-    print(json.dumps({"debug": os.environ.get("TK100_DEBUG", "0"), "status": status, "case": args.case, "rows": rows}), flush=True)
+    print(json.dumps({"status": status, "case": args.case, "rows": rows}), flush=True)
     return 0
+
+
+def first_maximum_merge(gathered):
+    """Host restatement of the merge rule (tuisko-engine/src/sampling.rs:162-173 over shards):
+    `gathered` [world, rows, 2] int32 (value bits, global index, -1 = none) -> [rows, 2]; the
+    greater value in IEEE total order wins, equal values go to the lowest global index."""
+    import numpy as np
+
+    world, rows, _ = gathered.shape
+    out = np.zeros((rows, 2), np.int32)
+    for t in range(rows):
+        best = None
+        for r in range(world):
+            bits, idx = int(gathered[r, t, 0]) & 0xFFFFFFFF, int(gathered[r, t, 1])
+            if idx < 0:
+                continue
+            key = bits ^ (0xFFFFFFFF if bits & 0x80000000 else 0x80000000)
+            if best is None or (key, -idx) > (best[0], -best[1]):
+                best = (key, idx, int(gathered[r, t, 0]))
+        out[t] = (best[2], best[1]) if best else (0, -1)
+    return out
 
 
 def run_native(args):
@@ -692,21 +1162,17 @@ def run_native(args):
     def projection_only():
         op.launch(None, m, None, codes, scales, wc, ws, None, logits, scratch, pairs)
 
-    def local_pairs():
-        """This rank's own (max, index) pairs of the last step, for the sanity check."""
-        if peer_addresses is None:
-            return pairs.cpu().numpy()
-        op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, pairs)
-        torch.cuda.synchronize()
-        return pairs.cpu().numpy()
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(3):
         step()
+    kernel_name = ctx.last_kernel
     barrier()
     # One step as a CUDA graph (kernels + the NCCL gather), replayed: the way the reference's
     # engine runs this path (tuisko-engine/src/program.rs:149-154, 303-319).
@@ -722,19 +1188,31 @@ def run_native(args):
         run_step = step
         torch.cuda.synchronize()
     launches_per_step = (ctx.launch_count - launches0) // 2 if mode == "graph" else None
+    if rank == 0:
+        sampler.wait_for_first_sample()
     for _ in range(max(3, args.warmup)):
         run_step()
+    # rank 0 alone spent host time on the sampler; the exchange kernels of the other ranks give a
+    # late peer 2 s, so the ranks meet again before the timed region
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    # rank 0 alone just spent host time starting the sampler; the exchange kernels of the other
-    # ranks give a late peer 2 s, so the ranks meet again before the timed region
-    barrier()
+    first_clock_sample = sampler.mark()
     launches0 = ctx.launch_count
     ms = time_region(torch, run_step, args.steps)
     launches = (launches_per_step * args.steps if launches_per_step is not None
                 else ctx.launch_count - launches0)
+    barrier()
+    # The reference's protocol on the same step: 40 samples of `inner` replays each (at least
+    # half a second of load in total, which also gives the clock sampler something to see).
+    inner = max(1, min(256, int(0.5e3 / SAMPLES / max(ms / args.steps, 1e-3)) + 1))
+    sample_us = []
+    for _ in range(SAMPLES):
+        if world > 1:
+            dist.barrier()
+        sample_us.append(time_region(torch, run_step, inner) * 1e3 / inner)
+    st = torch.tensor(sample_us, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    sample_us = sorted(float(v) for v in st.tolist())
     barrier()
     # End to end: the same step with the pinned-host -> device copy of the hidden rows in front
     # and the device -> pinned-host copy of the selected (value, index) pairs behind, recorded
@@ -751,10 +1229,18 @@ def run_native(args):
     barrier()
     ms_e2e = time_region(torch, run_e2e, args.steps, sync_each=True)
     barrier()
+    # ... and without a graph: every operator call made from the host, per step (C-ABI cost)
+    for _ in range(3):
+        step_e2e()
+        torch.cuda.synchronize()
+    barrier()
+    ms_e2e_eager = time_region(torch, step_e2e, args.steps, sync_each=True)
+    barrier()
     for _ in range(3):
         projection_only()
-    ms_proj = time_region(torch, projection_only, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    ms_proj = time_region(torch, projection_only, max(args.steps, 20))
+    ms_proj = ms_proj / max(args.steps, 20) * args.steps
+    clocks = sampler.stop(first_clock_sample) if rank == 0 else None
 
     tp = []
     if world > 1 and not args.no_extra:
@@ -762,23 +1248,70 @@ def run_native(args):
             t_ms, t_mode, t_route = tp_layer_slice(torch, tk, dist, rank, world, m_tp, local,
                                                    nccl_reduce=args.nccl_reduce)
             tp.append([m_tp, t_ms, t_mode, t_route])
-    times = torch.tensor([ms, ms_e2e, ms_proj] + [t[1] for t in tp], dtype=torch.float64, device=dev)
+    times = torch.tensor([ms, ms_e2e, ms_proj, ms_e2e_eager] + [t[1] for t in tp],
+                         dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     vals = [float(v) for v in times.tolist()]
-    ms, ms_e2e, ms_proj = vals[:3]
-    for t, v in zip(tp, vals[3:]):
+    ms, ms_e2e, ms_proj, ms_e2e_eager = vals[:4]
+    for t, v in zip(tp, vals[4:]):
         t[1] = v
 
-    # sanity: the selected token is the arg-max of the logits this step wrote
-    run_step()
-    torch.cuda.synchronize()
-    final = (merged if world > 1 else pairs).cpu().numpy()
-    mine = local_pairs()
-    rounded = logits.to(torch.bfloat16).float()
-    for t in range(m):
-        first = int(torch.nonzero(rounded[t] == rounded[t].max())[0, 0]) + offset
-        assert int(mine[t, 1]) == first, "device argmax disagrees with its own logits"
+    # ---- correctness of what was timed
+    def local_pairs():
+        """This rank's own (max, index) pairs for the current inputs (finalize route)."""
+        op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, pairs)
+        torch.cuda.synchronize()
+        return pairs.cpu().numpy().copy()
+
+    def check_step(tag):
+        """One step; the device argmax must equal the first maximum of the logits this rank
+        wrote, and at N > 1 the merged pair must equal, bit for bit and on every rank, the host
+        merge of all ranks' local pairs (gathered with NCCL)."""
+        run_step()
+        torch.cuda.synchronize()
+        final = (merged if world > 1 else pairs).cpu().numpy().copy()
+        mine = local_pairs()
+        rounded = logits.to(torch.bfloat16).float()
+        for t in range(m):
+            first = int(torch.nonzero(rounded[t] == rounded[t].max())[0, 0]) + offset
+            assert int(mine[t, 1]) == first, f"{tag}: device argmax disagrees with its own logits"
+        if world == 1:
+            return {"scenario": tag, "token0_index": int(final[0, 1])}
+        all_local = torch.zeros((world, m, 2), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(all_local.view(-1), torch.from_numpy(mine).to(dev).view(-1))
+        expect = first_maximum_merge(all_local.cpu().numpy())
+        assert np.array_equal(final, expect), (
+            f"{tag}: rank {rank} merged pair {final.tolist()} != host merge {expect.tolist()}")
+        all_final = torch.zeros((world, m, 2), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(all_final.view(-1), torch.from_numpy(final).to(dev).view(-1))
+        af = all_final.cpu().numpy()
+        assert all(np.array_equal(af[r], af[0]) for r in range(world)), f"{tag}: ranks disagree"
+        return {"scenario": tag, "token0_index": int(final[0, 1]),
+                "winner_rank": int(final[0, 1]) // shard,
+                "local_indices_token0": [int(v) for v in all_local[:, 0, 1].tolist()]}
+
+    checks = [check_step("random weights")]
+    if world > 1:
+        # Plant a row that wins by a wide margin -- its codes are the token's own activation
+        # codes, so its logit is the sum of their squares -- in the LAST rank's shard, then the
+        # same row in a second shard so that the maximum is an exact cross-shard tie.
+        planted_row = 5
+        def plant(in_rank, local_row):
+            if rank == in_rank:
+                wc[local_row].copy_(codes[0])
+                ws.view(torch.int16)[local_row] = 0x3F80  # BF16 1.0
+            torch.cuda.synchronize()
+            dist.barrier()
+        plant(world - 1, planted_row)
+        c = check_step("winner planted in the last rank's shard")
+        assert c["token0_index"] == (world - 1) * shard + planted_row, c
+        checks.append(c)
+        tie_rank = 1 if world > 2 else 0
+        plant(tie_rank, planted_row + 4)
+        c = check_step("exact tie between two shards")
+        assert c["token0_index"] == tie_rank * shard + planted_row + 4, c
+        checks.append(c)
     status = ctx.device_status()
     assert status == 0, f"device status word {status:#x}"
 
@@ -791,20 +1324,25 @@ def run_native(args):
         shard_bytes = algorithmic_bytes(m, shard, HIDDEN, 4)
         proj_ms = ms_proj / args.steps
         achieved = shard_bytes / proj_ms / 1e6
+        cfg = workload_config(m, vocab, world)
         line = {
             "metric": "fp8_lm_head_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3",
-            "data": "synthetic",
-            "config": {"workload": f"fp8_lm_head_argmax K={HIDDEN} vocab={vocab} M={m}",
-                       "rows": m, "vocab_shard_rows": shard, "parallelism": f"vocab-shard x{world}",
-                       "launch": mode, "exchange": exchange,
-                       "l2": "weight shard (%.0f MB) larger than L2, streamed once per step"
-                             % (shard * HIDDEN / 1e6),
-                       "tokens_per_s": m / (per_step * 1e-3), "us_per_step": per_step * 1e3},
+            "data": "synthetic", "config": cfg,
+            "run": {"vocab_shard_rows": shard, "launch": mode, "exchange": exchange,
+                    "tokens_per_s": m / (per_step * 1e-3), "us_per_step": per_step * 1e3},
+            "protocol": {"samples": SAMPLES, "replays_per_sample": inner,
+                         "us_per_step": {"median": statistics.median(sample_us),
+                                         "p10": percentile(sample_us, 0.1),
+                                         "p90": percentile(sample_us, 0.9)},
+                         "source": "qual/src/device_benchmark.rs:993-1101 (40 samples, median/p10/p90)"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": m * HIDDEN * 2,
                     "d2h_bytes_per_step": m * 8, "us_per_step": ms_e2e / args.steps * 1e3,
-                    "launch": e2e_mode},
+                    "launch": e2e_mode,
+                    "eager": {"value": total_bytes / (ms_e2e_eager / args.steps) / 1e6,
+                              "us_per_step": ms_e2e_eager / args.steps * 1e3,
+                              "note": "every operator call made from the host each step, no graph"}},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
@@ -812,10 +1350,13 @@ def run_native(args):
                          "traffic_source": "ncu dram read+write bytes of this kernel at vocab "
                                            "248320, M=1 (1 272 757 504 B), scaled by algorithmic bytes",
                          "peak_kind": peak_kind,
-                         "kernel": "fp8_projection_kernel<16> (+ argmax finalize, < 2 us)",
-                         "us_per_launch": proj_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
+                         "kernel": kernel_name + " (+ argmax finalize, < 2 us)" if world == 1
+                                   else kernel_name,
+                         "algorithmic_bytes": shard_bytes,
+                         "us_per_launch": proj_ms * 1e3, "frac_of_8TBs": achieved / NOMINAL_HBM_GBS},
             "clocks": clocks,
-            "selected_tokens": final[:, 1].tolist()[:8],
+            "checks": checks,
+            "selected_tokens": [c["token0_index"] for c in checks],
         }
         if tp:
             line["tp_layer_slice"] = [
@@ -824,12 +1365,18 @@ def run_native(args):
                  "parallelism": f"column(QKV,GDN-in,gate_up) + row(down) x{world}, fp32 partial sums"}
                 for t in tp]
         if world == 1 and not args.no_cpu:
-            gbs, dt, threads, note, _ = cpu_lm_head(m, 3, 1, budget_s=15.0,
-                                                    sample_rows=args.cpu_sample_rows)
+            gbs, dt, threads, note, srows = cpu_lm_head(m, 3, 1, budget_s=15.0,
+                                                        sample_rows=args.cpu_sample_rows)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-                                    "sample": note, "seconds_per_sample": dt}
+                                    "sample": note, "seconds_per_sample": dt,
+                                    "sampled_vocab_rows": srows}
         if world == 1 and not args.no_extra:
-            line["extra"] = extra_rows(torch, tk, ctx, peak)
+            rows, deviation = config_rows(torch, tk, ctx, peak, peak_kind,
+                                          {"m": m, "vocab": vocab, "wc": wc, "ws": ws},
+                                          with_cpu=not args.no_cpu)
+            line["configs"] = rows
+            if deviation is not None:
+                line["w4a4_vs_a16"] = deviation
         print(json.dumps(line), flush=True)
     if world > 1:
         # Graphs that hold NCCL kernels are still alive here and tearing the process group
@@ -860,7 +1407,9 @@ def main():
                     help="N > 1: gather the pairs with NCCL instead of the fused peer exchange")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
-    ap.add_argument("--case", default="", help="run one side case only: nvfp4:M or fp8:N:M")
+    ap.add_argument("--case", default="",
+                    help="run one side case only: nvfp4:M[:gate_up|down], fp8:N:M, norm:M, exchange, issue")
+    ap.add_argument("--case-reps", type=int, default=20, help="timed launches of a --case run")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

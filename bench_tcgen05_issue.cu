@@ -1,17 +1,16 @@
 // Micro-benchmark behind the NVFP4 kernels' design: how fast one thread can issue block-scaled
 // tcgen05.mma together with the tcgen05.cp scale copies they need, with the operands already
 // resident in shared memory (no loads).  One CTA per SM, clock64 around the loop, CUDA events
-// around the launch.  Not linked into the library.  Every wait is bounded.
-//
-//   nvcc -ccbin g++ -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 \
-//        -o tcgen05_issue_bench tcgen05_issue_bench.cu && ./tcgen05_issue_bench
+// around the launch.  Not linked into the library: `python bench.py --case issue` compiles it
+// next to this file and runs it (the tensor-pipe ceiling of the instruction mix that the
+// block-scaled FP4 roofline fractions are read against).  Every wait is bounded.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
 
-#include "../ptx.cuh"
+#include "tuiskollm_b200/csrc/ptx.cuh"
 
 using namespace tk100;
 

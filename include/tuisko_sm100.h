@@ -94,6 +94,10 @@ TK100_API const char* tk100_last_error(const tk100_ctx* ctx);
 TK100_API tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* word);
 /* Number of kernels this context has launched (for launch accounting). */
 TK100_API uint64_t tk100_launch_count(const tk100_ctx* ctx);
+/* Name of the kernel instantiation the last projection launch on this context took, e.g.
+ * "fp8_projection_kernel<16,1> splits=1" (token tile, ring variant) -- for reports and route
+ * tests; valid until the next call.  No counterpart in the reference. */
+TK100_API const char* tk100_last_kernel(tk100_ctx* ctx);
 
 /* ResidualNormOp::launch_plain (tuisko-kernels-sm120/src/residual_norm.rs:425-456). */
 TK100_API tk100_status tk100_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
@@ -290,9 +294,12 @@ TK100_API tk100_status tk100_f32_to_bf16(tk100_ctx* ctx, tk100_stream stream, si
  *   - the first call on each device looks up the array's device address, the SM count and
  *     the kernel attributes (the device must be current); make that first call before any
  *     stream capture begins;
- *   - all calls on a device share the one array: each call clears the tickets and the fault
- *     word on `stream` before its kernel, and two calls whose kernels could overlap on the
- *     GPU (different streams, no dependency) race on it -- serialise them;
+ *   - all calls on a device share the one array: each call clears the tickets on `stream`
+ *     before its kernel, and two calls whose kernels could overlap on the GPU (different
+ *     streams, no dependency) race on it -- serialise them;
+ *   - a bounded in-kernel wait that runs out leaves TK100_DEVICE_WAIT_TIMEOUT in the array's
+ *     fault word and the output of that call (and of later calls, whose CTAs leave at once
+ *     while the bit is set) is invalid; tk100_fp8_projection_static_status reads and clears it;
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
  * `message` (may be NULL) receives the failure text, at most message_capacity bytes. */
 #define TK100_STATIC_MAX_ROWS 256
@@ -301,6 +308,11 @@ TK100_API tk100_status tk100_fp8_projection_static(
     tk100_stream stream, int rows, int out_rows, int columns, const uint8_t* activation_codes,
     const float* activation_scales, const uint8_t* weight_codes, const uint16_t* weight_scales,
     uint16_t* output, char* message, size_t message_capacity);
+/* No counterpart in the reference.  Reads and clears the fault word of the static scratch on the
+ * current device (the counterpart of tk100_device_status for the context-free entry point; same
+ * TK100_DEVICE_* bits); synchronises `stream`, allocates nothing.  Call it on the stream the
+ * static launches used, after them. */
+TK100_API tk100_status tk100_fp8_projection_static_status(tk100_stream stream, uint32_t* word);
 
 #ifdef __cplusplus
 } /* extern "C" */

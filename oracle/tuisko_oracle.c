@@ -463,3 +463,13 @@ TKO_API int tko_num_threads(void) {
   return 1;
 #endif
 }
+
+/* Sets the OpenMP team size for the loops above (a launcher such as torch.distributed.run
+ * exports OMP_NUM_THREADS=1 to its ranks; the CPU baseline wants all online cores). */
+TKO_API void tko_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}

@@ -77,6 +77,8 @@ def lib() -> C.CDLL:
         L.tko_nvfp4_w4a4_dot.restype = C.c_int
         L.tko_nvfp4_w4a4_dot.argtypes = [u8p, u8p, C.c_float, sz, sz, u8p, u8p, C.c_float, sz, f64p]
         L.tko_num_threads.restype = C.c_int
+        L.tko_set_num_threads.restype = None
+        L.tko_set_num_threads.argtypes = [C.c_int]
         L.tko_init()
         _lib = L
     return _lib
@@ -271,3 +273,9 @@ def nvfp4_w4a4_dot(a_codes, a_scales, a_divisor, w_codes, w_scales, w_divisor) -
 
 def num_threads() -> int:
     return int(lib().tko_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """OpenMP team size of the oracle's loops; returns the size now in force."""
+    lib().tko_set_num_threads(int(n))
+    return num_threads()

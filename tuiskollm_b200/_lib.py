@@ -41,6 +41,7 @@ SIGNATURES = {
     "tk100_last_error": (C.c_char_p, [_vp]),
     "tk100_device_status": (_i, [_vp, _vp, C.POINTER(C.c_uint32)]),
     "tk100_launch_count": (C.c_uint64, [_vp]),
+    "tk100_last_kernel": (C.c_char_p, [_vp]),
     "tk100_rms_norm": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "tk100_residual_rms_norm": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "tk100_residual_rms_norm_quantize": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -67,6 +68,7 @@ SIGNATURES = {
                                  C.POINTER(C.c_uint64), _vp]),
     "tk100_fp8_projection_static": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, C.c_char_p,
                                          C.c_size_t]),
+    "tk100_fp8_projection_static_status": (_i, [_vp, C.POINTER(C.c_uint32)]),
 }
 
 _lib = None

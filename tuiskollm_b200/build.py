@@ -47,6 +47,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 def _compile(verbose: bool) -> str:
+    """TK100_EXPERIMENT=1 in the environment of the build adds -DTK100_EXPERIMENT: the library
+    then honours the TK100_DEBUG performance-experiment bits (which make results wrong); the
+    default build has no such code."""
     tmp = "%s.%d.tmp" % (LIB, os.getpid())
     cmd = [
         nvcc_path(), "-std=c++17", "-O3", "-lineinfo",
@@ -54,7 +57,8 @@ def _compile(verbose: bool) -> str:
         "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
         "-Xptxas", "-v" if verbose else "-warn-spills",
         "-o", tmp,
-    ] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+    ] + (["-DTK100_EXPERIMENT"] if os.environ.get("TK100_EXPERIMENT") == "1" else []) \
+      + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a private gcc; nvcc wants the system one
     if os.path.exists("/usr/bin/g++"):

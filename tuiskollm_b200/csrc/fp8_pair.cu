@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kThreads, kStages <= 3 ? 2 : 1)
         const uint64_t desc_a = umma_desc_sw128(base + kWTile);
 #pragma unroll
         for (int k4 = 0; k4 < kTileKBytes / 32; ++k4) {
-          if (p.debug & DBG_NO_MMA) break;
+          if (TK100_DBG(p, DBG_NO_MMA)) break;
           umma_f8f6f4_pair(tmem, desc_w + 2 * k4, desc_a + 2 * k4, IDESC, (i | k4) != 0);
         }
         umma_commit_pair(&ctl->empty[s]);
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, kStages <= 3 ? 2 : 1)
     tc_fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
-    if (!(p.debug & DBG_NO_EPILOGUE)) {
+    if (!TK100_DBG(p, DBG_NO_EPILOGUE)) {
 #pragma unroll 1
       for (int c0 = part * 16; c0 < kTok; c0 += 32) {
         if (tok0 + c0 >= p.rows) break;  // warp-uniform

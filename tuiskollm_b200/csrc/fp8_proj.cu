@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       // First pass over the ring: the weight tiles do not depend on the predecessor kernel,
       // so they are requested before pdl_wait(); the activation-code tiles of the same
       // stages follow once the predecessor (the quantiser) is known to be complete.
-      const bool load_a = !(p.debug & DBG_NO_ACT);
+      const bool load_a = !TK100_DBG(p, DBG_NO_ACT);
       const uint32_t tx_bytes = load_a ? STAGE_BYTES : kWStageBytes;
       const int pre = nkb < STAGES ? nkb : STAGES;
       for (int i = 0; i < pre; ++i) {
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         const uint64_t desc_a = umma_desc_sw128(w_addr + kWStageBytes);
 #pragma unroll
         for (int k4 = 0; k4 < kTileKBytes / 32; ++k4) {
-          if (p.debug & DBG_NO_MMA) break;
+          if (TK100_DBG(p, DBG_NO_MMA)) break;
           // +2 in the address field = +32 bytes along K inside the swizzled row
           umma_f8f6f4(tmem, desc_w + 2 * k4, desc_a + 2 * k4, IDESC, (i | k4) != 0);
         }
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       }
     };
 
-    if (p.debug & DBG_NO_EPILOGUE) {
+    if (TK100_DBG(p, DBG_NO_EPILOGUE)) {
       // experiment: accumulator left unread
     } else if (p.splits == 1) {
 #pragma unroll 1
@@ -357,10 +357,10 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          if (c0 + j < valid_tok && !(p.debug & 8)) __stcg(mine + (c0 + j) * kTileRows, __uint_as_float(r[j]));
+          if (c0 + j < valid_tok && !TK100_DBG(p, 8)) __stcg(mine + (c0 + j) * kTileRows, __uint_as_float(r[j]));
         }
       }
-      if (!(p.debug & 16)) __threadfence();
+      if (!TK100_DBG(p, 16)) __threadfence();
       epilogue_barrier();
       if (et == 0) {
         unsigned int* counter = p.counters + tile_m * gridDim.x + tile_n;
@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         ctl->is_last = last ? 1u : 0u;
       }
       epilogue_barrier();
-      if (ctl->is_last && !(p.debug & 32)) {
+      if (ctl->is_last && !TK100_DBG(p, 32)) {
         __threadfence();
         const size_t split_stride =
             static_cast<size_t>(gridDim.y) * gridDim.x * (BLOCK_TOK * kTileRows);
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       // peers' shared memory and added in split order (fixed, so bit-reproducible).
       cluster_arrive();
       cluster_wait();
-      if (!(p.debug & DBG_NO_EPILOGUE)) {
+      if (!TK100_DBG(p, DBG_NO_EPILOGUE)) {
         const uint32_t rank = cluster_cta_rank();
         const uint32_t my_addr = smem_u32(reinterpret_cast<float*>(smem) + row_in_tile);
 #pragma unroll 1
@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       cluster_wait();
     }
 
-    if (want_argmax && !(p.debug & DBG_NO_EPILOGUE) &&
+    if (want_argmax && !TK100_DBG(p, DBG_NO_EPILOGUE) &&
         (p.splits == 1 || clustered || ctl->is_last)) {
       epilogue_barrier();
       for (int j = et; j < valid_tok; j += kEpilogueThreads) {

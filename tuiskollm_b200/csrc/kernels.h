@@ -9,13 +9,23 @@
 
 namespace tk100 {
 
-// True unless TK100_PDL=0: kernels are launched with programmatic stream serialisation so
-// that a kernel's set-up and weight prefetch overlap the tail of its predecessor.
+// Process-wide switches, read from the environment by read_process_switches() when a context
+// is created (or the context-free entry point sets a device up) and never by a launch:
+// TK100_PDL=0 turns programmatic stream serialisation off (with it a kernel's set-up and weight
+// prefetch overlap the tail of its predecessor).
+void read_process_switches();
 bool pdl_enabled();
 
-// Performance-experiment switches read once from TK100_DEBUG (results are wrong when any is
-// set): 1 = skip the epilogue, 2 = skip the UMMA issue, 4 = skip the activation loads.
+// Performance-experiment switches (1 = skip the epilogue, 2 = skip the UMMA issue, 4 = skip the
+// activation loads; results are wrong when any is set).  They exist only in a library built
+// with -DTK100_EXPERIMENT, which reads them from TK100_DEBUG; the default build compiles every
+// test of them to `false`.
 enum : uint32_t { DBG_NO_EPILOGUE = 1, DBG_NO_MMA = 2, DBG_NO_ACT = 4 };
+#ifdef TK100_EXPERIMENT
+#define TK100_DBG(p, bits) (((p).debug & (bits)) != 0)
+#else
+#define TK100_DBG(p, bits) false
+#endif
 uint32_t debug_flags();
 
 // A cluster shape other than (1, 1, 1) launches thread-block clusters of that shape.
@@ -123,6 +133,9 @@ constexpr long long kPeerSumOneShotElems = 16384;  // up to here every rank rece
 struct PeerSumParams {
   long long elems;        // values per rank, multiple of 8
   long long chunk;        // two-shot: values of one rank's chunk (multiple of 8); world * chunk >= elems
+  long long chunk_capacity;  // the chunk of a call at the buffer's full capacity: slot / result stride
+  long long one_shot_stride4;  // one-shot slot stride in float4 (fixed by the capacity)
+  size_t one_shot_offset;  // byte offset of the one-shot slots inside every rank's buffer
   int world, rank;
   int one_shot;
   const float* partial;   // this rank's [elems] fp32

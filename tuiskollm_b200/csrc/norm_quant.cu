@@ -198,21 +198,23 @@ cudaError_t launch_chunks(cudaStream_t stream, int rows, int hidden, int threads
 
 }  // namespace
 
-bool pdl_enabled() {
-  static const bool enabled = [] {
-    const char* v = std::getenv("TK100_PDL");
-    return !(v && v[0] == '0');
-  }();
-  return enabled;
+namespace {
+bool g_pdl = true;
+uint32_t g_debug = 0;
+}  // namespace
+
+void read_process_switches() {
+  const char* v = std::getenv("TK100_PDL");
+  g_pdl = !(v && v[0] == '0');
+#ifdef TK100_EXPERIMENT
+  const char* d = std::getenv("TK100_DEBUG");
+  g_debug = d ? static_cast<uint32_t>(std::atoi(d)) : 0u;
+#endif
 }
 
-uint32_t debug_flags() {
-  static const uint32_t flags = [] {
-    const char* v = std::getenv("TK100_DEBUG");
-    return v ? static_cast<uint32_t>(std::atoi(v)) : 0u;
-  }();
-  return flags;
-}
+bool pdl_enabled() { return g_pdl; }
+
+uint32_t debug_flags() { return g_debug; }
 
 bool norm_geometry(int hidden, int* threads, int* chunks) {
   if (hidden <= 0 || (hidden & 7) != 0) return false;

@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
         const uint32_t code_bytes = NW * kWTile + BLOCK_TOK * kStageKBytes;
         mbar_arrive_expect_tx(&ctl->full[s],
-                              (p.debug & DBG_NO_ACT)
+                              TK100_DBG(p, DBG_NO_ACT)
                                   ? NW * (kWTile + sf_bytes)
                                   : code_bytes + (NW + 1) * sf_bytes);
         tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, w_tile * kRows, pol_w);
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         }
       };
       auto load_activations = [&](int i, int s) {
-        if (p.debug & DBG_NO_ACT) return;
+        if (TK100_DBG(p, DBG_NO_ACT)) return;
         uint8_t* stage = smem + s * STAGE_BYTES;
         const int kb = kb_begin + i;
         tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kb * kStageKBytes, tok0, pol_a);
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         const int steps = min(4, (p.k - (kb_begin + i) * kStageK) / 64);
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          if (k4 >= steps || (p.debug & DBG_NO_MMA)) break;
+          if (k4 >= steps || TK100_DBG(p, DBG_NO_MMA)) break;
           const uint32_t slot = sf_base + static_cast<uint32_t>(((i * 4 + k4) % kSfSlots) * kSfSlotCols);
           tmem_cp_32x128b_warpx4(slot, umma_desc_noswizzle_rows16(base + OFF_SFA + k4 * kSfChunk));
           if (GATE_UP) {
@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
     tc_fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
-    if (p.debug & DBG_NO_EPILOGUE) {
+    if (TK100_DBG(p, DBG_NO_EPILOGUE)) {
       // experiment: accumulators left unread
     } else if (GATE_UP) {
 #pragma unroll 1
@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
   if (pair_swiglu) {
     cluster_arrive();
     cluster_wait();
-    if (warp >= 2 && !(p.debug & DBG_NO_EPILOGUE)) {
+    if (warp >= 2 && !TK100_DBG(p, DBG_NO_EPILOGUE)) {
       constexpr int H = BLOCK_TOK / 2;
       const int quad = warp & 3;
       const int half = (warp - 2) >> 2;
@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
     // peers' shared memory and are added in split order (fixed => bit-reproducible).
     cluster_arrive();
     cluster_wait();
-    if (warp >= 2 && !(p.debug & DBG_NO_EPILOGUE)) {
+    if (warp >= 2 && !TK100_DBG(p, DBG_NO_EPILOGUE)) {
       const int quad = warp & 3;
       const int half = (warp - 2) >> 2;
       const int row_in_tile = quad * 32 + lane;

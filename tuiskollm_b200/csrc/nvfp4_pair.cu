@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       pdl_wait();
       for (int i = 0; i < nkb && ok; ++i) {
-        if (p.debug & 8) break;  // experiment: no loads at all (the MMAs run on stale shared memory)
+        if (TK100_DBG(p, 8)) break;  // experiment: no loads at all (the MMAs run on stale shared memory)
         const int s = i % kStages;
         const uint32_t phase = (i / kStages) & 1;
         ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % kStages;
         const uint32_t phase = (i / kStages) & 1;
-        if (!(p.debug & 8)) ok = mbar_wait(&ctl->full[s], phase, p.status);
+        if (!TK100_DBG(p, 8)) ok = mbar_wait(&ctl->full[s], phase, p.status);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t base = smem_u32(smem + s * kStageBytes);
@@ -162,9 +162,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int steps = min(4, (p.k - i * kStageK) / 64);
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          if (k4 >= steps || (p.debug & DBG_NO_MMA)) break;
+          if (k4 >= steps || TK100_DBG(p, DBG_NO_MMA)) break;
           const uint32_t slot = sf_base + static_cast<uint32_t>(((i * 4 + k4) % kSfSlots) * kSfSlotCols);
-          if (!(p.debug & 16)) {  // experiment switch: MMAs without the scale copies
+          if (!TK100_DBG(p, 16)) {  // experiment switch: MMAs without the scale copies
             tmem_cp_32x128b_warpx4_pair(slot, umma_desc_noswizzle_rows16(base + kOffSfa + k4 * kSfChunk));
             tmem_cp_32x128b_warpx4_pair(slot + 4, umma_desc_noswizzle_rows16(base + kOffSfb + k4 * kSfChunk));
             tmem_cp_32x128b_warpx4_pair(slot + 8,
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
-    if (p.debug & DBG_NO_EPILOGUE) {
+    if (TK100_DBG(p, DBG_NO_EPILOGUE)) {
       // experiment: accumulator left unread
     } else if (!GATE_UP) {
 #pragma unroll 1
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (GATE_UP) {
     cluster_arrive();
     cluster_wait();
-    if (warp >= 2 && !(p.debug & DBG_NO_EPILOGUE)) {
+    if (warp >= 2 && !TK100_DBG(p, DBG_NO_EPILOGUE)) {
       const int quad = warp & 3;
       const int half = (warp - 2) >> 2;
       const int row_in_tile = quad * 32 + lane;

@@ -19,21 +19,30 @@ thread_local std::string g_create_error;
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-// TK100_CLUSTER=0 falls back to the global-scratch split-K reduction (for A/B runs).
-bool cluster_reduce_enabled() {
-  static const bool enabled = [] {
-    const char* v = std::getenv("TK100_CLUSTER");
-    return !(v && v[0] == '0');
-  }();
-  return enabled;
-}
-
-int env_int(const char* name) {
+int env_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
-  return v ? std::atoi(v) : 0;
+  return (v && v[0]) ? std::atoi(v) : fallback;
 }
 
 }  // namespace
+
+Tuning Tuning::from_environment() {
+  Tuning t;
+  t.splits = env_int("TK100_SPLITS", t.splits);
+  t.block_tok = env_int("TK100_BLOCK_TOK", t.block_tok);
+  t.slots_per_sm = env_int("TK100_SLOTS_PER_SM", t.slots_per_sm);
+  t.deep_ring = env_int("TK100_DEEP_RING", t.deep_ring);
+  t.l2_prefetch = env_int("TK100_L2_PREFETCH", t.l2_prefetch);
+  t.nvfp4_l2_prefetch = env_int("TK100_NVFP4_L2_PREFETCH", t.nvfp4_l2_prefetch);
+  t.cluster = env_int("TK100_CLUSTER", t.cluster);
+  t.fp8_pair = env_int("TK100_FP8_PAIR", t.fp8_pair);
+  t.fp8_pair_min_rows = env_int("TK100_FP8_PAIR_MIN_ROWS", t.fp8_pair_min_rows);
+  t.nvfp4_pair = env_int("TK100_PAIR", t.nvfp4_pair);
+  t.nvfp4_pair_min_rows = env_int("TK100_PAIR_MIN_ROWS", t.nvfp4_pair_min_rows);
+  t.swiglu_pairs = env_int("TK100_SWIGLU_PAIRS", t.swiglu_pairs);
+  t.fused_exchange = env_int("TK100_FUSED_EXCHANGE", t.fused_exchange);
+  return t;
+}
 
 // --------------------------------------------------------------------- Context
 
@@ -95,8 +104,8 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
   }
   ctx->config_ = cfg;
   ctx->sm_count_ = prop.multiProcessorCount;
-  ctx->forced_splits_ = env_int("TK100_SPLITS");
-  ctx->forced_block_tok_ = env_int("TK100_BLOCK_TOK");
+  read_process_switches();
+  ctx->tuning_ = Tuning::from_environment();
 
   cudaDriverEntryPointQueryResult q;
   e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_fn_, cudaEnableDefault, &q);
@@ -160,11 +169,17 @@ Context::~Context() {
   if (peer_sum_state_) cudaFree(peer_sum_state_);
 }
 
+const char* Context::last_kernel() {
+  char text[160];
+  std::snprintf(text, sizeof text, "%s<%d,%d> splits=%d%s", route_.family, route_.a, route_.b,
+                route_.splits, route_.cluster ? " cluster" : "");
+  route_text_ = text;
+  return route_text_.c_str();
+}
+
 Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                            CUtensorMap* out) {
-  char key[96];
-  std::snprintf(key, sizeof key, "%p:%llu:%llu:%u", base, static_cast<unsigned long long>(rows),
-                static_cast<unsigned long long>(row_bytes), box_rows);
+  const MapKey key{base, rows, row_bytes, box_rows, 0u};
   auto it = maps_.find(key);
   if (it != maps_.end()) {
     *out = it->second;
@@ -191,8 +206,7 @@ Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, 
 }
 
 Status Context::scale_map(const void* base, uint64_t chunks, CUtensorMap* out) {
-  char key[96];
-  std::snprintf(key, sizeof key, "sf:%p:%llu", base, static_cast<unsigned long long>(chunks));
+  const MapKey key{base, chunks, 512u, 4u, 1u};
   auto it = maps_.find(key);
   if (it != maps_.end()) {
     *out = it->second;
@@ -375,15 +389,14 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   // Prefill shapes with a plain BF16 output: CTA pairs (256-row x 256-token pair tiles) halve
   // the operand bytes per MAC, which is what bounds the one-CTA kernel there.
   {
-    const char* pe = std::getenv("TK100_FP8_PAIR");
-    const char* pm = std::getenv("TK100_FP8_PAIR_MIN_ROWS");
-    const int min_rows = pm ? std::atoi(pm) : 256;
+    const Tuning& tune = ctx_.tuning();
+    const int min_rows = tune.fp8_pair_min_rows;
     // a launch of fewer than 32 pair CTAs (a small tensor-parallel shard of the plane) leaves
     // most SMs idle: the one-CTA kernel splits K instead (TK100_FP8_PAIR=2 takes the pair route
     // anyway).  Shards of 32-48 pair CTAs were measured faster on pairs than split.
     const long long pair_ctas = 2LL * ((rows + 255) / 256) * (out_rows / 256);
-    if (!(pe && pe[0] == '0') && rows >= min_rows && out_rows % 256 == 0 &&
-        (pair_ctas >= 32 || (pe && pe[0] == '2')) && output &&
+    if (tune.fp8_pair != 0 && rows >= min_rows && out_rows % 256 == 0 &&
+        (pair_ctas >= 32 || tune.fp8_pair == 2) && output &&
         !logits_f32 && !argmax_scratch && ctx_.forced_block_tok() == 0 && ctx_.forced_splits() == 0) {
       CUtensorMap map_w, map_a;
       TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(out_rows),
@@ -397,13 +410,14 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
       q.splits = 1;
       // at most one CTA per SM: the longer ring
       q.deep_ring = 2LL * ((rows + 255) / 256) * (out_rows / 256) <= ctx_.sm_count() ? 1 : 0;
-      if (const char* dr = std::getenv("TK100_DEEP_RING")) q.deep_ring = dr[0] != '0';
+      if (tune.deep_ring >= 0) q.deep_ring = tune.deep_ring != 0;
       q.act_scales = activation_scales;
       q.w_scales = weight_scales;
       q.out = output;
       q.status = ctx_.status_word();
       q.debug = debug_flags();
       ctx_.count_launch();
+      ctx_.note_route("fp8_pair_kernel", q.deep_ring ? 6 : 3, 0, 1, 1);
       return ctx_.check(launch_fp8_pair(stream, map_w, map_a, q), "launching the FP8 pair projection");
     }
   }
@@ -425,8 +439,8 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   // CTAs per SM by shared memory and registers: three up to 32-token tiles, two up to 128
   long long slots =
       static_cast<long long>(ctx_.sm_count()) * (block_tok <= 32 ? 3 : block_tok <= 128 ? 2 : 1);
-  if (const char* sp = std::getenv("TK100_SLOTS_PER_SM")) {
-    if (std::atoi(sp) > 0) slots = static_cast<long long>(ctx_.sm_count()) * std::atoi(sp);
+  if (ctx_.tuning().slots_per_sm > 0) {
+    slots = static_cast<long long>(ctx_.sm_count()) * ctx_.tuning().slots_per_sm;
   }
   int splits = static_cast<int>(slots / tiles);
   if (ctx_.forced_splits() > 0) splits = ctx_.forced_splits();
@@ -452,12 +466,12 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.out_rows = out_rows;
   p.k = columns;
   p.splits = splits;
-  p.cluster = cluster_reduce_enabled() ? 1 : 0;
+  p.cluster = ctx_.tuning().cluster != 0 ? 1 : 0;
   {
-    const char* dr = std::getenv("TK100_DEEP_RING");
+    const bool dr = ctx_.tuning().deep_ring >= 0;
     // unsplit launches with at most two CTAs per SM (an LM-head shard on 8 GPUs): measured
     // 26 us instead of 32 us for a 31 040-row shard; split launches are faster with three
-    p.deep_ring = dr ? (dr[0] - '0') : (splits == 1 && tiles <= 2LL * ctx_.sm_count());
+    p.deep_ring = dr ? ctx_.tuning().deep_ring : (splits == 1 && tiles <= 2LL * ctx_.sm_count());
     // between three and four CTAs per SM worth of tiles: the 3-stage ring, four CTAs per SM, one
     // wave (a 4-way LM-head shard: 485 tiles on 148 SMs)
     if (!dr && splits == 1 && block_tok == 16 && tiles > 3LL * ctx_.sm_count() &&
@@ -469,8 +483,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     // Queueing the CTA's weight slice at L2 before the ring starts looked good only while the
     // rotating weight copies of the measurement still hit L2; on cold weights it costs
     // (N = 12288, M = 1: 12.7 -> 14.0 us), so it stays an experiment switch.
-    const char* lp = std::getenv("TK100_L2_PREFETCH");
-    p.l2_prefetch = lp ? std::atoi(lp) : 0;
+    p.l2_prefetch = ctx_.tuning().l2_prefetch;
   }
   p.act_scales = activation_scales;
   p.w_scales = weight_scales;
@@ -483,6 +496,11 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.status = ctx_.status_word();
   p.debug = debug_flags();
   ctx_.count_launch();
+  {
+    // the ring variant launch_fp8_projection picks for this tile size
+    const int ring = (block_tok <= 32 && p.deep_ring == 1) ? 1 : (block_tok <= 16 && p.deep_ring == 2) ? 2 : 0;
+    ctx_.note_route("fp8_projection_kernel", block_tok, ring, splits, p.cluster && splits > 1);
+  }
   TK100_TRY(ctx_.check(launch_fp8_projection(stream, block_tok, map_w, map_a, p),
                        "launching the FP8 projection"));
   if (pairs) {
@@ -584,14 +602,13 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
 
   // Prefill shapes: CTA pairs (256-row x 256-token pair tiles) halve the operand bytes per MAC.
   {
-    const char* pe = std::getenv("TK100_PAIR");
-    const char* pm = std::getenv("TK100_PAIR_MIN_ROWS");
-    const int min_rows = pm ? std::atoi(pm) : 1024;
+    const int pe = ctx_.tuning().nvfp4_pair;
+    const int min_rows = ctx_.tuning().nvfp4_pair_min_rows;
     // Off unless TK100_PAIR=1 (down) or 2 (gate_up too): with two CTAs per SM the 128 x 128
     // tiles of the plain kernel overlap one CTA's epilogue with the other's loop and lose less
     // to the last wave (down at M = 2048: 149 us, CTA pairs 191 us).
-    const bool allowed = pe && (pe[0] == '1' || pe[0] == '2');
-    const bool this_op = gate_up ? (pe && pe[0] == '2') : (out_rows % 256 == 0);
+    const bool allowed = pe == 1 || pe == 2;
+    const bool this_op = gate_up ? pe == 2 : (out_rows % 256 == 0);
     if (allowed && this_op && rows >= min_rows) {
       const uint64_t w_rows = static_cast<uint64_t>(out_rows) * (gate_up ? 2 : 1);
       const uint64_t chunks_per_tile = static_cast<uint64_t>(columns / 64);
@@ -614,6 +631,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
       q.status = ctx_.status_word();
       q.debug = debug_flags();
       ctx_.count_launch();
+      ctx_.note_route("nvfp4_pair_kernel", gate_up ? 1 : 0, 0, 1, 1);
       TK100_TRY(ctx_.check(launch_nvfp4_pair(stream, gate_up, map_w, map_a, map_wsf, map_asf, q),
                            "launching the NVFP4 pair projection"));
       return quantise_after();
@@ -655,14 +673,11 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   p.out_rows = out_rows;
   p.k = columns;
   p.splits = splits;
-  p.cluster = cluster_reduce_enabled() ? 1 : 0;
+  p.cluster = ctx_.tuning().cluster != 0 ? 1 : 0;
   p.up_row_offset = gate_up ? out_rows : 0;
-  {
-    // Queueing the slice at L2 first does not pay (measured at M = 1: gate/up 20.7 -> 22.0 us,
-    // down 13.4 -> 14.9 us), so only TK100_NVFP4_L2_PREFETCH=n turns it on.
-    const char* lp = std::getenv("TK100_NVFP4_L2_PREFETCH");
-    p.l2_prefetch = lp ? std::atoi(lp) : 0;
-  }
+  // Queueing the slice at L2 first does not pay (measured at M = 1: gate/up 20.7 -> 22.0 us,
+  // down 13.4 -> 14.9 us), so only TK100_NVFP4_L2_PREFETCH=n turns it on.
+  p.l2_prefetch = ctx_.tuning().nvfp4_l2_prefetch;
   p.w_scales = weight_scales;
   p.a_scales = activation_scales;
   // the reference passes 1/divisor to its kernel (nvfp4/swiglu.rs:541); both divisors here
@@ -679,10 +694,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   // M = 1 24.4 -> 20.7 us, M = 256 51.6 -> 45.2 us, M = 2048 368 -> 318 us.  TK100_SWIGLU_PAIRS=0
   // selects the fused kernel.
   bool as_pairs = false;
-  if (gate_up) {
-    const char* ps = std::getenv("TK100_SWIGLU_PAIRS");
-    as_pairs = !(ps && ps[0] == '0');
-  }
+  if (gate_up) as_pairs = ctx_.tuning().swiglu_pairs != 0;
   if (as_pairs) {
     p.pair_swiglu = 1;
     p.splits = 1;
@@ -697,6 +709,8 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
     p.q_divisor = next->divisor;
   }
   ctx_.count_launch();
+  ctx_.note_route("nvfp4_gemm_kernel", block_tok, gate_up && !as_pairs ? 1 : 0, p.splits,
+                  as_pairs || (p.cluster && p.splits > 1));
   TK100_TRY(ctx_.check(launch_nvfp4_gemm(stream, block_tok, gate_up && !as_pairs, map_w, map_a, p),
                        "launching the NVFP4 projection"));
   return in_epilogue ? TK100_OK : quantise_after();
@@ -757,6 +771,8 @@ tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* 
 }
 
 uint64_t tk100_launch_count(const tk100_ctx* ctx) { return ctx ? ctx->impl->launches() : 0; }
+
+const char* tk100_last_kernel(tk100_ctx* ctx) { return ctx ? ctx->impl->last_kernel() : ""; }
 
 tk100_status tk100_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
                             const uint16_t* weight, uint16_t* output) {
@@ -910,17 +926,22 @@ tk100_status tk100_argmax_exchange(tk100_ctx* ctx, tk100_stream stream, int rows
 namespace {
 struct PeerSumLayout {
   long long chunk;       // two-shot chunk for `capacity` values
-  size_t result_offset, flag_offset, bytes;
+  long long one_shot;    // one-shot slot size in values
+  size_t one_shot_offset, result_offset, flag_offset, bytes;
 };
 // Layout of a peer-sum exchange buffer sized for `capacity` values on `world` ranks.
 PeerSumLayout peer_sum_layout(long long capacity, int world) {
   auto up = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
   PeerSumLayout l{};
   l.chunk = static_cast<long long>(up(static_cast<size_t>((capacity + world - 1) / world), 8));
-  const long long one_shot = capacity < tk100::kPeerSumOneShotElems ? capacity : tk100::kPeerSumOneShotElems;
-  const size_t slots_two = static_cast<size_t>(world) * l.chunk * sizeof(float);
-  const size_t slots_one = 2 * static_cast<size_t>(world) * one_shot * sizeof(float);
-  l.result_offset = up(slots_two > slots_one ? slots_two : slots_one, 256);
+  l.one_shot = capacity < tk100::kPeerSumOneShotElems ? capacity : tk100::kPeerSumOneShotElems;
+  l.one_shot = static_cast<long long>(up(static_cast<size_t>(l.one_shot), 8));
+  // two-shot slots first, one-shot slots behind them: disjoint, so a rank that has moved on to a
+  // step of the other form cannot touch what a slower rank still reads
+  const size_t slots_two = up(static_cast<size_t>(world) * l.chunk * sizeof(float), 256);
+  const size_t slots_one = 2 * static_cast<size_t>(world) * l.one_shot * sizeof(float);
+  l.one_shot_offset = slots_two;
+  l.result_offset = up(slots_two + slots_one, 256);
   l.flag_offset = l.result_offset + up(2 * static_cast<size_t>(world) * l.chunk * sizeof(uint16_t), 256);
   l.bytes = l.flag_offset + 256;
   return l;
@@ -963,6 +984,9 @@ tk100_status tk100_peer_sum_bf16(tk100_ctx* ctx, tk100_stream stream, size_t val
   q.chunk = ((q.elems + world - 1) / world + 7) / 8 * 8;
   q.partial = partial;
   q.output = output;
+  q.chunk_capacity = l.chunk;
+  q.one_shot_stride4 = l.one_shot / 4;
+  q.one_shot_offset = l.one_shot_offset;
   q.result_offset = l.result_offset;
   q.flag_offset = l.flag_offset;
   q.step_counter = ctx->impl->peer_sum_state();

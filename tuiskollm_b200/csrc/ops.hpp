@@ -10,6 +10,7 @@
 
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 #include "../../include/tuisko_sm100.h"
 #include "kernels.h"
@@ -19,6 +20,25 @@ namespace tk100 {
 // Result of a launch: the reference's GpuResult<()> flattened to a status code; the
 // message is kept on the context.
 using Status = tk100_status;
+
+// Route selectors for A/B measurements, read from TK100_* environment variables ONCE, when the
+// context is created; no launch function reads the environment.  -1 / 0 = the library's choice.
+struct Tuning {
+  int splits = 0;             // TK100_SPLITS: forced K split
+  int block_tok = 0;          // TK100_BLOCK_TOK: forced token tile
+  int slots_per_sm = 0;       // TK100_SLOTS_PER_SM: CTA slots per SM assumed by the split choice
+  int deep_ring = -1;         // TK100_DEEP_RING: ring variant of the FP8 projection
+  int l2_prefetch = 0;        // TK100_L2_PREFETCH: FP8 weight k-blocks queued at L2 first
+  int nvfp4_l2_prefetch = 0;  // TK100_NVFP4_L2_PREFETCH
+  int cluster = 1;            // TK100_CLUSTER=0: split-K through global scratch instead of DSMEM
+  int fp8_pair = 1;           // TK100_FP8_PAIR: 0 off, 1 from 32 pair CTAs, 2 always
+  int fp8_pair_min_rows = 256;
+  int nvfp4_pair = 0;         // TK100_PAIR: 1 down, 2 gate_up too (cta_group::2 variant)
+  int nvfp4_pair_min_rows = 1024;
+  int swiglu_pairs = 1;       // TK100_SWIGLU_PAIRS=0: one CTA holds the gate and the up tile
+  int fused_exchange = 1;     // TK100_FUSED_EXCHANGE=0: argmax exchange as its own launch only
+  static Tuning from_environment();
+};
 
 class Context {
  public:
@@ -49,10 +69,17 @@ class Context {
   uint32_t* status_word() const { return status_; }
   unsigned int* exchange_step() const { return exchange_step_; }
   unsigned int* peer_sum_state() const { return peer_sum_state_; }
-  int forced_splits() const { return forced_splits_; }
-  int forced_block_tok() const { return forced_block_tok_; }
+  const Tuning& tuning() const { return tuning_; }
+  int forced_splits() const { return tuning_.splits; }
+  int forced_block_tok() const { return tuning_.block_tok; }
   void count_launch(int n = 1) { launches_ += static_cast<uint64_t>(n); }
   uint64_t launches() const { return launches_; }
+  // Which kernel instantiation the last projection launch took (for reports and route tests):
+  // a pointer and four integers per launch, formatted only when somebody asks.
+  void note_route(const char* family, int a, int b, int splits, int cluster) {
+    route_ = {family, a, b, splits, cluster};
+  }
+  const char* last_kernel();
 
  private:
   Context() = default;
@@ -65,12 +92,35 @@ class Context {
   uint32_t* status_ = nullptr;
   unsigned int* exchange_step_ = nullptr;  // device step counter of the peer argmax exchange
   unsigned int* peer_sum_state_ = nullptr;  // peer sum: [0] step counter, [1..3] phase tickets
-  int forced_splits_ = 0;
-  int forced_block_tok_ = 0;
+  Tuning tuning_;
   uint64_t launches_ = 0;
+  struct RouteNote {
+    const char* family = "";
+    int a = 0, b = 0, splits = 0, cluster = 0;
+  } route_;
+  std::string route_text_;
   std::string last_error_;
   void* encode_fn_ = nullptr;
-  std::unordered_map<std::string, CUtensorMap> maps_;
+  // Encoded tensor maps by (base, rows, row bytes, box rows | kind): weight planes are encoded
+  // on their first launch (or by tk100_register_plane) and found again by a hash look-up.
+  struct MapKey {
+    const void* base;
+    uint64_t rows, row_bytes;
+    uint32_t box_rows, kind;
+    bool operator==(const MapKey& o) const {
+      return base == o.base && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows &&
+             kind == o.kind;
+    }
+  };
+  struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+      uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+      h ^= (k.rows + 0x7F4A7C15u) * 0xC2B2AE3D27D4EB4Full;
+      h ^= (k.row_bytes << 17) ^ (static_cast<uint64_t>(k.box_rows) << 3) ^ k.kind;
+      return static_cast<size_t>(h ^ (h >> 29));
+    }
+  };
+  std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps_;
 };
 
 // tuisko-kernels-sm120/src/residual_norm.rs:382-508

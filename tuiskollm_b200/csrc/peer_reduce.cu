@@ -5,9 +5,15 @@
 // Every rank owns an exchange buffer that all peers can address (plain peer stores and loads;
 // no multicast object, no TMA).  Same layout on every rank:
 //
-//   [slots]    fp32 partials as delivered by the senders
-//   [results]  2 parities x BF16 sums of all chunks (two-shot form only)
-//   [flags]    2 kinds x world step numbers (kind 0: partials delivered, 1: results delivered)
+//   [two-shot slots]  world x chunk fp32 partials as delivered by the senders
+//   [one-shot slots]  2 parities x world x one-shot capacity fp32 partials
+//   [results]         2 parities x BF16 sums of all chunks (two-shot form only)
+//   [flags]           2 kinds x world step numbers (kind 0: partials delivered, 1: results delivered)
+//
+// Every region and every stride inside it is fixed by the buffer's CAPACITY, not by the size of
+// the call at hand, and the one-shot and two-shot slots are disjoint: a rank that is one step
+// ahead (a decode step of 5120 values behind a prefill chunk of 64 x 5120, say) can therefore
+// never store into memory that a slower rank still reads for the step before.
 //
 // Small sums (up to kOneShotElems values) go ONE-SHOT: every rank stores its whole partial into
 // every peer's slot [parity][sender], raises flag 0 there, waits for all senders' flags in its own
@@ -102,7 +108,8 @@ __global__ void __launch_bounds__(kThreads)
   if (q.one_shot) {
     // ---- deliver the whole partial to every rank's slot [parity][rank]
     for (int d = 0; d < world; ++d) {
-      float4* dst = reinterpret_cast<float4*>(peers.base[d]) + (static_cast<long long>(parity) * world + rank) * n4;
+      float4* dst = reinterpret_cast<float4*>(peers.base[d] + q.one_shot_offset) +
+                    (static_cast<long long>(parity) * world + rank) * q.one_shot_stride4;
       for (long long i = tid; i < n4; i += stride) dst[i] = src[i];
     }
     if (last_cta(q.tickets + 0, &s_last) && threadIdx.x < world) {
@@ -110,11 +117,12 @@ __global__ void __launch_bounds__(kThreads)
     }
     if (!wait_flags(my_flags, world, step, q.status, &s_ok)) return;
     // ---- add the senders' partials in rank order, round once
-    const float4* slots = reinterpret_cast<const float4*>(mine) + static_cast<long long>(parity) * world * n4;
+    const float4* slots = reinterpret_cast<const float4*>(mine + q.one_shot_offset) +
+                          static_cast<long long>(parity) * world * q.one_shot_stride4;
     for (long long i = tid; i < n4; i += stride) {
       float4 acc = __ldcv(slots + i);
       for (int s = 1; s < world; ++s) {
-        const float4 v = __ldcv(slots + static_cast<long long>(s) * n4 + i);
+        const float4 v = __ldcv(slots + static_cast<long long>(s) * q.one_shot_stride4 + i);
         acc.x = __fadd_rn(acc.x, v.x);
         acc.y = __fadd_rn(acc.y, v.y);
         acc.z = __fadd_rn(acc.z, v.z);
@@ -127,11 +135,12 @@ __global__ void __launch_bounds__(kThreads)
   }
 
   // -------------------------------------------------------------------- two-shot
-  const long long chunk4 = q.chunk >> 2;  // float4 per chunk; chunk is a multiple of 8
+  const long long chunk4 = q.chunk >> 2;          // float4 per chunk of this call (chunk % 8 == 0)
+  const long long slot4 = q.chunk_capacity >> 2;  // slot / result stride: the capacity's chunk
   // ---- chunk d of this rank's partial -> rank d, slot [rank]
   for (long long i = tid; i < n4; i += stride) {
     const long long d = i / chunk4, off = i - d * chunk4;
-    reinterpret_cast<float4*>(peers.base[d])[static_cast<long long>(rank) * chunk4 + off] = src[i];
+    reinterpret_cast<float4*>(peers.base[d])[static_cast<long long>(rank) * slot4 + off] = src[i];
   }
   if (last_cta(q.tickets + 0, &s_last) && threadIdx.x < world) {
     st_release_sys(reinterpret_cast<unsigned int*>(peers.base[threadIdx.x] + q.flag_offset) + rank, step);
@@ -145,7 +154,7 @@ __global__ void __launch_bounds__(kThreads)
     for (long long i = tid; i < len4; i += stride) {
       float4 acc = __ldcv(slots + i);
       for (int s = 1; s < world; ++s) {
-        const float4 v = __ldcv(slots + static_cast<long long>(s) * chunk4 + i);
+        const float4 v = __ldcv(slots + static_cast<long long>(s) * slot4 + i);
         acc.x = __fadd_rn(acc.x, v.x);
         acc.y = __fadd_rn(acc.y, v.y);
         acc.z = __fadd_rn(acc.z, v.z);
@@ -154,7 +163,7 @@ __global__ void __launch_bounds__(kThreads)
       const uint2 r = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
       for (int d = 0; d < world; ++d) {
         uint2* res = reinterpret_cast<uint2*>(peers.base[d] + q.result_offset) +
-                     static_cast<long long>(parity) * world * chunk4;
+                     static_cast<long long>(parity) * world * slot4;
         res[begin4 + i] = r;
       }
     }
@@ -166,7 +175,7 @@ __global__ void __launch_bounds__(kThreads)
   // ---- all chunks are here: result region -> output
   {
     const uint2* res = reinterpret_cast<const uint2*>(mine + q.result_offset) +
-                       static_cast<long long>(parity) * world * chunk4;
+                       static_cast<long long>(parity) * world * slot4;
     for (long long i = tid; i < n4; i += stride) reinterpret_cast<uint2*>(q.output)[i] = __ldcv(res + i);
   }
   if (last_cta(q.tickets + 2, &s_last) && threadIdx.x == 0) *q.step_counter = step;

@@ -91,6 +91,7 @@ tk100_status setup_current_device(DeviceState** out) {
       return fail(TK100_ERR_MODULE, "[gpu.module] preparing the FP8 projection routes failed (%lld)",
                   e);
     }
+    read_process_switches();
     st.scratch = static_cast<unsigned char*>(ptr);
     st.ready = true;
   }
@@ -194,9 +195,11 @@ extern "C" TK100_API tk100_status tk100_fp8_projection_static(
 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   unsigned char* tail = st->scratch + kStaticPartialBytes;
-  // The scratch keeps whatever the previous call left: tickets and the fault word must
-  // start at zero (partials are fully rewritten before they are read).
-  cudaError_t e = cudaMemsetAsync(tail, 0, kStaticTailBytes, cs);
+  // The scratch keeps whatever the previous call left: the tickets must start at zero
+  // (partials are fully rewritten before they are read).  The fault word behind the tickets is
+  // NOT cleared here: it collects the faults of all calls until
+  // tk100_fp8_projection_static_status reads and clears it.
+  cudaError_t e = cudaMemsetAsync(tail, 0, kStaticCounters * sizeof(unsigned int), cs);
   if (e != cudaSuccess) {
     return fail(TK100_ERR_DRIVER, "[gpu.driver] clearing the static scratch failed (%lld)", e);
   }
@@ -217,4 +220,21 @@ extern "C" TK100_API tk100_status tk100_fp8_projection_static(
                 e);
   }
   return TK100_OK;
+}
+
+extern "C" TK100_API tk100_status tk100_fp8_projection_static_status(tk100_stream stream,
+                                                                     uint32_t* word) {
+  using namespace tk100;
+  g_message = nullptr;
+  g_message_capacity = 0;
+  if (!word) return TK100_ERR_LAUNCH;
+  DeviceState* st = nullptr;
+  tk100_status s = setup_current_device(&st);
+  if (s != TK100_OK) return s;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  unsigned char* fault = st->scratch + kStaticPartialBytes + kStaticCounters * sizeof(unsigned int);
+  cudaError_t e = cudaMemcpyAsync(word, fault, sizeof(uint32_t), cudaMemcpyDeviceToHost, cs);
+  if (e == cudaSuccess) e = cudaMemsetAsync(fault, 0, sizeof(uint32_t), cs);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
+  return e == cudaSuccess ? TK100_OK : TK100_ERR_DRIVER;
 }

@@ -87,6 +87,11 @@ class Context:
     def launch_count(self) -> int:
         return int(self._lib.tk100_launch_count(self.handle))
 
+    @property
+    def last_kernel(self) -> str:
+        """Kernel instantiation of the last projection launch (``tk100_last_kernel``)."""
+        return (self._lib.tk100_last_kernel(self.handle) or b"").decode()
+
 
 class ResidualNormOp:
     """tuisko-kernels-sm120/src/residual_norm.rs:382-508."""
@@ -317,3 +322,14 @@ def fp8_projection_static(stream, rows, out_rows, columns, activation_codes, act
                                              message, len(message))
     if status != 0:
         raise GpuError(status, message.value.decode())
+
+
+def fp8_projection_static_status(stream=None) -> int:
+    """Reads and clears the fault word of the static scratch on the current device (the
+    ``TK100_DEVICE_*`` bits that :meth:`Context.device_status` reports for the context route)."""
+    lib = _lib.load()
+    word = C.c_uint32(0)
+    status = lib.tk100_fp8_projection_static_status(_stream(stream), C.byref(word))
+    if status != 0:
+        raise GpuError(status, "[gpu.driver] reading the static scratch's fault word failed")
+    return word.value
