@@ -142,6 +142,40 @@ def test_pair_route_matches_oracle_and_one_cta_route(tk, oracle, out_rows, rows,
     assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-4)
 
 
+@pytest.mark.parametrize("out_rows,rows", [(8192, 512), (8192, 2048), (12288, 512), (12288, 2048)])
+def test_benchmarked_prefill_shapes_sampled_tiles(tk, ctx, oracle, out_rows, rows):
+    """The prefill shapes the benchmark times (K = 5120, M = 512 / 2048, N = 8192 / 12288) run on
+    the CTA-pair kernel; the f64 oracle cannot do the whole product in seconds, so whole
+    128 x 128 tiles are sampled -- first, last and two inner weight tiles x first, an inner and
+    the last token tile -- after the activation codes and scales of ALL rows are checked bit for
+    bit."""
+    from tuiskollm_b200 import synth
+
+    hidden = 5120
+    x = synth.torch_normal_bf16(44, rows, (rows, hidden), "cuda")
+    w, s = synth.torch_fp8_weights(44, out_rows, out_rows, hidden, "cuda")
+    planes = Planes(rows + 1, hidden, out_rows)
+    tk.GdnInputProjectionOp(ctx, out_rows).launch(None, rows, x, planes.codes, planes.scales, w, s,
+                                                  planes.out)
+    torch.cuda.synchronize()
+    assert ctx.last_kernel.startswith("fp8_pair_kernel"), ctx.last_kernel
+    xb = _u16(x)
+    oc, os_ = oracle.quantize_e4m3(xb)
+    assert np.array_equal(host(planes.codes)[:rows], oc)
+    assert np.array_equal(host(planes.scales)[:rows].view(np.uint32), os_.view(np.uint32))
+    got = _u16(planes.out)
+    n_tiles, m_tiles = out_rows // 128, rows // 128
+    for tt in sorted({0, m_tiles // 2 + 1, m_tiles - 1}):
+        ts = slice(tt * 128, (tt + 1) * 128)
+        for wt in sorted({0, 1, n_tiles // 2, n_tiles - 1}):
+            rs = slice(wt * 128, (wt + 1) * 128)
+            exp = oracle.fp8_projection(oc[ts], os_[ts], host(w[rs]), _u16(s[rs]))
+            check_close(got[ts, rs], exp, 1 / 16, 0.01, f"tile ({tt}, {wt})")
+            assert max_relative_error(got[ts, rs], exp, 0.25) <= 1e-2
+    planes.check_inactive(rows)
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 8])
 @pytest.mark.parametrize("block_tok", [0, 64])
 def test_split_k_is_exact_and_deterministic(tk, oracle, splits, block_tok):

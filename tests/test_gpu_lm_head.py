@@ -189,13 +189,15 @@ def test_vocab_shards_merge_to_the_single_gpu_answer(tk, ctx, oracle, shards):
     assert got["index"][1] == min(b, other)
 
 
-def test_full_vocabulary_properties(tk, ctx, oracle):
-    """Full LM-head size (248320 x 5120, M = 1): too large for the CPU oracle as a whole, so
-    check (1) the device argmax equals greedy_index over the BF16 plane it wrote, (2) a
-    sample of 512 rows (including both ends and the last tile) against the f64 oracle."""
+@pytest.mark.parametrize("rows", [1, 4, 32])
+def test_full_vocabulary_properties(tk, ctx, oracle, rows):
+    """Full LM-head size (248320 x 5120, M = 1, 4, 32: the 16- and 32-token epilogues): too large
+    for the CPU oracle as a whole, so check (1) for every token the device argmax equals
+    greedy_index over the BF16 plane it wrote, (2) a sample of 512 rows (including both ends and
+    the last tile) against the f64 oracle, for all tokens."""
     from tuiskollm_b200 import synth
 
-    hidden, vocab, rows = 5120, 248320, 1
+    hidden, vocab = 5120, 248320
     wc, ws = synth.torch_fp8_weights(11, 1, vocab, hidden, "cuda")
     xb = synth.normal_bf16(11, 2, (rows, hidden))
     _, p, scratch, launch = lm_head(tk, ctx, dev(xb.view(np.int16)), wc, ws.view(torch.int16), rows,
@@ -204,7 +206,9 @@ def test_full_vocabulary_properties(tk, ctx, oracle):
     torch.cuda.synchronize()
     logits = _u16(p["out"])
     got = pairs_of(p["pairs"], rows)
-    assert got["index"][0] == oracle.greedy_index(logits[0])
+    for t in range(rows):
+        assert got["index"][t] == oracle.greedy_index(logits[t]), t
+    assert np.array_equal(oracle.f32_to_bf16(host(p["f32"])[:rows]), logits)
     rng = np.random.default_rng(0)
     sample = np.unique(np.concatenate([rng.integers(0, vocab, 500), [0, 1, 127, 128, vocab - 129, vocab - 128, vocab - 1]]))
     idx = torch.from_numpy(sample).cuda()

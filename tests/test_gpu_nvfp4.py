@@ -321,10 +321,9 @@ def test_gate_up_cluster_pairs_and_fused_kernel_agree(tk, oracle, rows, monkeypa
 
 
 def test_activation_quantiser_rounding_ties(tk, oracle):
-    """The quantiser decides each E2M1 code by comparing x * divisor with midpoint * scale instead
-    of dividing; values that sit exactly on the rounding midpoints (ties to the even code), one
-    BF16 step beside them, and beyond the largest magnitude must come out as the oracle's
-    divide-then-round does."""
+    """Values that sit exactly on the E2M1 rounding midpoints after the quantiser's IEEE divide
+    (ties go to the even code), one BF16 step beside them, and beyond the largest magnitude must
+    come out as the oracle's divide-then-round does."""
     k = 64
     mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
     mid_bits = mids.view(np.uint32) >> 16
@@ -473,6 +472,38 @@ def test_full_size_prefill_sampled_tiles(tk, ctx, oracle):
             exp = oracle.silu_mul(dots[:, :128], dots[:, 128:])
             got = _u16(mid)[tt * 128:(tt + 1) * 128, rows_g]
             assert max_relative_error(got, exp, 4 * float(np.abs(exp).mean())) <= 1e-2
+    assert ctx.device_status() == 0
+
+
+def test_full_size_prefill_down_sampled_tiles(tk, ctx, oracle):
+    """Configuration 4's down projection at full size (M = 2048, 5120 x 17408: unsplit 128-token
+    tiles over 68 k-blocks): first, last and two inner weight tiles x first and last token tile
+    against the W4A4 oracle, the activation quantiser bit for bit on those token tiles."""
+    from tuiskollm_b200 import synth
+
+    rows = 2048
+    x = synth.torch_normal_bf16(13, 1, (rows, INTER), "cuda")
+    dn_codes, dn_scales, dn_div = synth.torch_nvfp4_weights(13, 2, HIDDEN, INTER, "cuda")
+    a_div = float(np.float32(448.0 * 6.0 / 6.0))
+    codes, scales = act_planes(tk, rows, INTER)
+    out = sentinel_plane((rows, HIDDEN), torch.int16)
+    tk.Nvfp4DownOp(ctx).launch(None, rows, x, dn_codes, dn_scales, dn_div, out,
+                               activation_codes=codes, activation_scales=scales,
+                               input_global_divisor=a_div)
+    torch.cuda.synchronize()
+    groups = INTER // 16
+    xb = _u16(x.view(torch.int16))
+    got = _u16(out)
+    for tt in (0, rows // 128 - 1):
+        ts = slice(tt * 128, (tt + 1) * 128)
+        oc, osc = oracle.nvfp4_quantize(xb[ts], a_div)
+        assert np.array_equal(host(codes[ts]), oc)
+        assert np.array_equal(host(scales[tt * 128 * groups:(tt + 1) * 128 * groups]), osc)
+        for wt in (0, 13, 22, HIDDEN // 128 - 1):
+            rs = slice(wt * 128, (wt + 1) * 128)
+            exp = oracle.nvfp4_w4a4_dot(oc, osc, a_div, host(dn_codes[rs]),
+                                        host(dn_scales[wt * 128 * groups:(wt + 1) * 128 * groups]), dn_div)
+            assert max_relative_error(got[ts, rs], exp, 4 * float(np.abs(exp).mean())) <= 1e-2, (tt, wt)
     assert ctx.device_status() == 0
 
 
