@@ -9,7 +9,9 @@ vocabulary is split contiguously over the N ranks, every rank streams its shard 
 step and the per-shard (max, index) pairs are exchanged over NVLink and merged.
 
 One step = quantise the hidden rows + stream the weight shard through the tcgen05
-projection kernel + argmax finalize (N = 1) or the fused peer exchange + merge (N > 1).
+projection kernel + argmax finalize (N = 1) or peer exchange + merge (N > 1) -- ONE kernel
+launch: at decode sizes every CTA quantises the hidden rows itself and the last CTA to finish
+unpacks, exchanges and merges the maxima.
 
   value     whole-job algorithmic GB/s with the hidden rows resident in HBM, from EXACTLY
             `--steps` graph replays between two barriers (max over ranks)
@@ -1134,7 +1136,9 @@ def run_native(args):
             try:
                 from tuiskollm_b200 import dist as tkd
                 _xbuf, _xhdl, peer_addresses = tkd.alloc_exchange(m, world, torch.device("cuda", local))
-                exchange = "peer stores over NVLink fused with the merge (one kernel)"
+                exchange = ("peer stores over NVLink fused with the merge (one kernel behind the projection)"
+                            if args.split_exchange else
+                            "peer stores over NVLink and merge by the projection kernel's last CTA")
             except Exception as exc:  # symmetric memory unavailable: keep the NCCL route
                 exchange += f" (peer exchange unavailable: {type(exc).__name__}: {exc})"[:300]
     # all ranks must agree on the route
@@ -1146,8 +1150,12 @@ def run_native(args):
 
     def step():
         if peer_addresses is not None:
-            op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, None)
-            op.exchange(None, m, world, rank, scratch, peer_addresses, merged)
+            if args.split_exchange:  # projection, then the exchange + merge as its own launch
+                op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, None)
+                op.exchange(None, m, world, rank, scratch, peer_addresses, merged)
+            else:  # one launch: quantise + project + argmax + peer exchange + merge
+                op.launch_sharded(None, m, x, codes, scales, wc, ws, None, logits, scratch, world,
+                                  rank, peer_addresses, merged)
             return
         op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, pairs)
         if world > 1:
@@ -1203,7 +1211,11 @@ def run_native(args):
     barrier()
     # The reference's protocol on the same step: 40 samples of `inner` replays each (at least
     # half a second of load in total, which also gives the clock sampler something to see).
-    inner = max(1, min(256, int(0.5e3 / SAMPLES / max(ms / args.steps, 1e-3)) + 1))
+    # (every rank must replay the same number of steps: the count comes from the slowest rank's time)
+    ms_all = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms_all, op=dist.ReduceOp.MAX)
+    inner = max(1, min(256, int(0.5e3 / SAMPLES / max(float(ms_all.item()) / args.steps, 1e-3)) + 1))
     sample_us = []
     for _ in range(SAMPLES):
         if world > 1:
@@ -1350,8 +1362,8 @@ def run_native(args):
                          "traffic_source": "ncu dram read+write bytes of this kernel at vocab "
                                            "248320, M=1 (1 272 757 504 B), scaled by algorithmic bytes",
                          "peak_kind": peak_kind,
-                         "kernel": kernel_name + " (+ argmax finalize, < 2 us)" if world == 1
-                                   else kernel_name,
+                         "kernel": kernel_name + " (quantiser in its prologue, finalize / exchange "
+                                                 "in its last CTA)",
                          "algorithmic_bytes": shard_bytes,
                          "us_per_launch": proj_ms * 1e3, "frac_of_8TBs": achieved / NOMINAL_HBM_GBS},
             "clocks": clocks,
@@ -1405,6 +1417,8 @@ def main():
                     help="tensor-parallel slice: NCCL all-reduce + rounding kernel instead of the peer sum")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="N > 1: gather the pairs with NCCL instead of the fused peer exchange")
+    ap.add_argument("--split-exchange", action="store_true",
+                    help="N > 1: the peer exchange as a launch of its own behind the projection")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--case", default="",

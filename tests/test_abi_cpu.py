@@ -96,3 +96,38 @@ def test_synth_nvfp4_weights_match_oracle_definition(oracle):
     ocodes, oscales = oracle.nvfp4_quantize(oracle.f32_to_bf16(w), float(div))
     assert np.array_equal(codes, ocodes) and np.array_equal(scales, oscales)
     assert scales.max() <= 0x7E and div == np.float32(448.0 * 6.0) / np.abs(w).max()
+
+
+def test_rust_ffi_declares_exactly_the_header_symbols():
+    """The Rust side of the boundary (crates/tuisko-gpu/src/ffi_sm100.rs, not compiled in this
+    image) must declare every exported function, no more and no fewer, and the crate's build
+    script must compile the same sources as the Python build."""
+    from tuiskollm_b200 import build as cuda_build
+
+    ffi = open(os.path.join(ROOT, "crates", "tuisko-gpu", "src", "ffi_sm100.rs")).read()
+    declared = sorted(set(re.findall(r"pub fn (tk100_[a-z0-9_]+)\s*\(", ffi)))
+    assert declared == header_symbols()
+    build_rs = open(os.path.join(ROOT, "crates", "tuisko-kernels-sm100", "build.rs")).read()
+    listed = re.findall(r'"([a-z0-9_]+\.cu)"', build_rs.split("const SOURCES", 1)[1].split("];", 1)[0])
+    assert listed == cuda_build.SOURCES
+    lib_rs = open(os.path.join(ROOT, "crates", "tuisko-kernels-sm100", "src", "lib.rs")).read()
+    used = set(re.findall(r"ffi::(tk100_[a-z0-9_]+)", lib_rs))
+    assert used <= set(declared), used - set(declared)
+
+
+def test_no_launch_function_reads_the_environment():
+    """Route selectors are read once (Tuning::from_environment at tk100_create,
+    read_process_switches); nothing else in the library calls getenv."""
+    csrc = os.path.join(ROOT, "tuiskollm_b200", "csrc")
+    hits = []
+    for name in sorted(os.listdir(csrc)):
+        text = open(os.path.join(csrc, name)).read()
+        for m in re.finditer(r"getenv", text):
+            line = text[:m.start()].count("\n") + 1
+            hits.append((name, line))
+    allowed = {"ops.cu", "norm_quant.cu"}
+    assert {n for n, _ in hits} <= allowed, hits
+    ops = open(os.path.join(csrc, "ops.cu")).read()
+    assert ops.count("getenv") == 1  # inside env_int(), which only Tuning::from_environment calls
+    body = ops.split("Tuning Tuning::from_environment()", 1)[1].split("\n}\n", 1)[0]
+    assert ops.count("env_int(") == body.count("env_int(") + 1  # + its definition

@@ -59,6 +59,7 @@ def test_lm_head_matches_oracle_and_greedy_rule(tk, ctx, oracle, rows):
     torch.cuda.synchronize()
     oc, os_ = oracle.quantize_e4m3(xb)
     assert np.array_equal(host(p["codes"])[:rows], oc)
+    assert np.array_equal(host(p["scales"])[:rows].view(np.uint32), os_.view(np.uint32))
     exp = oracle.fp8_projection(oc, os_, wc, ws)
     logits = _u16(p["out"])[:rows]
     check_close(logits, exp, 1 / 16, 0.01, "BF16 logits")
@@ -90,6 +91,76 @@ def test_lm_head_matches_oracle_and_greedy_rule(tk, ctx, oracle, rows):
     torch.cuda.synchronize()
     for k, v in p.items():
         assert np.array_equal(host(v.view(torch.uint8)), eager[k]), k
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 3, 4, 5])
+def test_fused_quantiser_and_tail_equal_the_separate_launches(tk, oracle, rows, monkeypatch):
+    """Up to 4 rows the projection kernel quantises the hidden rows in its prologue and its last
+    CTA unpacks the maxima; TK100_FUSED_QUANT=0 / TK100_FUSED_TAIL=0 keep the quantiser and the
+    finalizer as launches of their own.  Every plane must come out bit-identical on both routes,
+    eagerly and as graph replays, with and without split K (the 4160-row plane is unsplit with the
+    longer ring, the 1040-row plane splits K eight ways)."""
+    from tuiskollm_b200 import synth
+
+    hidden = 5120
+    for vocab in (4096 + 64, 1040):
+        xb = synth.normal_bf16(78, rows, (rows, hidden))
+        wc, ws = synth.fp8_weights(78, 100 + vocab, vocab, hidden)
+        x, w, s = dev(xb.view(np.int16)), dev(wc), dev(ws.view(np.int16))
+        planes = {}
+        for route, (fq, ft) in (("fused", ("1", "1")), ("separate", ("0", "0"))):
+            monkeypatch.setenv("TK100_FUSED_QUANT", fq)
+            monkeypatch.setenv("TK100_FUSED_TAIL", ft)
+            c = tk.Context(device=0)
+            launches = c.launch_count
+            op, p, scratch, launch = lm_head(tk, c, x, w, s, rows, vocab, 0, rows + 1, hidden)
+            launch()
+            torch.cuda.synchronize()
+            expect_launches = 1 if (route == "fused" and rows <= 4) else (2 if route == "fused" else 3)
+            assert c.launch_count - launches == expect_launches, (route, rows)
+            for name in ("codes", "scales", "out", "f32", "pairs"):
+                assert_inactive_untouched(p[name], rows)
+            assert int(scratch.abs().sum()) == 0, "argmax scratch must be left zero"
+            eager = {k: host(v.view(torch.uint8)).copy() for k, v in p.items()}
+            g = graph_replay(launch)
+            for v in p.values():
+                v.view(torch.uint8).fill_(0xA5)
+            g.replay()
+            g.replay()
+            torch.cuda.synchronize()
+            for k, v in p.items():
+                assert np.array_equal(host(v.view(torch.uint8)), eager[k]), (route, k)
+            assert c.device_status() == 0
+            planes[route] = eager
+        for k in planes["fused"]:
+            assert np.array_equal(planes["fused"][k], planes["separate"][k]), (vocab, k)
+        oc, os_ = oracle.quantize_e4m3(xb)
+        assert np.array_equal(planes["fused"]["codes"][:rows], oc)
+        assert np.array_equal(planes["fused"]["scales"][: 4 * rows].view(np.uint32), os_.view(np.uint32))
+
+
+def test_sharded_entry_on_one_rank_equals_the_plain_entry(tk, ctx, oracle):
+    """tk100_fp8_lm_head_sharded with world = 1 (its own buffer list empty) gives the pairs of
+    tk100_fp8_lm_head, step after step, and leaves the scratch zero."""
+    from tuiskollm_b200 import synth
+
+    hidden, vocab, rows = 5120, 2048 + 64, 2
+    wc, ws = synth.fp8_weights(79, 2, vocab, hidden)
+    w, s = dev(wc), dev(ws.view(np.int16))
+    for step in range(3):
+        xb = synth.normal_bf16(79, 10 + step, (rows, hidden))
+        x = dev(xb.view(np.int16))
+        op, p, scratch, launch = lm_head(tk, ctx, x, w, s, rows, vocab, 0, rows, hidden, f32=False)
+        launch()
+        merged = sentinel_plane((rows, 2), torch.int32)
+        op.launch_sharded(None, rows, x, p["codes"], p["scales"], w, s, p["out"], None, scratch, 1, 0,
+                          None, merged)
+        torch.cuda.synchronize()
+        a, b = pairs_of(merged, rows), pairs_of(p["pairs"], rows)
+        assert np.array_equal(a["index"], b["index"]) and np.array_equal(a["value"], b["value"])
+        assert a["index"][0] == oracle.greedy_index(_u16(p["out"])[0])
+        assert int(scratch.abs().sum()) == 0
     assert ctx.device_status() == 0
 
 

@@ -86,7 +86,13 @@ def _exchange_worker(rank, port):
 
     w, s = set_weights(wc, ws)
 
+    state = {"one_launch": False}
+
     def step():
+        if state["one_launch"]:  # projection, argmax, exchange and merge in one kernel
+            op.launch_sharded(None, rows, x, codes, scales, w, s, logits, None, scratch, WORLD, rank,
+                              peers, merged)
+            return
         op.launch(None, rows, x, codes, scales, w, s, logits, None, scratch, None)
         op.exchange(None, rows, WORLD, rank, scratch, peers, merged)
 
@@ -101,8 +107,8 @@ def _exchange_worker(rank, port):
         # ... and equal to greedy_index over the whole vocabulary's BF16 logits as the two
         # shards wrote them (the selection rule the host sampler applies to that plane), which in
         # turn lie within tolerance of the CPU oracle's projection
-        parts = [torch.empty_like(logits) for _ in range(WORLD)]
-        dist.all_gather(parts, logits)
+        parts = [torch.empty_like(logits).view(torch.uint8) for _ in range(WORLD)]
+        dist.all_gather(parts, logits.view(torch.uint8))  # NCCL has no 16-bit integer type
         plane = np.concatenate([p.cpu().numpy().view(np.uint16) for p in parts], axis=1)
         for t in range(rows):
             assert int(got[t, 1]) == O.greedy_index(plane[t]), f"{tag}: token {t}"
@@ -113,7 +119,10 @@ def _exchange_worker(rank, port):
         return got
 
     winners = set()
-    for i in range(4):  # eager steps, fresh hidden rows every step, rank 1 late on odd steps
+    for i in range(8):  # eager steps, fresh hidden rows every step, rank 1 late on odd steps;
+        # the two forms of the exchange (own launch / inside the projection) alternate in pairs and
+        # share the device step counter
+        state["one_launch"] = (i // 2) % 2 == 1
         xb = synth.normal_bf16(61, 10 + i, (rows, hidden))
         x.copy_(up(xb.view(np.int16)))
         if rank == 1 and i % 2 == 1:
@@ -139,7 +148,8 @@ def _exchange_worker(rank, port):
     got = check("cross-shard tie", xb, wc2, ws2)
     assert int(got[0, 1]) == min(best, other)
 
-    # graph replay: the step number lives on the device, the parities alternate
+    # graph replay of the one-launch form: the step number lives on the device, the parities alternate
+    state["one_launch"] = True
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())

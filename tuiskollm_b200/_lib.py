@@ -52,6 +52,8 @@ SIGNATURES = {
     "tk100_fp8_gdn_input": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_projection": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_lm_head": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tk100_fp8_lm_head_sharded": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                       _i, _i, C.POINTER(C.c_uint64), _vp]),
     "tk100_argmax_merge": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "tk100_argmax_exchange": (_i, [_vp, _vp, _i, _i, _i, _vp, C.POINTER(C.c_uint64), _vp]),
     "tk100_nvfp4_quantize_activation": (_i, [_vp, _vp, _i, _i, _vp, C.c_float, _vp, _vp]),

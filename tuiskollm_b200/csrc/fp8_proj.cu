@@ -55,8 +55,11 @@ struct Control {
   uint64_t tmem_full;
   unsigned long long red[BLOCK_TOK];  // per-token argmax keys of this CTA
   float a_scale[BLOCK_TOK];
+  float q_amax[4][kFusedQuantRows];  // fused quantiser: per-warp maxima of the epilogue warps
   uint32_t tmem_base;
   uint32_t is_last;
+  uint32_t tail_last;                // fused tail: this CTA is the last of the launch
+  uint32_t tail_step;
 };
 
 template <int BLOCK_TOK, int DEEP = 0>
@@ -73,6 +76,80 @@ __device__ __forceinline__ void epilogue_barrier() {
 // IEEE total-order key of an f32 bit pattern: larger key <=> greater under total_cmp.
 __device__ __forceinline__ uint32_t total_order_key(uint32_t bits) {
   return bits ^ ((bits & 0x80000000u) ? 0xffffffffu : 0x80000000u);
+}
+
+__device__ __forceinline__ ArgmaxPair unpack_key(unsigned long long packed) {
+  const uint32_t key = static_cast<uint32_t>(packed >> 32);
+  ArgmaxPair o;
+  o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
+  o.index = packed == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(packed));
+  return o;
+}
+
+// Vocabulary-sharded greedy selection without a collective library call.  The calling threads
+// (`tid` of `nthreads`, one CTA) unpack this rank's packed (max, index) keys, store them straight
+// into every peer's exchange buffer over NVLink (plain peer stores), clear the keys, then wait --
+// bounded -- for the pairs of all peers in this rank's own buffer and merge with the
+// first-maximum rule.
+// Every pair travels as two 8-byte words that carry the step number in their upper half:
+// {step, value bits} and {step, index}.  An aligned 8-byte store is indivisible, so a word
+// whose tag equals the current step IS the sender's data of this step: no fence, no separate
+// flag and no second round trip (one NVLink write latency per exchange).
+// Buffer layout on every rank (same offsets everywhere): [2 parities][world][rows][2] words.
+// Steps alternate parity, and a rank can be at most one step ahead of its peers (finishing a
+// step needs every peer's words of that step), so a fast rank's next step never overwrites what
+// a slow rank is still waiting for.
+__device__ __forceinline__ void exchange_and_merge(int tid, int nthreads, int rows, int world, int rank,
+                                                   unsigned long long* keys, const ExchangePeers& peers,
+                                                   unsigned int step, ArgmaxPair* out, uint32_t* status) {
+  const unsigned long long tag = static_cast<unsigned long long>(step) << 32;
+  const size_t parity_words = 2 * static_cast<size_t>(world) * rows;
+  const size_t base = (step & 1u) * parity_words;
+  for (int t = tid; t < rows; t += nthreads) {
+    const unsigned long long packed = __ldcg(keys + t);
+    keys[t] = 0ull;
+    const uint32_t key = static_cast<uint32_t>(packed >> 32);
+    const uint32_t value_bits = key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu);
+    const uint32_t index = packed == 0ull ? 0xffffffffu : 0xffffffffu - static_cast<uint32_t>(packed);
+    for (int pr = 0; pr < world; ++pr) {
+      volatile unsigned long long* dst = reinterpret_cast<volatile unsigned long long*>(peers.base[pr]) +
+                                         base + 2 * (static_cast<size_t>(rank) * rows + t);
+      dst[0] = tag | value_bits;
+      dst[1] = tag | index;
+    }
+  }
+  // every row: wait for each sender's two words of this step, merge as they are read
+  const volatile unsigned long long* mine =
+      reinterpret_cast<const volatile unsigned long long*>(peers.base[rank]) + base;
+  const uint64_t start = global_timer_ns();
+  for (int t = tid; t < rows; t += nthreads) {
+    unsigned long long best = 0ull;
+    bool ok = true;
+    for (int sdr = 0; sdr < world && ok; ++sdr) {
+      const volatile unsigned long long* slot = mine + 2 * (static_cast<size_t>(sdr) * rows + t);
+      unsigned long long w0, w1;
+      for (;;) {
+        w0 = slot[0];
+        w1 = slot[1];
+        if ((w0 >> 32) == step && (w1 >> 32) == step) break;
+        if (global_timer_ns() - start > 2000000000ull) {
+          atomicOr(status, STATUS_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+      const uint32_t vbits = static_cast<uint32_t>(w0);
+      const uint32_t idx = static_cast<uint32_t>(w1);
+      if (idx == 0xffffffffu) continue;  // the sender had no candidate
+      const unsigned long long packed =
+          (static_cast<unsigned long long>(total_order_key(vbits)) << 32) |
+          static_cast<unsigned long long>(0xffffffffu - idx);
+      best = packed > best ? packed : best;
+    }
+    if (!ok) continue;  // results are invalid; the status word says so
+    out[t] = unpack_key(best);
+  }
 }
 
 template <int BLOCK_TOK, int DEEP>  // DEEP: 0 normal ring, 1 deep, 2 wide
@@ -127,15 +204,19 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     return;
   }
 
+  // Fused activation quantiser (16-token tiles only): the epilogue warps make each stage's code
+  // tile themselves, so a full[] barrier takes two arrivals: the weight TMA and that warp.
+  bool fused_quant = false;
+  if constexpr (BLOCK_TOK == 16) fused_quant = p.x_bf16 != nullptr;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->full[s], fused_quant ? 2 : 1);
       mbar_init(&ctl->empty[s], 1);
     }
     mbar_init(&ctl->tmem_full, 1);
     fence_mbar_init();
     prefetch_tensormap(&tmap_w);
-    prefetch_tensormap(&tmap_a);
+    if (!fused_quant) prefetch_tensormap(&tmap_a);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, TMEM_COLS);
@@ -155,7 +236,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       // First pass over the ring: the weight tiles do not depend on the predecessor kernel,
       // so they are requested before pdl_wait(); the activation-code tiles of the same
       // stages follow once the predecessor (the quantiser) is known to be complete.
-      const bool load_a = !TK100_DBG(p, DBG_NO_ACT);
+      const bool load_a = !TK100_DBG(p, DBG_NO_ACT) && !fused_quant;
       const uint32_t tx_bytes = load_a ? STAGE_BYTES : kWStageBytes;
       const int pre = nkb < STAGES ? nkb : STAGES;
       for (int i = 0; i < pre; ++i) {
@@ -222,9 +303,101 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     const bool want_argmax = p.argmax_keys != nullptr;
 
     pdl_wait();  // activation scales, scratch and outputs belong to the predecessor until now
-    for (int j = et; j < BLOCK_TOK; j += kEpilogueThreads) {
-      ctl->a_scale[j] = (j < valid_tok) ? p.act_scales[tok0 + j] : 0.0f;
-      ctl->red[j] = 0ull;
+    if constexpr (BLOCK_TOK == 16) {
+      if (fused_quant) {
+        // ---- per-token scale: amax over the whole BF16 row (all K, whatever this CTA's K range),
+        // the four epilogue warps together; rows <= kFusedQuantRows
+        const int chunks = p.k >> 3;  // 16-byte chunks per row
+        float amax[kFusedQuantRows];
+#pragma unroll
+        for (int t = 0; t < kFusedQuantRows; ++t) amax[t] = 0.0f;
+        for (int c = et; c < chunks; c += kEpilogueThreads) {
+#pragma unroll
+          for (int t = 0; t < kFusedQuantRows; ++t) {
+            if (t < valid_tok) {
+              const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x_bf16 + static_cast<size_t>(tok0 + t) * p.k) + c);
+              const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                amax[t] = fmaxf(amax[t], fmaxf(fabsf(bf16x2_lo(w4[q])), fabsf(bf16x2_hi(w4[q]))));
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < kFusedQuantRows; ++t) {
+          amax[t] = warp_max(amax[t]);
+          if (lane == 0) ctl->q_amax[warp - 2][t] = amax[t];
+        }
+        epilogue_barrier();
+        if (et < BLOCK_TOK) {
+          float scale = 0.0f;
+          if (et < valid_tok) {
+            const float a = fmaxf(fmaxf(ctl->q_amax[0][et], ctl->q_amax[1][et]),
+                                  fmaxf(ctl->q_amax[2][et], ctl->q_amax[3][et]));
+            if (!(a <= 3.0e38f)) atomicOr(p.status, STATUS_NONFINITE_INPUT);
+            scale = (a == 0.0f) ? 1.0f : __fdiv_rn(a, 448.0f);
+            if (tile_n == 0 && split == 0 && p.scales_out) p.scales_out[tok0 + et] = scale;
+          }
+          ctl->a_scale[et] = scale;
+          ctl->red[et] = 0ull;
+        }
+        epilogue_barrier();
+        // ---- each stage's code tile: epilogue warp w makes the k-blocks i = w, w + 4, ...; a lane
+        // owns 4 consecutive columns of every token (8 bytes of BF16 in, 4 code bytes out, written
+        // where the 128-byte swizzle of a TMA box would have put them)
+        const int ew = warp - 2;
+        const bool publish = tile_n == 0 && p.codes_out != nullptr;
+        const int chunk = lane >> 2, within = (lane & 3) * 4;
+        uint2 cur[kFusedQuantRows], nxt[kFusedQuantRows];
+        auto fetch = [&](int i, uint2 (&dst)[kFusedQuantRows]) {
+#pragma unroll
+          for (int t = 0; t < kFusedQuantRows; ++t) {
+            if (t < valid_tok && i < nkb) {
+              dst[t] = __ldg(reinterpret_cast<const uint2*>(p.x_bf16 + static_cast<size_t>(tok0 + t) * p.k +
+                                                           static_cast<size_t>(kb_begin + i) * kTileKBytes) + lane);
+            } else {
+              dst[t] = make_uint2(0u, 0u);
+            }
+          }
+        };
+        fetch(ew, cur);
+        bool okq = true;
+        for (int i = ew; i < nkb && okq; i += 4) {
+          fetch(i + 4, nxt);
+          const int s = i % STAGES;
+          if (i >= STAGES) {
+            okq = mbar_wait(&ctl->empty[s], ((i / STAGES) & 1) ^ 1, p.status);
+            if (!okq) break;
+          }
+          uint8_t* a_tile = smem + s * STAGE_BYTES + kWStageBytes;
+#pragma unroll
+          for (int t = 0; t < kFusedQuantRows; ++t) {
+            if (t < valid_tok) {
+              const float sc = ctl->a_scale[t];
+              const uint32_t lo = f32x2_to_e4m3x2(__fdiv_rn(bf16x2_lo(cur[t].x), sc), __fdiv_rn(bf16x2_hi(cur[t].x), sc));
+              const uint32_t hi = f32x2_to_e4m3x2(__fdiv_rn(bf16x2_lo(cur[t].y), sc), __fdiv_rn(bf16x2_hi(cur[t].y), sc));
+              const uint32_t word = lo | (hi << 16);
+              *reinterpret_cast<uint32_t*>(a_tile + t * kTileKBytes + ((chunk ^ (t & 7)) << 4) + within) = word;
+              if (publish) {
+                *reinterpret_cast<uint32_t*>(p.codes_out + static_cast<size_t>(tok0 + t) * p.k +
+                                             static_cast<size_t>(kb_begin + i) * kTileKBytes + lane * 4) = word;
+              }
+            }
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the UMMA reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->full[s]);
+#pragma unroll
+          for (int t = 0; t < kFusedQuantRows; ++t) cur[t] = nxt[t];
+        }
+      }
+    }
+    if (!fused_quant) {
+      for (int j = et; j < BLOCK_TOK; j += kEpilogueThreads) {
+        ctl->a_scale[j] = (j < valid_tok) ? p.act_scales[tok0 + j] : 0.0f;
+        ctl->red[j] = 0ull;
+      }
     }
     const float w_scale = row_ok ? bf16_bits_to_f32(p.w_scales[n]) : 0.0f;
     epilogue_barrier();
@@ -451,6 +624,42 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         if (best != 0ull) atomicMax(p.argmax_keys + tok0 + j, best);
       }
     }
+    if (p.tail_ticket != nullptr) {
+      // Fused tail: every CTA takes a ticket once its maxima are in the global keys; the CTA that
+      // draws the last one finalises (one GPU) or exchanges with the peers and merges.
+      __threadfence();
+      epilogue_barrier();
+      if (et == 0) {
+        const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+        const unsigned int ticket = atomicAdd(p.tail_ticket, 1u);
+        const bool last = ticket == total - 1;
+        unsigned int step = 0;
+        if (last) {
+          *p.tail_ticket = 0u;  // re-armed for the next launch
+          if (p.world > 1) {
+            step = *p.step_counter + 1u;
+            if (step == 0u) step = 1u;  // 0 is what a zero-filled buffer holds
+            *p.step_counter = step;
+          }
+          __threadfence();
+        }
+        ctl->tail_step = step;
+        ctl->tail_last = last ? 1u : 0u;
+      }
+      epilogue_barrier();
+      if (ctl->tail_last) {
+        if (p.world > 1) {
+          exchange_and_merge(et, kEpilogueThreads, p.rows, p.world, p.rank, p.argmax_keys, p.peers,
+                             ctl->tail_step, p.pairs_out, p.status);
+        } else {
+          for (int t = et; t < p.rows; t += kEpilogueThreads) {
+            const unsigned long long packed = __ldcg(p.argmax_keys + t);
+            p.argmax_keys[t] = 0ull;
+            p.pairs_out[t] = unpack_key(packed);
+          }
+        }
+      }
+    }
   }
   if (clustered && warp < 2) {
     // the TMA and UMMA warps take part in the two cluster barriers of the reduction
@@ -475,12 +684,7 @@ __global__ void argmax_finalize_kernel(int rows, unsigned long long* keys, Argma
   if (t >= rows) return;
   const unsigned long long packed = keys[t];
   keys[t] = 0ull;
-  const uint32_t key = static_cast<uint32_t>(packed >> 32);
-  const uint32_t bits = key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu);
-  ArgmaxPair out;
-  out.value = __uint_as_float(bits);
-  out.index = packed == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(packed));
-  pairs[t] = out;
+  pairs[t] = unpack_key(packed);
 }
 
 __global__ void argmax_merge_kernel(int rows, int shards, const ArgmaxPair* gathered,
@@ -498,25 +702,10 @@ __global__ void argmax_merge_kernel(int rows, int shards, const ArgmaxPair* gath
         static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(c.index));
     best = packed > best ? packed : best;
   }
-  const uint32_t key = static_cast<uint32_t>(best >> 32);
-  ArgmaxPair o;
-  o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
-  o.index = best == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(best));
-  out[t] = o;
+  out[t] = unpack_key(best);
 }
 
-// Vocabulary-sharded greedy selection without a collective library call: one CTA per rank
-// unpacks its shard's (max, index) pairs and stores them straight into every peer's exchange
-// buffer over NVLink (plain peer stores), then waits -- bounded -- for the pairs of all peers
-// in its own buffer and merges with the first-maximum rule.
-// Every pair travels as two 8-byte words that carry the step number in their upper half:
-// {step, value bits} and {step, index}.  An aligned 8-byte store is indivisible, so a word
-// whose tag equals the current step IS the sender's data of this step: no fence, no separate
-// flag and no second round trip (one NVLink write latency per exchange).
-// Buffer layout on every rank (same offsets everywhere): [2 parities][world][rows][2] words.
-// Steps alternate parity, and a rank can be at most one step ahead of its peers (finishing a
-// step needs every peer's words of that step), so a fast rank's next step never overwrites what
-// a slow rank is still waiting for.
+// The exchange as a launch of its own (one CTA per rank): see exchange_and_merge.
 __global__ void __launch_bounds__(256)
     argmax_exchange_kernel(int rows, int world, int rank, unsigned long long* keys,
                            ExchangePeers peers, unsigned int* step_counter, ArgmaxPair* out,
@@ -530,60 +719,7 @@ __global__ void __launch_bounds__(256)
     *step_counter = s_step;
   }
   __syncthreads();
-  const unsigned int step = s_step;
-  const unsigned long long tag = static_cast<unsigned long long>(step) << 32;
-  const size_t parity_words = 2 * static_cast<size_t>(world) * rows;
-  const size_t base = (step & 1u) * parity_words;
-
-  for (int t = threadIdx.x; t < rows; t += blockDim.x) {
-    const unsigned long long packed = keys[t];
-    keys[t] = 0ull;
-    const uint32_t key = static_cast<uint32_t>(packed >> 32);
-    const uint32_t value_bits = key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu);
-    const uint32_t index = packed == 0ull ? 0xffffffffu : 0xffffffffu - static_cast<uint32_t>(packed);
-    for (int pr = 0; pr < world; ++pr) {
-      volatile unsigned long long* dst = reinterpret_cast<volatile unsigned long long*>(peers.base[pr]) +
-                                         base + 2 * (static_cast<size_t>(rank) * rows + t);
-      dst[0] = tag | value_bits;
-      dst[1] = tag | index;
-    }
-  }
-  // every row: wait for each sender's two words of this step, merge as they are read
-  const volatile unsigned long long* mine =
-      reinterpret_cast<const volatile unsigned long long*>(peers.base[rank]) + base;
-  const uint64_t start = global_timer_ns();
-  for (int t = threadIdx.x; t < rows; t += blockDim.x) {
-    unsigned long long best = 0ull;
-    bool ok = true;
-    for (int sdr = 0; sdr < world && ok; ++sdr) {
-      const volatile unsigned long long* slot = mine + 2 * (static_cast<size_t>(sdr) * rows + t);
-      unsigned long long w0, w1;
-      for (;;) {
-        w0 = slot[0];
-        w1 = slot[1];
-        if ((w0 >> 32) == step && (w1 >> 32) == step) break;
-        if (global_timer_ns() - start > 2000000000ull) {
-          atomicOr(status, STATUS_WAIT_TIMEOUT);
-          ok = false;
-          break;
-        }
-      }
-      if (!ok) break;
-      const uint32_t vbits = static_cast<uint32_t>(w0);
-      const uint32_t idx = static_cast<uint32_t>(w1);
-      if (idx == 0xffffffffu) continue;  // the sender had no candidate
-      const unsigned long long packed =
-          (static_cast<unsigned long long>(total_order_key(vbits)) << 32) |
-          static_cast<unsigned long long>(0xffffffffu - idx);
-      best = packed > best ? packed : best;
-    }
-    if (!ok) continue;  // results are invalid; the status word says so
-    const uint32_t key = static_cast<uint32_t>(best >> 32);
-    ArgmaxPair o;
-    o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
-    o.index = best == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(best));
-    out[t] = o;
-  }
+  exchange_and_merge(threadIdx.x, blockDim.x, rows, world, rank, keys, peers, s_step, out, status);
 }
 
 template <int BLOCK_TOK>

@@ -77,6 +77,19 @@ cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, cons
                                  float nvfp4_divisor = 0.0f);
 
 // ------------------------------------------------------------------ fp8_proj.cu
+struct ArgmaxPair {
+  float value;
+  int32_t index;
+};
+// Peer exchange buffers of the vocabulary-sharded argmax (device addresses, one per rank;
+// entry `rank` is this rank's own buffer).
+constexpr int kMaxExchangeRanks = 8;
+struct ExchangePeers {
+  unsigned char* base[kMaxExchangeRanks];
+};
+// Largest row count whose activation quantiser the projection kernel runs itself.
+constexpr int kFusedQuantRows = 4;
+
 struct Fp8ProjParams {
   int rows;       // active tokens M
   int out_rows;   // weight rows N (this shard)
@@ -98,6 +111,21 @@ struct Fp8ProjParams {
   unsigned int* counters;       // one per output tile, zero between launches
   uint32_t* status;
   uint32_t debug;               // experiment switches (debug_flags()); 0 in normal use
+  // Fused activation quantiser (16-token tiles, rows <= kFusedQuantRows): when x_bf16 is set the
+  // CTA computes the per-token scales from the BF16 rows itself and writes each stage's code tile
+  // into shared memory (tmap_a is not read); the CTAs of output tile 0 also publish the codes
+  // and scales to codes_out / scales_out, the planes the unfused quantiser would have written.
+  const uint16_t* x_bf16;       // [rows, k] or null
+  uint8_t* codes_out;           // [rows, k]
+  float* scales_out;            // [rows]
+  // Fused tail of the LM head: the last CTA of the launch to finish (ticket) unpacks the packed
+  // maxima into pairs_out (world == 1) or exchanges them with the peers and merges (world > 1),
+  // and clears argmax_keys.  Null ticket = no fused tail.
+  unsigned int* tail_ticket;
+  ArgmaxPair* pairs_out;        // [rows]
+  int world, rank;
+  unsigned int* step_counter;   // device step number of the exchange
+  ExchangePeers peers;
 };
 
 // block_tok is the token tile (16, 32, 64, 128 or 256).
@@ -112,19 +140,9 @@ cudaError_t fp8_pair_prepare();
 cudaError_t launch_fp8_pair(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                             const Fp8ProjParams& p);
 
-struct ArgmaxPair {
-  float value;
-  int32_t index;
-};
 // keys -> pairs, and clears the keys for the next launch.
 cudaError_t launch_argmax_finalize(cudaStream_t stream, int rows, unsigned long long* keys,
                                    ArgmaxPair* pairs);
-// Peer exchange buffers of the vocabulary-sharded argmax (device addresses, one per rank;
-// entry `rank` is this rank's own buffer).
-constexpr int kMaxExchangeRanks = 8;
-struct ExchangePeers {
-  unsigned char* base[kMaxExchangeRanks];
-};
 cudaError_t launch_argmax_exchange(cudaStream_t stream, int rows, int world, int rank,
                                    unsigned long long* keys, const ExchangePeers& peers,
                                    unsigned int* step_counter, ArgmaxPair* out, uint32_t* status);

@@ -81,6 +81,22 @@ __device__ __forceinline__ float silu_stable(float v) {
   return __fdividef(v >= 0.0f ? v : v * ex, 1.0f + ex);
 }
 
+// One value per lane, a 16-column block = 16 consecutive lanes: the block's E4M3 scale code
+// (bits 8..15 of the result) and this lane's E2M1 code (bits 0..3), as nvfp4_quantize_kernel
+// defines them.  Kept out of line so that the sixteen calls of an epilogue chunk do not interleave
+// (the surrounding kernel runs at its register limit).
+static __device__ __noinline__ uint32_t nvfp4_code_of_lane(uint32_t bf16_bits, float divisor) {
+  const float v = __uint_as_float(bf16_bits << 16);
+  float amax = fmaxf(0.0f, fabsf(v));
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const uint32_t sc = f32x2_to_e4m3x2(__fdiv_rn(__fmul_rn(amax, divisor), 6.0f), 0.0f) & 0xffu;
+  const float sf = e4m3_to_f32(sc);
+  const uint32_t nib = sf == 0.0f ? (signbit(v) ? 0x8u : 0u)
+                                  : (f32x2_to_e2m1x2(__fdiv_rn(__fmul_rn(v, divisor), sf), 0.0f) & 0xfu);
+  return nib | (sc << 8);
+}
+
 template <int BLOCK_TOK, bool GATE_UP>
 __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 2)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
@@ -471,7 +487,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
             }
           }
         }
-        if (p.q_codes) {
+        if (BLOCK_TOK == 32 && p.q_codes) {
           // NVFP4 form of the rounded outputs, as nvfp4_quantize_kernel defines it: a block is 16
           // consecutive outputs of a token = 16 lanes of this warp (out_rows is a multiple of
           // 128, so every lane holds a valid row).
@@ -494,16 +510,9 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (c0 + j < valid_tok) {  // warp-uniform
-              const float v = __uint_as_float(bits[j] << 16);
-              float amax = fmaxf(0.0f, fabsf(v));
-#pragma unroll
-              for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-              const uint32_t sc = f32x2_to_e4m3x2(__fdiv_rn(__fmul_rn(amax, p.q_divisor), 6.0f), 0.0f) & 0xffu;
-              const float sf = e4m3_to_f32(sc);
-              const uint32_t nib =
-                  sf == 0.0f ? (signbit(v) ? 0x8u : 0u)
-                             : (f32x2_to_e2m1x2(__fdiv_rn(__fmul_rn(v, p.q_divisor), sf), 0.0f) & 0xfu);
-              store_q(j, nib, __shfl_xor_sync(0xffffffffu, nib, 1), sc);
+              const uint32_t packed = nvfp4_code_of_lane(bits[j], p.q_divisor);
+              const uint32_t nib = packed & 0xfu;
+              store_q(j, nib, __shfl_xor_sync(0xffffffffu, nib, 1), packed >> 8);
             }
           }
         }

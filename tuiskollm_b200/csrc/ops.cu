@@ -40,7 +40,8 @@ Tuning Tuning::from_environment() {
   t.nvfp4_pair = env_int("TK100_PAIR", t.nvfp4_pair);
   t.nvfp4_pair_min_rows = env_int("TK100_PAIR_MIN_ROWS", t.nvfp4_pair_min_rows);
   t.swiglu_pairs = env_int("TK100_SWIGLU_PAIRS", t.swiglu_pairs);
-  t.fused_exchange = env_int("TK100_FUSED_EXCHANGE", t.fused_exchange);
+  t.fused_exchange = env_int("TK100_FUSED_TAIL", t.fused_exchange);
+  t.fused_quant = env_int("TK100_FUSED_QUANT", t.fused_quant);
   return t;
 }
 
@@ -143,8 +144,8 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
             cudaMalloc(&ctx->counters_, ctx->counter_count_ * sizeof(unsigned int)) ==
                 cudaSuccess &&
             cudaMalloc(&ctx->status_, sizeof(uint32_t)) == cudaSuccess &&
-            cudaMalloc(&ctx->exchange_step_, sizeof(unsigned int)) == cudaSuccess &&
-            cudaMemset(ctx->exchange_step_, 0, sizeof(unsigned int)) == cudaSuccess &&
+            cudaMalloc(&ctx->exchange_step_, 2 * sizeof(unsigned int)) == cudaSuccess &&
+            cudaMemset(ctx->exchange_step_, 0, 2 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMalloc(&ctx->peer_sum_state_, 4 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->peer_sum_state_, 0, 4 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->counters_, 0, ctx->counter_count_ * sizeof(unsigned int)) ==
@@ -357,7 +358,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
                                float* activation_scales, const uint8_t* weight_codes,
                                const uint16_t* weight_scales, uint16_t* output, float* logits_f32,
                                unsigned long long* argmax_scratch, tk100_argmax_pair* pairs,
-                               int vocab_offset) {
+                               int vocab_offset, const ArgmaxTail* tail) {
   TK100_TRY(check_rows(ctx_, name_, rows));
   if (out_rows < 16 || out_rows % 16 != 0) {
     return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name_ + ": " +
@@ -383,8 +384,33 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
                      std::string("[gpu.launch] ") + name_ + ": argmax scratch plane is null");
   }
   if (argmax_scratch) TK100_TRY(check_plane(ctx_, name_, "argmax scratch", argmax_scratch, 8));
+  ExchangePeers peers{};
+  const int world = tail ? tail->world : 1;
+  if (tail) {
+    if (world < 1 || world > kMaxExchangeRanks || tail->rank < 0 || tail->rank >= world || !pairs ||
+        rows > 4096 || (world > 1 && !tail->peer_buffers)) {
+      return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name_ +
+                                             ": bad exchange argument (1 <= world <= 8, 0 <= rank < "
+                                             "world, non-null pair and peer planes)");
+    }
+    for (int i = 0; i < world && world > 1; ++i) {
+      if (tail->peer_buffers[i] == 0 || (tail->peer_buffers[i] & 7) != 0) {
+        return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name_ +
+                                               ": peer buffer is null or misaligned");
+      }
+      peers.base[i] = reinterpret_cast<unsigned char*>(static_cast<uintptr_t>(tail->peer_buffers[i]));
+    }
+  }
 
-  if (input) TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
+  // Decode launches of at most kFusedQuantRows rows quantise inside the projection kernel (every
+  // CTA derives the per-token scale from the BF16 rows and makes its own code tiles; the codes and
+  // scales still reach the caller's planes, bit for bit what the quantiser kernel writes).
+  const bool fuse_quant = input != nullptr && rows <= kFusedQuantRows && ctx_.tuning().fused_quant != 0 &&
+                          (ctx_.forced_block_tok() == 0 || ctx_.forced_block_tok() == 16);
+  if (input && fuse_quant) TK100_TRY(check_plane(ctx_, name_, "input", input, 16));
+  if (input && !fuse_quant) {
+    TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
+  }
 
   // Prefill shapes with a plain BF16 output: CTA pairs (256-row x 256-token pair tiles) halve
   // the operand bytes per MAC, which is what bounds the one-CTA kernel there.
@@ -495,6 +521,22 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
   p.debug = debug_flags();
+  if (fuse_quant) {
+    p.x_bf16 = input;
+    p.codes_out = activation_codes;
+    p.scales_out = activation_scales;
+  }
+  // The last CTA of the launch unpacks the maxima (or exchanges them with the peers and merges):
+  // no finalize / exchange launch behind the projection.
+  const bool fuse_tail = pairs != nullptr && ctx_.tuning().fused_exchange != 0;
+  if (fuse_tail) {
+    p.tail_ticket = ctx_.tail_ticket();
+    p.pairs_out = reinterpret_cast<ArgmaxPair*>(pairs);
+    p.world = world;
+    p.rank = tail ? tail->rank : 0;
+    p.step_counter = ctx_.exchange_step();
+    p.peers = peers;
+  }
   ctx_.count_launch();
   {
     // the ring variant launch_fp8_projection picks for this tile size
@@ -503,11 +545,18 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   }
   TK100_TRY(ctx_.check(launch_fp8_projection(stream, block_tok, map_w, map_a, p),
                        "launching the FP8 projection"));
-  if (pairs) {
+  if (pairs && !fuse_tail) {
     ctx_.count_launch();
-    TK100_TRY(ctx_.check(launch_argmax_finalize(stream, rows, argmax_scratch,
-                                                reinterpret_cast<ArgmaxPair*>(pairs)),
-                         "launching the argmax finalizer"));
+    if (world > 1) {
+      TK100_TRY(ctx_.check(launch_argmax_exchange(stream, rows, world, tail->rank, argmax_scratch, peers,
+                                                  ctx_.exchange_step(),
+                                                  reinterpret_cast<ArgmaxPair*>(pairs), ctx_.status_word()),
+                           "launching the argmax exchange"));
+    } else {
+      TK100_TRY(ctx_.check(launch_argmax_finalize(stream, rows, argmax_scratch,
+                                                  reinterpret_cast<ArgmaxPair*>(pairs)),
+                           "launching the argmax finalizer"));
+    }
   }
   return TK100_OK;
 }
@@ -879,6 +928,28 @@ tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, in
               static_cast<int>(ctx->impl->config().hidden), input, activation_codes,
               activation_scales, weight_codes, weight_scales, output, logits_f32,
               reinterpret_cast<unsigned long long*>(argmax_scratch), pairs, vocab_offset);
+}
+
+tk100_status tk100_fp8_lm_head_sharded(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,
+                                       int vocab_offset, const uint16_t* input,
+                                       uint8_t* activation_codes, float* activation_scales,
+                                       const uint8_t* weight_codes, const uint16_t* weight_scales,
+                                       uint16_t* output, float* logits_f32, uint64_t* argmax_scratch,
+                                       int world, int rank, const uint64_t* peer_buffers,
+                                       tk100_argmax_pair* merged_pairs) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  if (vocab_offset < 0) {
+    return ctx->impl->fail(TK100_ERR_LAUNCH, "[gpu.launch] FP8 LM head: negative vocab offset");
+  }
+  tk100::ArgmaxTail tail;
+  tail.world = world;
+  tail.rank = rank;
+  tail.peer_buffers = peer_buffers;
+  return tk100::LmHeadOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, vocab_rows,
+              static_cast<int>(ctx->impl->config().hidden), input, activation_codes,
+              activation_scales, weight_codes, weight_scales, output, logits_f32,
+              reinterpret_cast<unsigned long long*>(argmax_scratch), merged_pairs, vocab_offset, &tail);
 }
 
 tk100_status tk100_argmax_merge(tk100_ctx* ctx, tk100_stream stream, int rows, int shards,

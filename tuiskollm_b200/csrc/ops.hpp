@@ -36,7 +36,8 @@ struct Tuning {
   int nvfp4_pair = 0;         // TK100_PAIR: 1 down, 2 gate_up too (cta_group::2 variant)
   int nvfp4_pair_min_rows = 1024;
   int swiglu_pairs = 1;       // TK100_SWIGLU_PAIRS=0: one CTA holds the gate and the up tile
-  int fused_exchange = 1;     // TK100_FUSED_EXCHANGE=0: argmax exchange as its own launch only
+  int fused_exchange = 1;     // TK100_FUSED_TAIL=0: argmax finalize / exchange as launches of their own
+  int fused_quant = 1;        // TK100_FUSED_QUANT=0: the activation quantiser always as its own launch
   static Tuning from_environment();
 };
 
@@ -68,6 +69,7 @@ class Context {
   size_t counter_count() const { return counter_count_; }
   uint32_t* status_word() const { return status_; }
   unsigned int* exchange_step() const { return exchange_step_; }
+  unsigned int* tail_ticket() const { return exchange_step_ + 1; }
   unsigned int* peer_sum_state() const { return peer_sum_state_; }
   const Tuning& tuning() const { return tuning_; }
   int forced_splits() const { return tuning_.splits; }
@@ -90,7 +92,8 @@ class Context {
   unsigned int* counters_ = nullptr;
   size_t counter_count_ = 0;
   uint32_t* status_ = nullptr;
-  unsigned int* exchange_step_ = nullptr;  // device step counter of the peer argmax exchange
+  unsigned int* exchange_step_ = nullptr;  // [0] device step counter of the peer argmax exchange,
+                                           // [1] ticket of the LM head's fused tail
   unsigned int* peer_sum_state_ = nullptr;  // peer sum: [0] step counter, [1..3] phase tickets
   Tuning tuning_;
   uint64_t launches_ = 0;
@@ -146,6 +149,14 @@ class ResidualNormOp {
 
 // tuisko-kernels-sm120/src/fp8/projection.rs:510-794: one class serves the three planes;
 // `name` only labels error messages ("FP8 QKV", "FP8 GDN input", "FP8 LM head", ...).
+// How the LM head's per-shard maxima leave the projection: merged with the peers' over NVLink
+// (world > 1) inside the same launch, or just unpacked (world == 1).
+struct ArgmaxTail {
+  int world = 1;
+  int rank = 0;
+  const uint64_t* peer_buffers = nullptr;  // `world` device addresses (tk100_argmax_exchange)
+};
+
 class Fp8ProjectionOp {
  public:
   Fp8ProjectionOp(Context& ctx, const char* name) : ctx_(ctx), name_(name) {}
@@ -155,7 +166,7 @@ class Fp8ProjectionOp {
                 uint8_t* activation_codes, float* activation_scales, const uint8_t* weight_codes,
                 const uint16_t* weight_scales, uint16_t* output, float* logits_f32 = nullptr,
                 unsigned long long* argmax_scratch = nullptr, tk100_argmax_pair* pairs = nullptr,
-                int vocab_offset = 0);
+                int vocab_offset = 0, const ArgmaxTail* tail = nullptr);
 
  private:
   Context& ctx_;

@@ -126,10 +126,9 @@ class ShardedLmHead:
                weight_scales, output, logits_f32, argmax_scratch, pairs, gathered, merged):
         """Projection + per-shard argmax, then (world > 1) all-gather + merge into ``merged``."""
         if self.world > 1 and self.peer_addresses is not None:
-            self.op.launch(stream, rows, input, activation_codes, activation_scales, weight_codes,
-                           weight_scales, output, logits_f32, argmax_scratch, None)
-            self.op.exchange(stream, rows, self.world, self.rank, argmax_scratch,
-                             self.peer_addresses, merged)
+            self.op.launch_sharded(stream, rows, input, activation_codes, activation_scales,
+                                   weight_codes, weight_scales, output, logits_f32, argmax_scratch,
+                                   self.world, self.rank, self.peer_addresses, merged)
             return merged
         self.op.launch(stream, rows, input, activation_codes, activation_scales, weight_codes,
                        weight_scales, output, logits_f32, argmax_scratch, pairs)

@@ -196,6 +196,19 @@ class LmHeadOp:
                                          _ptr(weight_scales), _ptr(output), _ptr(logits_f32),
                                          _ptr(argmax_scratch), _ptr(pairs)))
 
+    def launch_sharded(self, stream, rows, input, activation_codes, activation_scales, weight_codes,
+                       weight_scales, output, logits_f32, argmax_scratch, world, rank, peer_buffers,
+                       merged_pairs):
+        """Projection, per-shard argmax, peer exchange and merge in ONE launch
+        (``tk100_fp8_lm_head_sharded``); ``peer_buffers`` may be None when ``world == 1``."""
+        c = self.ctx
+        arr = (C.c_uint64 * world)(*[int(b) for b in peer_buffers]) if peer_buffers else None
+        c.check(c._lib.tk100_fp8_lm_head_sharded(
+            c.handle, _stream(stream), rows, self.vocab_rows, self.vocab_offset, _ptr(input),
+            _ptr(activation_codes), _ptr(activation_scales), _ptr(weight_codes), _ptr(weight_scales),
+            _ptr(output), _ptr(logits_f32), _ptr(argmax_scratch), world, rank, arr,
+            _ptr(merged_pairs)))
+
     def exchange(self, stream, rows, world, rank, argmax_scratch, peer_buffers, output_pairs):
         """Peer-store exchange + merge of the per-shard maxima (after ``launch`` with
         ``pairs=None``); ``peer_buffers`` lists every rank's exchange-buffer address."""
