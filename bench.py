@@ -9,9 +9,8 @@ vocabulary is split contiguously over the N ranks, every rank streams its shard 
 step and the per-shard (max, index) pairs are exchanged over NVLink and merged.
 
 One step = quantise the hidden rows + stream the weight shard through the tcgen05
-projection kernel + argmax finalize (N = 1) or peer exchange + merge (N > 1) -- ONE kernel
-launch: at decode sizes every CTA quantises the hidden rows itself and the last CTA to finish
-unpacks, exchanges and merges the maxima.
+projection kernel, whose last CTA to finish unpacks the maxima (N = 1) or exchanges them with
+the peers over NVLink and merges (N > 1): two kernel launches per step.
 
   value     whole-job algorithmic GB/s with the hidden rows resident in HBM, from EXACTLY
             `--steps` graph replays between two barriers (max over ranks)
@@ -1153,7 +1152,7 @@ def run_native(args):
             if args.split_exchange:  # projection, then the exchange + merge as its own launch
                 op.launch(None, m, x, codes, scales, wc, ws, None, logits, scratch, None)
                 op.exchange(None, m, world, rank, scratch, peer_addresses, merged)
-            else:  # one launch: quantise + project + argmax + peer exchange + merge
+            else:  # quantiser, then ONE launch: projection + argmax + peer exchange + merge
                 op.launch_sharded(None, m, x, codes, scales, wc, ws, None, logits, scratch, world,
                                   rank, peer_addresses, merged)
             return
@@ -1362,8 +1361,7 @@ def run_native(args):
                          "traffic_source": "ncu dram read+write bytes of this kernel at vocab "
                                            "248320, M=1 (1 272 757 504 B), scaled by algorithmic bytes",
                          "peak_kind": peak_kind,
-                         "kernel": kernel_name + " (quantiser in its prologue, finalize / exchange "
-                                                 "in its last CTA)",
+                         "kernel": kernel_name + " (finalize / peer exchange in its last CTA)",
                          "algorithmic_bytes": shard_bytes,
                          "us_per_launch": proj_ms * 1e3, "frac_of_8TBs": achieved / NOMINAL_HBM_GBS},
             "clocks": clocks,

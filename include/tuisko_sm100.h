@@ -144,8 +144,7 @@ TK100_API tk100_status tk100_quantize_activation_e4m3(tk100_ctx* ctx, tk100_stre
  * `out_rows` is the weight row count N (the reference fixes it per Arch; here it is a
  * run-time value, N % 16 == 0) and the reduction length is config.hidden.
  * input != NULL: quantise `input` into activation_codes/scales, then project (the
- * reference's two launches; up to 4 rows the projection kernel quantises by itself, with the
- * same bits in both planes).  input == NULL: activation_codes/scales already hold the
+ * reference's two launches).  input == NULL: activation_codes/scales already hold the
  * fused producer's output and only the projection runs.
  * Admitted rows: 1 <= rows <= config.max_rows; anything else is TK100_ERR_LAUNCH. */
 TK100_API tk100_status tk100_fp8_qkv(tk100_ctx* ctx, tk100_stream stream, int rows, int out_rows,
@@ -184,10 +183,7 @@ TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, in
  * -- bounded, ~2 s, then TK100_DEVICE_WAIT_TIMEOUT -- for the peers' pairs and writes the merged
  * pairs [rows], identical on every rank.  world == 1 degenerates to tk100_fp8_lm_head with
  * pairs.  Arguments as tk100_fp8_lm_head and tk100_argmax_exchange (peer_buffers may be NULL
- * when world == 1); every rank makes the same sequence of calls.  With input != NULL and at
- * most 4 rows the activation quantiser runs inside the projection kernel too (activation_codes
- * / activation_scales still receive what the quantiser launch would have written): the whole
- * decode step is one kernel. */
+ * when world == 1); every rank makes the same sequence of calls. */
 TK100_API tk100_status tk100_fp8_lm_head_sharded(
     tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows, int vocab_offset,
     const uint16_t* input, uint8_t* activation_codes, float* activation_scales,

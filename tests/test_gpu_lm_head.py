@@ -96,9 +96,9 @@ def test_lm_head_matches_oracle_and_greedy_rule(tk, ctx, oracle, rows):
 
 @pytest.mark.parametrize("rows", [1, 3, 4, 5])
 def test_fused_quantiser_and_tail_equal_the_separate_launches(tk, oracle, rows, monkeypatch):
-    """Up to 4 rows the projection kernel quantises the hidden rows in its prologue and its last
-    CTA unpacks the maxima; TK100_FUSED_QUANT=0 / TK100_FUSED_TAIL=0 keep the quantiser and the
-    finalizer as launches of their own.  Every plane must come out bit-identical on both routes,
+    """With TK100_FUSED_QUANT=1 the projection kernel quantises up to 4 hidden rows in its prologue
+    (off by default), and by default its last CTA unpacks the maxima; TK100_FUSED_QUANT=0 /
+    TK100_FUSED_TAIL=0 keep the quantiser and the finalizer as launches of their own.  Every plane must come out bit-identical on both routes,
     eagerly and as graph replays, with and without split K (the 4160-row plane is unsplit with the
     longer ring, the 1040-row plane splits K eight ways)."""
     from tuiskollm_b200 import synth

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  if (threadIdx.x == 0) TK100_STAMP(p, 0);
   const int kb_total = p.k / kTileKBytes;
   const int kb_begin = static_cast<int>(static_cast<long long>(split) * kb_total / p.splits);
   const int kb_end = static_cast<int>(static_cast<long long>(split + 1) * kb_total / p.splits);
@@ -227,6 +228,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_base;
   pdl_trigger();
+  if (threadIdx.x == 0) TK100_STAMP(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -245,6 +247,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
                     tile_n * kTileRows, pol_w);
       }
       pdl_wait();
+      TK100_STAMP(p, 2);
       for (int i = 0; i < pre && load_a; ++i) {
         tma_load_2d(smem + i * STAGE_BYTES + kWStageBytes, &tmap_a, &ctl->full[i],
                     (kb_begin + i) * kTileKBytes, tile_m * BLOCK_TOK, pol_a);
@@ -277,6 +280,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         const uint32_t phase = (i / STAGES) & 1;
         ok = mbar_wait(&ctl->full[s], phase, p.status);
         if (!ok) break;
+        if (i == 0) TK100_STAMP(p, 3);
         tc_fence_after_sync();
         const uint32_t w_addr = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t desc_w = umma_desc_sw128(w_addr);
@@ -290,6 +294,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         umma_commit(&ctl->empty[s]);  // frees the stage once these MMAs have read it
       }
       umma_commit(&ctl->tmem_full);  // accumulator complete (also releases the epilogue on error)
+      TK100_STAMP(p, 4);
     }
   } else {
     // ----------------------------------------------------------------- epilogue
@@ -403,6 +408,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     epilogue_barrier();
 
     mbar_wait(&ctl->tmem_full, 0, p.status);
+    if (et == 0) TK100_STAMP(p, 5);
     tc_fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
@@ -621,13 +627,18 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       epilogue_barrier();
       for (int j = et; j < valid_tok; j += kEpilogueThreads) {
         const unsigned long long best = ctl->red[j];
-        if (best != 0ull) atomicMax(p.argmax_keys + tok0 + j, best);
+        if (best != 0ull) {
+          // The value the atomic returns is stored to shared memory: the thread cannot pass the
+          // barrier below before the atomic has been performed at L2, which orders it before the
+          // ticket (no device-wide fence, which would also wait for this thread's logit stores).
+          const unsigned long long before = atomicMax(p.argmax_keys + tok0 + j, best);
+          if (p.tail_ticket != nullptr) ctl->red[j] = before;
+        }
       }
     }
     if (p.tail_ticket != nullptr) {
       // Fused tail: every CTA takes a ticket once its maxima are in the global keys; the CTA that
       // draws the last one finalises (one GPU) or exchanges with the peers and merges.
-      __threadfence();
       epilogue_barrier();
       if (et == 0) {
         const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
@@ -641,7 +652,6 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
             if (step == 0u) step = 1u;  // 0 is what a zero-filled buffer holds
             *p.step_counter = step;
           }
-          __threadfence();
         }
         ctl->tail_step = step;
         ctl->tail_last = last ? 1u : 0u;
@@ -661,6 +671,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       }
     }
   }
+  if (threadIdx.x == 64) TK100_STAMP(p, 6);
   if (clustered && warp < 2) {
     // the TMA and UMMA warps take part in the two cluster barriers of the reduction
     cluster_arrive();
@@ -675,6 +686,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     __syncwarp();
     tmem_dealloc(tmem, TMEM_COLS);
   }
+  if (threadIdx.x == 0) TK100_STAMP(p, 7);
 }
 
 __global__ void argmax_finalize_kernel(int rows, unsigned long long* keys, ArgmaxPair* pairs) {

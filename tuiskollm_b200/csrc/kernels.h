@@ -27,6 +27,24 @@ enum : uint32_t { DBG_NO_EPILOGUE = 1, DBG_NO_MMA = 2, DBG_NO_ACT = 4 };
 #define TK100_DBG(p, bits) false
 #endif
 uint32_t debug_flags();
+// Experiment builds only: a kernel writes %globaltimer at a few points of CTA `c` into
+// stamps[c * 8 + k] (k: 0 entry, 1 set-up done, 2 producer past the dependency wait, 3 first stage
+// full, 4 last UMMA issued, 5 accumulator complete, 6 epilogue done, 7 exit) when the plane is set
+// (its device address comes from TK100_STAMPS_PTR, read with the other switches).
+#ifdef TK100_EXPERIMENT
+#define TK100_STAMP(p, k)                                                                          \
+  do {                                                                                             \
+    if ((p).stamps) {                                                                              \
+      const size_t _c = blockIdx.x + static_cast<size_t>(gridDim.x) * (blockIdx.y + static_cast<size_t>(gridDim.y) * blockIdx.z); \
+      unsigned long long _t;                                                                       \
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(_t));                                       \
+      (p).stamps[_c * 8 + (k)] = _t;                                                               \
+    }                                                                                              \
+  } while (0)
+#else
+#define TK100_STAMP(p, k) do { } while (0)
+#endif
+unsigned long long* debug_stamps();
 
 // A cluster shape other than (1, 1, 1) launches thread-block clusters of that shape.
 template <typename... KArgs, typename... Args>
@@ -111,6 +129,7 @@ struct Fp8ProjParams {
   unsigned int* counters;       // one per output tile, zero between launches
   uint32_t* status;
   uint32_t debug;               // experiment switches (debug_flags()); 0 in normal use
+  unsigned long long* stamps;   // experiment builds: timestamp plane (TK100_STAMP), else null
   // Fused activation quantiser (16-token tiles, rows <= kFusedQuantRows): when x_bf16 is set the
   // CTA computes the per-token scales from the BF16 rows itself and writes each stage's code tile
   // into shared memory (tmap_a is not read); the CTAs of output tile 0 also publish the codes
@@ -195,6 +214,7 @@ struct Nvfp4Params {
   unsigned int* counters;
   uint32_t* status;
   uint32_t debug;      // experiment switches (debug_flags()); 0 in normal use
+  unsigned long long* stamps;  // experiment builds: timestamp plane (TK100_STAMP), else null
 };
 
 cudaError_t nvfp4_prepare();

@@ -201,6 +201,7 @@ cudaError_t launch_chunks(cudaStream_t stream, int rows, int hidden, int threads
 namespace {
 bool g_pdl = true;
 uint32_t g_debug = 0;
+unsigned long long* g_stamps = nullptr;
 }  // namespace
 
 void read_process_switches() {
@@ -209,12 +210,16 @@ void read_process_switches() {
 #ifdef TK100_EXPERIMENT
   const char* d = std::getenv("TK100_DEBUG");
   g_debug = d ? static_cast<uint32_t>(std::atoi(d)) : 0u;
+  const char* sp = std::getenv("TK100_STAMPS_PTR");
+  g_stamps = sp ? reinterpret_cast<unsigned long long*>(std::strtoull(sp, nullptr, 0)) : nullptr;
 #endif
 }
 
 bool pdl_enabled() { return g_pdl; }
 
 uint32_t debug_flags() { return g_debug; }
+
+unsigned long long* debug_stamps() { return g_stamps; }
 
 bool norm_geometry(int hidden, int* threads, int* chunks) {
   if (hidden <= 0 || (hidden & 7) != 0) return false;

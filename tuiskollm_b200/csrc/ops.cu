@@ -402,11 +402,18 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     }
   }
 
-  // Decode launches of at most kFusedQuantRows rows quantise inside the projection kernel (every
-  // CTA derives the per-token scale from the BF16 rows and makes its own code tiles; the codes and
-  // scales still reach the caller's planes, bit for bit what the quantiser kernel writes).
+  // Opt-in (TK100_FUSED_QUANT=1: launches of one wave, 2: every size): decode launches of at most
+  // kFusedQuantRows rows quantise inside the projection kernel (every CTA derives the per-token
+  // scale from the BF16 rows and makes its own code tiles; the codes and scales still reach the
+  // caller's planes, bit for bit what the quantiser kernel writes).  Measured slower than the
+  // quantiser launch in front, whose latency programmatic launch hides under the projection's
+  // weight prefetch: LM-head shard of 31 040 rows 30.8 -> 32.4 us per step, 248 320 rows
+  // 185.6 -> 188.2 us (the chain row load -> amax -> scale -> code tile delays the first UMMA of
+  // every CTA).
+  const long long fq_tiles = (out_rows + 127) / 128;
   const bool fuse_quant = input != nullptr && rows <= kFusedQuantRows && ctx_.tuning().fused_quant != 0 &&
-                          (ctx_.forced_block_tok() == 0 || ctx_.forced_block_tok() == 16);
+                          (ctx_.forced_block_tok() == 0 || ctx_.forced_block_tok() == 16) &&
+                          (fq_tiles <= 3LL * ctx_.sm_count() || ctx_.tuning().fused_quant == 2);
   if (input && fuse_quant) TK100_TRY(check_plane(ctx_, name_, "input", input, 16));
   if (input && !fuse_quant) {
     TK100_TRY(quantize(stream, rows, columns, input, activation_codes, activation_scales));
@@ -442,6 +449,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
       q.out = output;
       q.status = ctx_.status_word();
       q.debug = debug_flags();
+      q.stamps = debug_stamps();
       ctx_.count_launch();
       ctx_.note_route("fp8_pair_kernel", q.deep_ring ? 6 : 3, 0, 1, 1);
       return ctx_.check(launch_fp8_pair(stream, map_w, map_a, q), "launching the FP8 pair projection");
@@ -521,6 +529,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
   p.debug = debug_flags();
+  p.stamps = debug_stamps();
   if (fuse_quant) {
     p.x_bf16 = input;
     p.codes_out = activation_codes;
@@ -679,6 +688,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
       q.out_f32 = output_f32;
       q.status = ctx_.status_word();
       q.debug = debug_flags();
+      q.stamps = debug_stamps();
       ctx_.count_launch();
       ctx_.note_route("nvfp4_pair_kernel", gate_up ? 1 : 0, 0, 1, 1);
       TK100_TRY(ctx_.check(launch_nvfp4_pair(stream, gate_up, map_w, map_a, map_wsf, map_asf, q),
@@ -737,6 +747,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   p.counters = ctx_.counters();
   p.status = ctx_.status_word();
   p.debug = debug_flags();
+  p.stamps = debug_stamps();
   // gate/up runs as clusters of two plain tiles (gate CTA, up CTA; two CTAs per SM) that swap
   // half of their accumulators over distributed shared memory, each finishing half of the
   // tokens.  Measured against the fused kernel (one CTA holds both tiles, one CTA per SM):

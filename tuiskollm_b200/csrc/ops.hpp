@@ -37,7 +37,9 @@ struct Tuning {
   int nvfp4_pair_min_rows = 1024;
   int swiglu_pairs = 1;       // TK100_SWIGLU_PAIRS=0: one CTA holds the gate and the up tile
   int fused_exchange = 1;     // TK100_FUSED_TAIL=0: argmax finalize / exchange as launches of their own
-  int fused_quant = 1;        // TK100_FUSED_QUANT=0: the activation quantiser always as its own launch
+  int fused_quant = 0;        // TK100_FUSED_QUANT=1: launches of one wave and at most 4 rows quantise
+                              // inside the projection kernel, 2: at every size (measured slower
+                              // than the quantiser launch in front, so off by default)
   static Tuning from_environment();
 };
 
