@@ -214,6 +214,56 @@ def test_split_k_is_exact_and_deterministic(tk, oracle, splits, block_tok):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("rows", [1, 8, 16, 32])
+def test_split_k_reduction_routes_agree_bit_for_bit(tk, oracle, rows, monkeypatch):
+    """The three split-K reductions -- partial tiles pushed into a leader CTA's shared memory
+    (TK100_CLUSTER=2, an experiment switch), the symmetric two-barrier cluster reduction (1, what
+    the default takes) and fp32 tiles in global scratch behind a ticket (0) -- add the same partials in the same
+    order: every output bit must agree, at the decode shape of the QKV plane (N = 8192: six splits),
+    eagerly and under graph replay."""
+    from tuiskollm_b200 import synth
+
+    hidden, out_rows = 5120, 8192
+    xb = synth.normal_bf16(45, rows, (rows, hidden))
+    w, s = synth.torch_fp8_weights(45, 1, out_rows, hidden, "cuda")
+    x = dev(xb.view(np.int16))
+    outs, routes = {}, {}
+    for mode in ("2", "1", "0"):
+        monkeypatch.setenv("TK100_CLUSTER", mode)
+        c = tk.Context(device=0)
+        planes = Planes(rows + 1, hidden, out_rows)
+        op = tk.FullAttentionQkvOp(c, out_rows)
+        launch = lambda: op.launch(None, rows, x, planes.codes, planes.scales, w, s, planes.out)
+        launch()
+        torch.cuda.synchronize()
+        routes[mode] = c.last_kernel
+        eager = _u16(planes.out).copy()
+        g = graph_replay(launch)
+        planes.reset()
+        g.replay()
+        g.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(_u16(planes.out), eager), mode
+        planes.check_inactive(rows)
+        assert c.device_status() == 0, mode
+        outs[mode] = eager[:rows]
+    assert "splits=6" in routes["2"], routes
+    assert ("cluster-leader" in routes["2"]) == (rows <= 16), routes  # 32 rows x 5 tiles exceed the ring
+    monkeypatch.delenv("TK100_CLUSTER")
+    c = tk.Context(device=0)
+    planes = Planes(rows + 1, hidden, out_rows)
+    tk.FullAttentionQkvOp(c, out_rows).launch(None, rows, x, planes.codes, planes.scales, w, s, planes.out)
+    torch.cuda.synchronize()
+    assert c.last_kernel == routes["1"], (c.last_kernel, routes)
+    assert np.array_equal(_u16(planes.out)[:rows], outs["1"])
+    assert "cluster-leader" not in routes["1"] and "cluster" in routes["1"] and "cluster" not in routes["0"]
+    assert np.array_equal(outs["2"], outs["1"]) and np.array_equal(outs["2"], outs["0"])
+    oc, os_ = oracle.quantize_e4m3(xb)
+    sample = np.r_[0:256, 4000:4128, out_rows - 128:out_rows]
+    exp = oracle.fp8_projection(oc, os_, host(w)[sample], _u16(s)[sample])
+    assert max_relative_error(outs["2"][:, sample], exp, 0.25) <= 1e-2
+
+
 def test_fused_producer_feeds_projection(tk, ctx, oracle):
     """Decode slice of the first benchmark configuration: residual add + RMSNorm + quantise in
     one kernel, then the QKV projection reads the codes it wrote (input == NULL)."""

@@ -475,6 +475,57 @@ def test_full_size_prefill_sampled_tiles(tk, ctx, oracle):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("rows", [1, 8, 32, 200])
+def test_reduction_routes_of_the_mlp_agree_bit_for_bit(tk, oracle, rows, monkeypatch):
+    """Gate/up pairs and the split-K down projection with their partial tiles pushed into the
+    finishing CTA's shared memory (TK100_CLUSTER=2; by default only the pairs at 128-token tiles
+    push) against the two-barrier cluster exchange (1) and, for down, the global-scratch
+    reduction (0): same bits in the intermediate, in its NVFP4 form and in the output, at the full
+    MLP geometry."""
+    from tuiskollm_b200 import ops, synth
+
+    x = synth.torch_normal_bf16(17, rows, (rows, HIDDEN), "cuda")
+    gu = synth.torch_nvfp4_weights(17, 1, 2 * INTER, HIDDEN, "cuda")
+    dn = synth.torch_nvfp4_weights(17, 2, HIDDEN, INTER, "cuda")
+    a_div, m_div = float(np.float32(448.0)), float(np.float32(448.0 * 6.0 / 8.0))
+    got, routes = {}, {}
+    for mode in ("2", "1", "0"):
+        monkeypatch.setenv("TK100_CLUSTER", mode)
+        c = tk.Context(device=0)
+        a_codes, a_scales = act_planes(tk, rows + 1, HIDDEN)
+        m_codes, m_scales = act_planes(tk, rows + 1, INTER)
+        mid = sentinel_plane((rows + 1, INTER), torch.int16)
+        out = sentinel_plane((rows + 1, HIDDEN), torch.int16)
+        tk.Nvfp4SwiGluOp(c).launch_quantize(None, rows, x, gu[0], gu[1], gu[2], mid,
+                                            activation_codes=a_codes, activation_scales=a_scales,
+                                            input_global_divisor=a_div, output_global_divisor=m_div,
+                                            output_codes=m_codes, output_scales=m_scales)
+        r_gu = c.last_kernel
+        tk.Nvfp4DownOp(c).launch(None, rows, None, dn[0], dn[1], dn[2], out, activation_codes=m_codes,
+                                 activation_scales=m_scales, input_global_divisor=m_div)
+        torch.cuda.synchronize()
+        routes[mode] = (r_gu, c.last_kernel)
+        assert c.device_status() == 0, mode
+        for pl in (mid, out, m_codes):
+            assert_inactive_untouched(pl, rows)
+        got[mode] = (_u16(mid)[:rows].copy(), host(m_codes)[:rows].copy(), _u16(out)[:rows].copy())
+    assert "cluster-leader" in routes["2"][0] and "cluster-leader" not in routes["1"][0], routes
+    if rows <= 32:
+        assert "cluster-leader" in routes["2"][1], routes
+    for mode in ("1", "0"):
+        for a, b in zip(got["2"], got[mode]):
+            assert np.array_equal(a, b), (mode, routes)
+    # and the values are the W4A4 oracle's on a sample of the outputs
+    xb = _u16(x.view(torch.int16))
+    oc, osc = oracle.nvfp4_quantize(xb, a_div)
+    g = HIDDEN // 16
+    wc = np.concatenate([host(gu[0][:128]), host(gu[0][INTER:INTER + 128])])
+    ws = np.concatenate([host(gu[1][:128 * g]), host(gu[1][(INTER // 128) * 128 * g:(INTER // 128 + 1) * 128 * g])])
+    dots = oracle.nvfp4_w4a4_dot(oc, osc, a_div, wc, ws, gu[2])
+    exp = oracle.silu_mul(dots[:, :128], dots[:, 128:])
+    assert max_relative_error(got["2"][0][:, :128], exp, 4 * float(np.abs(exp).mean())) <= 1e-2
+
+
 def test_full_size_prefill_down_sampled_tiles(tk, ctx, oracle):
     """Configuration 4's down projection at full size (M = 2048, 5120 x 17408: unsplit 128-token
     tiles over 68 k-blocks): first, last and two inner weight tiles x first and last token tile

@@ -53,6 +53,8 @@ struct Control {
   uint64_t full[stages_for(BLOCK_TOK, 1)];
   uint64_t empty[stages_for(BLOCK_TOK, 1)];
   uint64_t tmem_full;
+  uint64_t go;    // split-K on a leader: the leader's ring is free, peers may store into it
+  uint64_t done;  // split-K on a leader: every peer's partial tile has landed (leader only)
   unsigned long long red[BLOCK_TOK];  // per-token argmax keys of this CTA
   float a_scale[BLOCK_TOK];
   float q_amax[4][kFusedQuantRows];  // fused quantiser: per-warp maxima of the epilogue warps
@@ -186,24 +188,10 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     }
   }
 
-  // A wait that timed out earlier in this stream has already made the results invalid:
-  // later CTAs leave at once instead of queueing more multi-second waits.  (Under
-  // programmatic launch the predecessor may still be running; a fault it raises after this
-  // read is caught by this kernel's own bounded waits.)
-  if (threadIdx.x == 0) ctl->is_last = *reinterpret_cast<volatile uint32_t*>(p.status);
-  __syncthreads();
-  const bool dead = (ctl->is_last & STATUS_WAIT_TIMEOUT) != 0;
   const bool clustered = p.cluster != 0 && p.splits > 1;
-  if (dead) {
-    // still owed to the other CTAs of the cluster: both cluster barriers
-    if (clustered) {
-      cluster_arrive();
-      cluster_wait();
-      cluster_arrive();
-      cluster_wait();
-    }
-    return;
-  }
+  // Split-K on a leader (p.cluster == 2): the peers store their partial tiles into the leader's
+  // shared memory and leave; the leader adds them in split order and finishes every token.
+  const bool on_leader = clustered && p.cluster == 2;
 
   // Fused activation quantiser (16-token tiles only): the epilogue warps make each stage's code
   // tile themselves, so a full[] barrier takes two arrivals: the weight TMA and that warp.
@@ -214,7 +202,10 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       mbar_init(&ctl->full[s], fused_quant ? 2 : 1);
       mbar_init(&ctl->empty[s], 1);
     }
+    ctl->is_last = 0u;
     mbar_init(&ctl->tmem_full, 1);
+    mbar_init(&ctl->go, 1);
+    mbar_init(&ctl->done, on_leader ? static_cast<uint32_t>(p.splits - 1) * 4u : 1u);
     fence_mbar_init();
     prefetch_tensormap(&tmap_w);
     if (!fused_quant) prefetch_tensormap(&tmap_a);
@@ -228,6 +219,9 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_base;
   pdl_trigger();
+  // the cluster's barriers exist from here on; the matching wait comes just before the first
+  // access to a peer's shared memory, long after every CTA has passed this point
+  if (on_leader) cluster_arrive();
   if (threadIdx.x == 0) TK100_STAMP(p, 1);
 
   if (warp == 0) {
@@ -508,6 +502,64 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
           }
         }
       }
+    } else if (on_leader) {
+      const uint32_t rank = cluster_cta_rank();  // = split: cluster dimension z covers the splits
+      cluster_wait();  // every CTA of the cluster has initialised its barriers
+      float* land = reinterpret_cast<float*>(smem);  // leader: [split - 1][token][row] over the ring
+      if (rank == 0) {
+        // the leader's MMAs have read the whole ring (tmem_full): the peers may store into it
+        if (et == 0) {
+          for (int r = 1; r < p.splits; ++r) mbar_arrive_remote(mapa_u32(smem_u32(&ctl->go), r));
+        }
+        mbar_wait_cluster(&ctl->done, 0, p.status);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+          if (c0 >= valid_tok) break;
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j0 = 0; j0 < 16; j0 += 4) {
+            if (c0 + j0 < valid_tok) {  // warp-uniform
+              float v[kMaxSplits][4];
+#pragma unroll
+              for (int sidx = 1; sidx < kMaxSplits; ++sidx) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[sidx][j] = (sidx < p.splits && c0 + j0 + j < valid_tok)
+                                   ? land[(static_cast<size_t>(sidx - 1) * valid_tok + c0 + j0 + j) * kTileRows + row_in_tile]
+                                   : 0.0f;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float acc = __fadd_rn(0.0f, __uint_as_float(r[j0 + j]));  // split 0 = this CTA
+#pragma unroll
+                for (int sidx = 1; sidx < kMaxSplits; ++sidx) {
+                  if (sidx < p.splits) acc = __fadd_rn(acc, v[sidx][j]);  // fixed split order
+                }
+                if (c0 + j0 + j < valid_tok) emit(c0 + j0 + j, acc);
+              }
+            }
+          }
+        }
+      } else {
+        mbar_wait_cluster(&ctl->go, 0, p.status);
+        const uint32_t slot = mapa_u32(smem_u32(land + static_cast<size_t>(rank - 1) * valid_tok * kTileRows + row_in_tile), 0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_TOK; c0 += 16) {
+          if (c0 >= valid_tok) break;
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid_tok) st_dsmem_f32(slot + static_cast<uint32_t>(c0 + j) * kTileRows * 4, __uint_as_float(r[j]));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(mapa_u32(smem_u32(&ctl->done), 0));
+      }
     } else if (clustered) {
       // Own partial tile -> own shared memory ([token][row] fp32, over ring stage 0, which
       // this CTA's MMAs have finished reading once tmem_full has fired).
@@ -584,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       }
     }
 
-    if (clustered) {
+    if (clustered && !on_leader) {
       // Every CTA of the cluster has published its tile after the first barrier; CTA `rank`
       // then finishes the tokens j = rank, rank + splits, ...: partials are read from the
       // peers' shared memory and added in split order (fixed, so bit-reproducible).
@@ -623,7 +675,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     }
 
     if (want_argmax && !TK100_DBG(p, DBG_NO_EPILOGUE) &&
-        (p.splits == 1 || clustered || ctl->is_last)) {
+        (p.splits == 1 || (clustered && !on_leader) || (on_leader && split == 0) || ctl->is_last)) {
       epilogue_barrier();
       for (int j = et; j < valid_tok; j += kEpilogueThreads) {
         const unsigned long long best = ctl->red[j];
@@ -672,7 +724,9 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     }
   }
   if (threadIdx.x == 64) TK100_STAMP(p, 6);
-  if (clustered && warp < 2) {
+  if (on_leader && warp < 2) {
+    cluster_wait();  // completes the barrier every thread arrived on after set-up
+  } else if (clustered && warp < 2) {
     // the TMA and UMMA warps take part in the two cluster barriers of the reduction
     cluster_arrive();
     cluster_wait();

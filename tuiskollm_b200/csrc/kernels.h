@@ -118,7 +118,10 @@ struct Fp8ProjParams {
   int l2_prefetch;  // > 0: before waiting for the predecessor, ask L2 for up to this many weight
                     // k-blocks beyond the ring (short weight streams that fit L2)
   int cluster;    // 1: the splits of a tile form a thread-block cluster and reduce over
-                  // distributed shared memory; 0: fp32 partial tiles in `partials` + tickets
+                  // distributed shared memory (every CTA finishes a share of the tokens, two
+                  // cluster barriers); 2: the peers store their partial tiles into the leader's
+                  // shared memory and leave, the leader finishes every token;
+                  // 0: fp32 partial tiles in `partials` + tickets
   const float* act_scales;      // [rows]
   const uint16_t* w_scales;     // [out_rows] BF16
   uint16_t* out;                // [rows, out_rows] BF16, may be null for the LM head
@@ -195,7 +198,9 @@ struct Nvfp4Params {
   int out_rows;        // outputs per token (weight rows of one tile family), multiple of 128
   int k;               // reduction length in elements, multiple of 256
   int splits;          // K splits (1 with gate/up fusion)
-  int cluster;         // 1: the splits of a tile reduce over distributed shared memory
+  int cluster;         // 1: the splits of a tile (or a gate/up pair) reduce over distributed shared
+                       // memory with two cluster barriers; 2: partial tiles are pushed into the
+                       // CTA that finishes them (split K: the leader; pairs: the partner)
   int pair_swiglu;     // 1: plain tiles in clusters of two (gate tile, up tile): the up CTA hands
                        // its accumulator to the gate CTA, which writes bf16(silu(gate) * up)
   int up_row_offset;   // gate/up fusion: first weight row of the up half (= out_rows)
@@ -218,6 +223,9 @@ struct Nvfp4Params {
 };
 
 cudaError_t nvfp4_prepare();
+// Bytes of the shared-memory ring of the plain projection kernel at this token tile (what a
+// pushed reduction may land in).
+size_t nvfp4_ring_bytes(int block_tok);
 // block_tok 32 or 128.  gate_up: weight plane holds gate rows then up rows; output is
 // bf16(silu(gate) * up).
 cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,

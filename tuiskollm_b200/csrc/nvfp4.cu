@@ -57,6 +57,8 @@ struct NvControl {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full;
+  uint64_t go;    // a cluster peer's ring is free: this CTA may store into the peer's shared memory
+  uint64_t done;  // the peers' stores into this CTA's shared memory have landed
   uint32_t tmem_base;
   uint32_t flag;
 };
@@ -158,18 +160,12 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
     }
   }
 
-  if (threadIdx.x == 0) ctl->flag = *reinterpret_cast<volatile uint32_t*>(p.status);
-  __syncthreads();
   const bool clustered = !GATE_UP && p.cluster != 0 && p.splits > 1;
-  if (ctl->flag & STATUS_WAIT_TIMEOUT) {
-    if (clustered || (!GATE_UP && p.pair_swiglu != 0)) {  // still owed to the cluster: both barriers of the reduction
-      cluster_arrive();
-      cluster_wait();
-      cluster_arrive();
-      cluster_wait();
-    }
-    return;
-  }
+  // p.cluster == 2: partial tiles are pushed into a peer's shared memory and summed there (split K:
+  // into the leader, which finishes every token; gate/up pairs: each CTA sends the half of its
+  // accumulator that the partner finishes), one-way stores and barrier arrivals instead of two
+  // cluster barriers around remote loads.
+  const bool pushed = !GATE_UP && p.cluster == 2 && (clustered || pair_swiglu);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -177,6 +173,10 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
       mbar_init(&ctl->empty[s], 1);
     }
     mbar_init(&ctl->tmem_full, 1);
+    mbar_init(&ctl->go, 1);
+    // arrivals: one per epilogue warp of every sending CTA
+    mbar_init(&ctl->done, pushed ? static_cast<uint32_t>(pair_swiglu ? 1 : p.splits - 1) * (kEpilogueThreads / 32) : 1u);
+    ctl->flag = 0u;
     fence_mbar_init();
     prefetch_tensormap(&tmap_w);
     prefetch_tensormap(&tmap_a);
@@ -190,6 +190,9 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_base;
   pdl_trigger();
+  // the cluster's barriers exist from here on; the matching wait comes just before the first
+  // access to a peer's shared memory
+  if (pushed) cluster_arrive();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -332,6 +335,27 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
           }
         }
       }
+    } else if (pair_swiglu && pushed) {
+      // Each CTA finishes half of the token tile: the gate CTA tokens [0, H), the up CTA [H, 2H).
+      // It sends the other half of its accumulator straight into the partner's shared memory
+      // ([token][row] fp32 over the partner's ring, once the partner says its ring is free).
+      constexpr int H = BLOCK_TOK / 2;
+      const int send0 = pair_rank == 0 ? H : 0;
+      cluster_wait();  // both CTAs have initialised their barriers
+      if (et == 0) mbar_arrive_remote(mapa_u32(smem_u32(&ctl->go), pair_rank ^ 1u));  // my ring is free
+      mbar_wait_cluster(&ctl->go, 0, p.status);
+      const uint32_t slot = mapa_u32(smem_u32(reinterpret_cast<float*>(smem) + row_in_tile), pair_rank ^ 1u);
+#pragma unroll 1
+      for (int c = half * 16; c < H; c += 32) {
+        if (send0 + c >= valid_tok) break;
+        uint32_t r[16];
+        tmem_ld16(taddr + send0 + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) st_dsmem_f32(slot + static_cast<uint32_t>(c + j) * kRows * 4, __uint_as_float(r[j]));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(mapa_u32(smem_u32(&ctl->done), pair_rank ^ 1u));
     } else if (pair_swiglu) {
       // Each CTA finishes half of the token tile: the gate CTA tokens [0, H), the up CTA
       // [H, 2H).  Here it parks the other half of its accumulator ([token][row] fp32 over the
@@ -364,6 +388,68 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
             else p.out[o] = static_cast<uint16_t>(f32_to_bf16_bits(v));
           }
         }
+      }
+    } else if (clustered && pushed) {
+      const uint32_t rank = cluster_cta_rank();  // = split
+      cluster_wait();
+      float* land = reinterpret_cast<float*>(smem);  // leader: [split - 1][token][row] over its ring
+      if (rank == 0) {
+        if (et == 0) {
+          for (int r = 1; r < p.splits; ++r) mbar_arrive_remote(mapa_u32(smem_u32(&ctl->go), r));
+        }
+        mbar_wait_cluster(&ctl->done, 0, p.status);
+#pragma unroll 1
+        for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+          if (c0 >= valid_tok) break;
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j0 = 0; j0 < 16; j0 += 4) {
+            if (c0 + j0 < valid_tok) {  // warp-uniform
+              float v[8][4];
+#pragma unroll
+              for (int sp = 1; sp < 8; ++sp) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[sp][j] = (sp < p.splits && c0 + j0 + j < valid_tok)
+                                 ? land[(static_cast<size_t>(sp - 1) * valid_tok + c0 + j0 + j) * kRows + row_in_tile]
+                                 : 0.0f;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float acc = __fadd_rn(0.0f, __uint_as_float(r[j0 + j]));  // split 0 = this CTA
+#pragma unroll
+                for (int sp = 1; sp < 8; ++sp) {
+                  if (sp < p.splits) acc = __fadd_rn(acc, v[sp][j]);  // fixed split order
+                }
+                if (c0 + j0 + j < valid_tok && row_ok) {
+                  const size_t o = static_cast<size_t>(tok0 + c0 + j0 + j) * p.out_rows + n;
+                  const float val = __fmul_rn(acc, s);
+                  if (p.out_f32) p.out_f32[o] = val;
+                  else p.out[o] = static_cast<uint16_t>(f32_to_bf16_bits(val));
+                }
+              }
+            }
+          }
+        }
+      } else {
+        mbar_wait_cluster(&ctl->go, 0, p.status);
+        const uint32_t slot = mapa_u32(smem_u32(land + static_cast<size_t>(rank - 1) * valid_tok * kRows + row_in_tile), 0);
+#pragma unroll 1
+        for (int c0 = half * 16; c0 < BLOCK_TOK; c0 += 32) {
+          if (c0 >= valid_tok) break;
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid_tok) st_dsmem_f32(slot + static_cast<uint32_t>(c0 + j) * kRows * 4, __uint_as_float(r[j]));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(mapa_u32(smem_u32(&ctl->done), 0));
       }
     } else if (clustered) {
       // split-K inside a thread-block cluster: park the partial tile in this CTA's shared
@@ -447,8 +533,12 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
   }
 
   if (pair_swiglu) {
-    cluster_arrive();
-    cluster_wait();
+    if (pushed) {
+      if (warp >= 2) mbar_wait_cluster(&ctl->done, 0, p.status);  // the partner's half has landed here
+    } else {
+      cluster_arrive();
+      cluster_wait();
+    }
     if (warp >= 2 && !TK100_DBG(p, DBG_NO_EPILOGUE)) {
       constexpr int H = BLOCK_TOK / 2;
       const int quad = warp & 3;
@@ -467,8 +557,14 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         uint32_t own[16];
         tmem_ld16(taddr + c0, own);
         float oth[16];
+        if (pushed) {  // the partner stored its half into this CTA's shared memory
+          const float* landed = reinterpret_cast<const float*>(smem) + row_in_tile;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) oth[j] = ld_dsmem_f32(other_addr + (c + j) * kRows * 4, pair_rank ^ 1u);
+          for (int j = 0; j < 16; ++j) oth[j] = landed[(c + j) * kRows];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) oth[j] = ld_dsmem_f32(other_addr + (c + j) * kRows * 4, pair_rank ^ 1u);
+        }
         tmem_ld_wait();
         uint32_t bits[16];
 #pragma unroll
@@ -518,11 +614,17 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
         }
       }
     }
-    cluster_arrive();  // both CTAs keep their shared memory until the partner has read it
-    cluster_wait();
+    if (pushed) {
+      if (warp < 2) cluster_wait();  // completes the barrier every thread arrived on after set-up
+    } else {
+      cluster_arrive();  // both CTAs keep their shared memory until the partner has read it
+      cluster_wait();
+    }
   }
 
-  if (clustered) {
+  if (clustered && pushed) {
+    if (warp < 2) cluster_wait();  // completes the barrier every thread arrived on after set-up
+  } else if (clustered) {
     // CTA `rank` of the cluster finishes tokens rank, rank + S, ...: partials come from the
     // peers' shared memory and are added in split order (fixed => bit-reproducible).
     cluster_arrive();
@@ -653,6 +755,11 @@ cudaError_t nv_prepare() {
 }
 
 }  // namespace
+
+size_t nvfp4_ring_bytes(int block_tok) {
+  return block_tok <= 32 ? static_cast<size_t>(nv_stages(32, false)) * nv_stage_bytes(32, false)
+                         : static_cast<size_t>(nv_stages(128, false)) * nv_stage_bytes(128, false);
+}
 
 cudaError_t nvfp4_prepare() {
   cudaError_t e;

@@ -173,7 +173,7 @@ Context::~Context() {
 const char* Context::last_kernel() {
   char text[160];
   std::snprintf(text, sizeof text, "%s<%d,%d> splits=%d%s", route_.family, route_.a, route_.b,
-                route_.splits, route_.cluster ? " cluster" : "");
+                route_.splits, route_.cluster == 2 ? " cluster-leader" : route_.cluster ? " cluster" : "");
   route_text_ = text;
   return route_text_.c_str();
 }
@@ -501,6 +501,16 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   p.k = columns;
   p.splits = splits;
   p.cluster = ctx_.tuning().cluster != 0 ? 1 : 0;
+  if (p.cluster && splits > 1 && ctx_.tuning().cluster == 2) {
+    // TK100_CLUSTER=2: split-K on a leader CTA when the peers' partial tiles fit its ring
+    // ((splits - 1) tiles of [tokens][128 rows] fp32).  Measured against the symmetric reduction:
+    // no gain at one token (QKV 10.0 -> 10.3 us: the "ring is free" handshake costs the hop that
+    // the second cluster barrier used to), a loss at 32 (GDN-in 16.3 -> 21.5 us: one CTA finishes
+    // every token), so it stays an experiment switch.
+    const size_t ring = static_cast<size_t>(fp8_projection_stages(block_tok)) * (128 * 128 + block_tok * 128);
+    const size_t land = static_cast<size_t>(splits - 1) * (rows < block_tok ? rows : block_tok) * 128 * sizeof(float);
+    if (land <= ring) p.cluster = 2;
+  }
   {
     const bool dr = ctx_.tuning().deep_ring >= 0;
     // unsplit launches with at most two CTAs per SM (an LM-head shard on 8 GPUs): measured
@@ -550,7 +560,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   {
     // the ring variant launch_fp8_projection picks for this tile size
     const int ring = (block_tok <= 32 && p.deep_ring == 1) ? 1 : (block_tok <= 16 && p.deep_ring == 2) ? 2 : 0;
-    ctx_.note_route("fp8_projection_kernel", block_tok, ring, splits, p.cluster && splits > 1);
+    ctx_.note_route("fp8_projection_kernel", block_tok, ring, splits, splits > 1 ? p.cluster : 0);
   }
   TK100_TRY(ctx_.check(launch_fp8_projection(stream, block_tok, map_w, map_a, p),
                        "launching the FP8 projection"));
@@ -759,6 +769,18 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
     p.pair_swiglu = 1;
     p.splits = 1;
   }
+  if (p.cluster && ctx_.tuning().cluster != 1) {
+    // Pushed exchange (one-way stores and barrier arrivals, no second cluster barrier) for the
+    // gate/up pairs at 128-token tiles (M = 2048: 320.6 -> 313.0 us; at decode sizes it measured
+    // the same or slightly slower, 21.9 -> 22.0 us).  TK100_CLUSTER=2 pushes everywhere it fits,
+    // split K included (down, M = 1: 14.05 -> 14.6 us, so off by default).
+    const size_t land = static_cast<size_t>(p.splits - 1) * (rows < block_tok ? rows : block_tok) * 128 * sizeof(float);
+    const bool everywhere = ctx_.tuning().cluster == 2;
+    if ((as_pairs && (block_tok == 128 || everywhere)) ||
+        (everywhere && p.splits > 1 && land <= nvfp4_ring_bytes(block_tok))) {
+      p.cluster = 2;
+    }
+  }
   // Decode shapes quantise in the epilogue of the CTA that finishes the tokens (saves a launch:
   // M = 1 23.2 -> 22.1 us); from 128-token tiles on that epilogue work is not hidden and the
   // quantiser kernel after the projection is faster (M = 2048: 351 against 419 us).
@@ -770,7 +792,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
   }
   ctx_.count_launch();
   ctx_.note_route("nvfp4_gemm_kernel", block_tok, gate_up && !as_pairs ? 1 : 0, p.splits,
-                  as_pairs || (p.cluster && p.splits > 1));
+                  (as_pairs || p.splits > 1) ? p.cluster : 0);
   TK100_TRY(ctx_.check(launch_nvfp4_gemm(stream, block_tok, gate_up && !as_pairs, map_w, map_a, p),
                        "launching the NVFP4 projection"));
   return in_epilogue ? TK100_OK : quantise_after();

@@ -30,7 +30,10 @@ struct Tuning {
   int deep_ring = -1;         // TK100_DEEP_RING: ring variant of the FP8 projection
   int l2_prefetch = 0;        // TK100_L2_PREFETCH: FP8 weight k-blocks queued at L2 first
   int nvfp4_l2_prefetch = 0;  // TK100_NVFP4_L2_PREFETCH
-  int cluster = 1;            // TK100_CLUSTER=0: split-K through global scratch instead of DSMEM
+  int cluster = 3;            // TK100_CLUSTER=0: split-K through global scratch instead of DSMEM,
+                              // 1: symmetric two-barrier cluster exchange everywhere, 2: partial
+                              // tiles pushed into the finishing CTA wherever they fit, 3 (default):
+                              // pushed for the gate/up pairs at 128-token tiles only
   int fp8_pair = 1;           // TK100_FP8_PAIR: 0 off, 1 from 32 pair CTAs, 2 always
   int fp8_pair_min_rows = 256;
   int nvfp4_pair = 0;         // TK100_PAIR: 1 down, 2 gate_up too (cta_group::2 variant)

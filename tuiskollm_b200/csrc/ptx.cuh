@@ -69,6 +69,14 @@ __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
 
+// shared::cluster address of the byte at local shared-memory address `local_smem_addr` in CTA
+// `rank` of this cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  return remote;
+}
+
 // fp32 load from the shared memory of CTA `rank` of this cluster, at the same offset as the
 // local shared-memory address `local_smem_addr` (distributed shared memory).
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_smem_addr, uint32_t rank) {
@@ -116,13 +124,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: about two seconds of wall time, then STATUS_WAIT_TIMEOUT and false.
+// Bounded wait: about two seconds of wall time, then STATUS_WAIT_TIMEOUT and false.  A wait that
+// gave up earlier in this stream has already made the results invalid, so once the bit is set
+// every later slow wait gives up at its first look instead of queueing more multi-second waits
+// (no kernel reads the status word on its way in: that load sat on every CTA's critical path).
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, uint32_t* status) {
   const uint64_t start = global_timer_ns();
   for (;;) {
     for (int i = 0; i < 1024; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
+    if (status && (*reinterpret_cast<volatile uint32_t*>(status) & STATUS_WAIT_TIMEOUT)) return false;
     if (global_timer_ns() - start > 2000000000ull) {
       if (status) atomicOr(status, STATUS_WAIT_TIMEOUT);
       return false;
@@ -136,6 +148,46 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     if (mbar_try_wait(bar, parity)) return true;
   }
   return mbar_wait_slow(bar, parity, status);
+}
+
+// Cluster-scope forms for barriers that CTAs of the same cluster arrive on remotely
+// (`cluster_addr` from mapa_u32): the arrive releases the arriving thread's prior writes --
+// its stores into the owner's shared memory included -- and the owner's wait acquires them.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded like mbar_wait.
+static __device__ __noinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t* status) {
+  const uint64_t start = global_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 1024; ++i) {
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    }
+    if (status && (*reinterpret_cast<volatile uint32_t*>(status) & STATUS_WAIT_TIMEOUT)) return false;
+    if (global_timer_ns() - start > 2000000000ull) {
+      if (status) atomicOr(status, STATUS_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+
+// fp32 store into the shared memory of another CTA of this cluster (`cluster_addr` from mapa_u32).
+__device__ __forceinline__ void st_dsmem_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
 // ----------------------------------------------------------------------- TMA
@@ -281,12 +333,6 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // Two CTAs of a cluster (ranks 2k, 2k+1) work as one UMMA unit: each holds 128 rows of the
 // "A" operand and half of the "B" columns in its own shared memory and 128 lanes of the
 // accumulator in its own TMEM; the even CTA issues the instructions for both.
-
-__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
-  return remote;
-}
 
 // Tiled load into this CTA's shared memory whose completion is counted on a barrier that may
 // live in the pair's other CTA (`mbar_cluster_addr` is a shared::cluster address); the data
