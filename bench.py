@@ -589,6 +589,50 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
                           "cpu": ("fp8", m, n_rows, HIDDEN)}
             keep.append((graph, x, codes, scales, outp, w, s))
 
+    # ---- the next rows of the path: dense-FP8 MLP (gate/up + SwiGLU, down) and the GDN output projection
+    gdn_value = 6144
+    for m in (1, 32, 256):
+        copies = 3 if m <= 32 else 1
+        gu_planes = [synth.torch_fp8_weights(SEED, 70 + c, 2 * inter, HIDDEN, dev) for c in range(copies)]
+        dn_planes = [synth.torch_fp8_weights(SEED, 75 + c, HIDDEN, inter, dev) for c in range(copies)]
+        go_planes = [synth.torch_fp8_weights(SEED, 80 + c, HIDDEN, gdn_value, dev) for c in range(max(copies, 4 if m <= 32 else 1))]
+        x = synth.torch_normal_bf16(SEED, 9, (m, HIDDEN), dev)
+        xi = synth.torch_normal_bf16(SEED, 10, (m, inter), dev)
+        xg = synth.torch_normal_bf16(SEED, 11, (m, gdn_value), dev)
+        c1 = torch.empty((m, HIDDEN), dtype=torch.uint8, device=dev)
+        c2 = torch.empty((m, inter), dtype=torch.uint8, device=dev)
+        c3 = torch.empty((m, gdn_value), dtype=torch.uint8, device=dev)
+        s1, s2, s3 = (torch.empty((m,), dtype=torch.float32, device=dev) for _ in range(3))
+        mid = torch.empty((m, inter), dtype=torch.bfloat16, device=dev)
+        out = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=dev)
+        out_g = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device=dev)
+        sw_op, dn_op, go_op = tk.Fp8SwiGluOp(ctx), tk.Fp8DownOp(ctx), tk.GdnOutputProjectionOp(ctx, gdn_value)
+        sw_op.launch(None, m, x, c1, s1, gu_planes[0][0], gu_planes[0][1], mid)
+        dn_op.launch(None, m, xi, c2, s2, dn_planes[0][0], dn_planes[0][1], out)
+        go_op.launch(None, m, xg, c3, s3, go_planes[0][0], go_planes[0][1], out_g)
+        for nm, op_, planes_, args, by, fl in (
+                ("fp8_swiglu", sw_op, gu_planes, (c1, s1, mid), 2 * inter * HIDDEN + 4 * inter + m * HIDDEN + 4 * m + 2 * m * inter,
+                 2.0 * m * 2 * inter * HIDDEN),
+                ("fp8_down", dn_op, dn_planes, (c2, s2, out), algorithmic_bytes(m, HIDDEN, inter, 2), 2.0 * m * HIDDEN * inter),
+                ("fp8_gdn_output", go_op, go_planes, (c3, s3, out_g), algorithmic_bytes(m, HIDDEN, gdn_value, 2),
+                 2.0 * m * HIDDEN * gdn_value)):
+            state = {"i": 0}
+
+            def run(op_=op_, planes_=planes_, args=args, state=state, m=m):
+                w, sc = planes_[state["i"] % len(planes_)]
+                state["i"] += 1
+                op_.launch(None, m, None, args[0], args[1], w, sc, args[2])
+
+            run()
+            kernel = ctx.last_kernel
+            graph = capture(torch, run, len(planes_))
+            case = f"{nm}:M{m}"
+            proto.add(case, graph.replay, len(planes_))
+            meta[case] = {"config": "next", "op": nm, "M": m, "kernel": kernel,
+                          "kind": "hbm" if m <= 32 else "fp8_tensor", "bytes": by, "flops": fl, "cpu": None}
+            keep.append(graph)
+        keep.append((gu_planes, dn_planes, go_planes, x, xi, xg, c1, c2, c3, s1, s2, s3, mid, out, out_g))
+
     # ---- fused residual + RMSNorm + quantise (configurations 1 and 5, and the metric's M = 512)
     normop = tk.ResidualNormOp(ctx)
     nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)

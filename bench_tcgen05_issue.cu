@@ -88,6 +88,105 @@ __global__ void __launch_bounds__(128, 1) bench_kernel(long long* cycles, uint32
   if (threadIdx.x < 32) tmem_dealloc(tmem, 512);
 }
 
+// CTA pairs (tcgen05 cta_group::2, M = 256, N = 256): the even CTA issues the MMAs for both.
+//   PMODE 0: MMA only.
+//   PMODE 1: per K step three cta_group::2 scale copies (SFA, two SFB tiles), then the MMA.
+//   PMODE 2: every CTA issues its own three copies with cta_group::1 (the odd CTA's run beside
+//            the even CTA's MMAs, unsynchronised: rate only), the even CTA the cta_group::2 MMA.
+template <int PMODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+    pair_kernel(long long* cycles, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  const uint32_t rank = cluster_cta_rank();
+  // kPairStages x ([W 16 KB][A 16 KB (128 tokens)][SF 8 KB]); PMODE >= 3 walks the stages like a
+  // ring (fresh operand addresses every K block of 256), PMODE < 3 stays on stage 0
+  constexpr int kPairStages = 4, kPairStage = 16384 + 16384 + 8192;
+  for (int i = threadIdx.x; i < kPairStages * kPairStage / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(smem)[i] = 0x38383838u;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  fence_proxy_async_smem();
+  if (threadIdx.x < 32) {
+    tmem_alloc_pair(&tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base;
+  if (threadIdx.x == 0) {
+    const uint32_t base0 = smem_u32(smem);
+    const uint32_t sf_base = tmem + 256;
+    constexpr uint32_t IDESC = umma_idesc_nvfp4(256, 256);
+    const long long t0 = clock64();
+    for (int it = 0; it < kIters; ++it) {
+      const int k4 = it & 3;
+      const uint32_t base = base0 + (PMODE >= 3 ? ((it >> 2) % kPairStages) * kPairStage : 0);
+      const uint64_t dw = umma_desc_sw128(base);
+      const uint64_t da = umma_desc_sw128(base + 16384);
+      const uint32_t sfsm = base + 32768;
+      const uint32_t slot = sf_base + (it % 8) * 16;
+      if ((PMODE == 1 || PMODE == 4) && rank == 0) {
+        tmem_cp_32x128b_warpx4_pair(slot, umma_desc_noswizzle_rows16(sfsm + k4 * 512));
+        tmem_cp_32x128b_warpx4_pair(slot + 4, umma_desc_noswizzle_rows16(sfsm + 2048 + k4 * 512));
+        tmem_cp_32x128b_warpx4_pair(slot + 8, umma_desc_noswizzle_rows16(sfsm + 4096 + k4 * 512));
+      }
+      if (PMODE == 2) {
+        tmem_cp_32x128b_warpx4(slot, umma_desc_noswizzle_rows16(sfsm + k4 * 512));
+        tmem_cp_32x128b_warpx4(slot + 4, umma_desc_noswizzle_rows16(sfsm + 2048 + k4 * 512));
+        tmem_cp_32x128b_warpx4(slot + 8, umma_desc_noswizzle_rows16(sfsm + 4096 + k4 * 512));
+      }
+      if (rank == 0) umma_nvfp4_pair(tmem, dw + 2 * k4, da + 2 * k4, IDESC, slot, slot + 4, 1u);
+    }
+    if (rank == 0) {
+      umma_commit_pair(&bar);
+    } else if (PMODE == 2) {
+      umma_commit(&bar);  // the odd CTA's own copies
+    }
+    if (rank == 0 || PMODE == 2) mbar_wait(&bar, 0, status);
+    else mbar_wait(&bar, 0, status);  // the even CTA's commit arrives here too
+    const long long t1 = clock64();
+    cycles[blockIdx.x] = t1 - t0;
+  }
+  __syncthreads();
+  tc_fence_before_sync();
+  cluster_arrive();
+  cluster_wait();
+  if (threadIdx.x < 32) tmem_dealloc_pair(tmem, 512);
+}
+
+template <int PMODE>
+void run_pair(const char* name, long long* d_cycles, uint32_t* d_status) {
+  const size_t smem = 1024 + 4 * (16384 + 16384 + 8192);
+  cudaFuncSetAttribute(pair_kernel<PMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaEvent_t a, b;
+  cudaEventCreate(&a);
+  cudaEventCreate(&b);
+  pair_kernel<PMODE><<<148, 128, smem>>>(d_cycles, d_status);
+  cudaDeviceSynchronize();
+  cudaEventRecord(a);
+  pair_kernel<PMODE><<<148, 128, smem>>>(d_cycles, d_status);
+  cudaEventRecord(b);
+  cudaError_t e = cudaDeviceSynchronize();
+  float ms = 0;
+  cudaEventElapsedTime(&ms, a, b);
+  long long h[148];
+  cudaMemcpy(h, d_cycles, sizeof(h), cudaMemcpyDeviceToHost);
+  uint32_t st = 0;
+  cudaMemcpy(&st, d_status, 4, cudaMemcpyDeviceToHost);
+  const double flop = 2.0 * 256 * 256 * 64 * (double)kIters * 74;
+  printf("%-34s pair M=256 N=256  %8.1f us  %7.1f cycles/k-step  %6.2f PF  (err %d status %u)\n", name,
+         ms * 1e3, (double)h[0] / kIters, flop / (ms * 1e-3) / 1e15, (int)e, st);
+}
+
 template <int N, int MODE>
 void run(const char* name, long long* d_cycles, uint32_t* d_status) {
   const size_t smem = 1024 + 16384 + N * 128 + 8192;
@@ -129,5 +228,10 @@ int main() {
   run<256, 2>("grouped 12 cp then 4 mma", d_cycles, d_status);
   run<64, 0>("mma only", d_cycles, d_status);
   run<64, 1>("interleaved", d_cycles, d_status);
+  run_pair<0>("pair: mma only", d_cycles, d_status);
+  run_pair<1>("pair: 3 cp.cg2 + mma", d_cycles, d_status);
+  run_pair<2>("pair: 3 cp.cg1 per CTA + mma.cg2", d_cycles, d_status);
+  run_pair<3>("pair: mma only, ring of 4 stages", d_cycles, d_status);
+  run_pair<4>("pair: 3 cp.cg2 + mma, ring", d_cycles, d_status);
   return 0;
 }

@@ -92,6 +92,21 @@ unsafe extern "C" {
         input: *const u16, activation_codes: *mut u8, activation_scales: *mut f32,
         weight_codes: *const u8, weight_scales: *const u16, output: *mut u16,
     ) -> Tk100Status;
+    pub fn tk100_fp8_swiglu(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, input: *const u16,
+        activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
+        weight_scales: *const u16, output: *mut u16,
+    ) -> Tk100Status;
+    pub fn tk100_fp8_down(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, input: *const u16,
+        activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
+        weight_scales: *const u16, output: *mut u16,
+    ) -> Tk100Status;
+    pub fn tk100_fp8_gdn_output(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, columns: c_int, input: *const u16,
+        activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
+        weight_scales: *const u16, output: *mut u16,
+    ) -> Tk100Status;
     pub fn tk100_fp8_lm_head(
         ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, vocab_rows: c_int, vocab_offset: c_int,
         input: *const u16, activation_codes: *mut u8, activation_scales: *mut f32,

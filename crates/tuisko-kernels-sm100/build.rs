@@ -12,8 +12,10 @@ const SOURCES: &[&str] = &[
     "norm_quant.cu",
     "fp8_proj.cu",
     "fp8_pair.cu",
+    "fp8_mlp.cu",
     "nvfp4.cu",
     "nvfp4_pair.cu",
+    "nvfp4_persist.cu",
     "peer_reduce.cu",
     "ops.cu",
     "static_entry.cu",

@@ -244,14 +244,53 @@ impl<A: Sm100Arch> GdnOutputProjectionOp<A> {
         output: *mut u16,
     ) -> GpuResult<()> {
         self.ctx.check(unsafe {
-            ffi::tk100_fp8_projection(
-                self.ctx.raw, stream.cu_stream().cast(), rows_i32(rows), A::HIDDEN as i32,
-                A::GDN_VALUE_ROWS as i32, input, activation_codes, activation_scales, weight_codes,
-                weight_scales, output,
+            ffi::tk100_fp8_gdn_output(
+                self.ctx.raw, stream.cu_stream().cast(), rows_i32(rows), A::GDN_VALUE_ROWS as i32,
+                input, activation_codes, activation_scales, weight_codes, weight_scales, output,
             )
         })
     }
 }
+
+macro_rules! fp8_mlp_op {
+    ($(#[$doc:meta])* $name:ident, $entry:ident) => {
+        $(#[$doc])*
+        pub struct $name<A: Sm100Arch = Qwen38_27B> {
+            ctx: Arc<Sm100Context>,
+            _arch: PhantomData<A>,
+        }
+
+        impl<A: Sm100Arch> $name<A> {
+            /// Replaces the module load and route preparation of the sm_120 operator.
+            pub fn new(ctx: &Arc<Sm100Context>) -> GpuResult<Self> {
+                Ok(Self { ctx: Arc::clone(ctx), _arch: PhantomData })
+            }
+
+            /// Same argument order as the sm_120 `launch`.
+            pub unsafe fn launch(
+                &self, stream: &CudaStream, rows: usize, input: *const u16,
+                activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
+                weight_scales: *const u16, output: *mut u16,
+            ) -> GpuResult<()> {
+                self.ctx.check(unsafe {
+                    ffi::$entry(
+                        self.ctx.raw, stream.cu_stream().cast(), rows_i32(rows), input,
+                        activation_codes, activation_scales, weight_codes, weight_scales, output,
+                    )
+                })
+            }
+        }
+    };
+}
+
+fp8_mlp_op!(
+    /// `DenseFp8SwiGluOp` (`tuisko-kernels-sm120/src/fp8/swiglu.rs:366-376`): gate/up + SwiGLU.
+    DenseFp8SwiGluOp, tk100_fp8_swiglu
+);
+fp8_mlp_op!(
+    /// `DenseFp8DownOp` (`tuisko-kernels-sm120/src/fp8/down.rs:197-207`).
+    DenseFp8DownOp, tk100_fp8_down
+);
 
 /// `LmHeadOp` (`tuisko-kernels-sm120/src/fp8/projection.rs:704-793`) with the greedy selection of
 /// `tuisko-engine/src/sampling.rs:162-173` folded into the kernel.

@@ -162,6 +162,31 @@ TK100_API tk100_status tk100_fp8_projection(tk100_ctx* ctx, tk100_stream stream,
                                   float* activation_scales, const uint8_t* weight_codes,
                                   const uint16_t* weight_scales, uint16_t* output);
 
+/* Dense-FP8 MLP (tuisko-engine/src/dense_fp8_mlp.rs:404-452 calls the two in this order).
+ * Fp8SwiGluOp::launch (tuisko-kernels-sm120/src/fp8/swiglu.rs:366-376), same argument order:
+ * weight_codes [2 * intermediate, hidden] E4M3 with the gate rows first, weight_scales
+ * [2 * intermediate] BF16; output [rows, intermediate] = bf16(silu(gate) * up), SiLU as
+ * v / (1 + 2^(-v log2 e)) (device/fp8_swiglu.rs:13-15).  input == NULL: the activation planes
+ * already hold the fused producer's codes and scales. */
+TK100_API tk100_status tk100_fp8_swiglu(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                        const uint16_t* input, uint8_t* activation_codes,
+                                        float* activation_scales, const uint8_t* weight_codes,
+                                        const uint16_t* weight_scales, uint16_t* output);
+/* Fp8DownOp::launch (tuisko-kernels-sm120/src/fp8/down.rs:197-207): input / activation planes
+ * are [rows, intermediate] (the per-token E4M3 quantisation runs over the whole 17 408-wide
+ * row), weight_codes [hidden, intermediate], output [rows, hidden]. */
+TK100_API tk100_status tk100_fp8_down(tk100_ctx* ctx, tk100_stream stream, int rows,
+                                      const uint16_t* input, uint8_t* activation_codes,
+                                      float* activation_scales, const uint8_t* weight_codes,
+                                      const uint16_t* weight_scales, uint16_t* output);
+/* GdnOutputProjectionOp::launch (tuisko-kernels-sm120/src/fp8/gdn_output.rs:178): reduction
+ * length `columns` = the GDN value width (6144 for the reference's model, % 128 == 0), weight_codes
+ * [hidden, columns], output [rows, hidden]. */
+TK100_API tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream, int rows, int columns,
+                                            const uint16_t* input, uint8_t* activation_codes,
+                                            float* activation_scales, const uint8_t* weight_codes,
+                                            const uint16_t* weight_scales, uint16_t* output);
+
 /* LmHeadOp::launch (tuisko-kernels-sm120/src/fp8/projection.rs:751-793) with the greedy
  * selection of tuisko-engine/src/sampling.rs:162-173 folded into the same kernel.
  * vocab_rows / vocab_offset describe this rank's contiguous shard of the vocabulary

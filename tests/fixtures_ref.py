@@ -125,3 +125,62 @@ def nvfp4_closed_form_dot(x_bits: np.ndarray, token: int, row: int, codes, scale
     so = tab[scales[O.nvfp4_scale_offset(row, og, groups)]]
     se = tab[scales[O.nvfp4_scale_offset(row, eg, groups)]]
     return ((groups - 1) * group_dot(og) * so + group_dot(eg) * se) / NVFP4_WEIGHT_SCALE_DIVISOR
+
+
+# ------------------------------------------------ dense-FP8 MLP and GDN output (torch builders)
+# qual/src/fp8_swiglu.rs:13-20, qual/src/fp8_down.rs:13-20, qual/src/gdn_output.rs:13-16
+MLP_TOKEN_FACTORS = np.array([1.0, 0.5, 0.25, 0.125, -1.0, -0.5, -0.25, -0.125], dtype=np.float32)
+GDN_OUT_INPUT_PATTERN = np.array([0.875, -0.75, 0.625, -0.5, 0.375, -0.25, 0.125, -0.0625],
+                                 dtype=np.float32)
+FP8_SWIGLU_ROUTES = (1, 2, 3, 4, 5, 6, 7, 8, 32, 64, 128)  # qual/src/fp8_swiglu.rs:14
+
+
+def mlp_input(rows: int, columns: int, pattern=FP8_INPUT_PATTERN) -> np.ndarray:
+    """make_input of qual/src/fp8_swiglu.rs:165-173 / fp8_down.rs:169-176 / gdn_output.rs:141-148:
+    BF16 bits [rows, columns], pattern by flat index, factor by token & 7."""
+    idx = np.arange(rows * columns)
+    vals = pattern[idx & (len(pattern) - 1)] * MLP_TOKEN_FACTORS[(idx // columns) & 7]
+    return O.f32_to_bf16(vals).reshape(rows, columns)
+
+
+def fp8_swiglu_weights(intermediate: int, hidden: int, device):
+    """make_weights of qual/src/fp8_swiglu.rs:175-191: one code per source row,
+    WEIGHT_CODES[(row + (row >= I)) & 3]; BF16 scales SCALE_VALUES[row & 3].  Torch tensors."""
+    import torch
+
+    rows = torch.arange(2 * intermediate, device=device)
+    sel = (rows + (rows >= intermediate).long()) & 3
+    codes = torch.from_numpy(WEIGHT_CODES).to(device)[sel][:, None].expand(-1, hidden).contiguous()
+    scales = torch.from_numpy(O.f32_to_bf16(SCALE_VALUES).view(np.int16)).to(device)[rows & 3].contiguous()
+    return codes, scales
+
+
+def fp8_swiglu_expected(represented_sum: float, scale: np.float32, intermediate: int) -> np.ndarray:
+    """Closed form of qual/src/fp8_swiglu.rs:268-281, f64 [intermediate]."""
+    row = np.arange(intermediate)
+    up_src = row + intermediate
+    base = represented_sum * np.float64(scale)
+    gate = base * WEIGHT_VALUES[row & 3].astype(np.float64) * SCALE_VALUES[row & 3].astype(np.float64)
+    up = base * WEIGHT_VALUES[(up_src + 1) & 3].astype(np.float64) * SCALE_VALUES[up_src & 3].astype(np.float64)
+    return gate / (1.0 + np.exp(-gate)) * up
+
+
+def fp8_down_weights(hidden: int, intermediate: int, device):
+    """make_weights of qual/src/fp8_down.rs:178-194: WEIGHT_CODES[(row + column) & 3]."""
+    import torch
+
+    r = torch.arange(hidden, device=device)[:, None]
+    c = torch.arange(intermediate, device=device)[None, :]
+    codes = torch.from_numpy(WEIGHT_CODES).to(device)[(r + c) & 3].contiguous()
+    scales = torch.from_numpy(O.f32_to_bf16(SCALE_VALUES).view(np.int16)).to(device)[r[:, 0] & 3].contiguous()
+    return codes, scales
+
+
+def gdn_output_weights(hidden: int, columns: int, device):
+    """make_weights of qual/src/gdn_output.rs:150-166: WEIGHT_CODES[row & 3] along the whole row."""
+    import torch
+
+    r = torch.arange(hidden, device=device)
+    codes = torch.from_numpy(WEIGHT_CODES).to(device)[r & 3][:, None].expand(-1, columns).contiguous()
+    scales = torch.from_numpy(O.f32_to_bf16(SCALE_VALUES).view(np.int16)).to(device)[r & 3].contiguous()
+    return codes, scales

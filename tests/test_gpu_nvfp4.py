@@ -526,6 +526,64 @@ def test_reduction_routes_of_the_mlp_agree_bit_for_bit(tk, oracle, rows, monkeyp
     assert max_relative_error(got["2"][0][:, :128], exp, 4 * float(np.abs(exp).mean())) <= 1e-2
 
 
+@pytest.mark.parametrize("rows", [256, 300, 700, 1030])
+def test_persistent_pair_route_matches_plain_route_and_oracle(tk, oracle, rows, monkeypatch):
+    """Prefill token counts run on persistent CTA pairs (256-row x 256-token pair tiles, each pair
+    walking several tiles, gate/up halves exchanged through the partner's shared memory).  On a
+    small geometry with ragged token counts: every output within tolerance of the W4A4 oracle,
+    inactive rows untouched, and the same bits as the one-CTA kernels (TK100_PERSIST=0) -- both
+    add the K blocks in order into one fp32 accumulator."""
+    from tuiskollm_b200 import synth
+
+    hidden, inter = 1024, 1536
+    xb = synth.normal_bf16(18, rows, (rows, hidden))
+    gu_codes, gu_scales, gu_div = synth.nvfp4_weights(18, 1, 2 * inter, hidden)
+    dn_codes, dn_scales, dn_div = synth.nvfp4_weights(18, 2, hidden, inter)
+    a_div, m_div = float(np.float32(448.0 * 6.0 / 5.0)), float(np.float32(448.0 * 6.0 / 8.0))
+    got = {}
+    for route, env in (("persistent", "1"), ("plain", "0")):
+        monkeypatch.setenv("TK100_PERSIST", env)
+        monkeypatch.setenv("TK100_PERSIST_MIN_ROWS", "256")
+        c = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=2048)
+        a_codes, a_scales = act_planes(tk, rows + 1, hidden)
+        m_codes, m_scales = act_planes(tk, rows + 1, inter)
+        mid = sentinel_plane((rows + 1, inter), torch.int16)
+        out = sentinel_plane((rows + 1, hidden), torch.int16)
+        part = sentinel_plane((rows + 1, hidden), torch.float32)
+        tk.Nvfp4SwiGluOp(c).launch_quantize(None, rows, dev(xb.view(np.int16)), dev(gu_codes), dev(gu_scales),
+                                            float(gu_div), mid, activation_codes=a_codes,
+                                            activation_scales=a_scales, input_global_divisor=a_div,
+                                            output_global_divisor=m_div, output_codes=m_codes,
+                                            output_scales=m_scales)
+        r_gu = c.last_kernel
+        tk.Nvfp4DownOp(c).launch(None, rows, None, dev(dn_codes), dev(dn_scales), float(dn_div), out,
+                                 activation_codes=m_codes, activation_scales=m_scales,
+                                 input_global_divisor=m_div)
+        r_dn = c.last_kernel
+        tk.Nvfp4DownOp(c).launch_partial(None, rows, None, dev(dn_codes), dev(dn_scales), float(dn_div),
+                                         part, activation_codes=m_codes, activation_scales=m_scales,
+                                         input_global_divisor=m_div)
+        torch.cuda.synchronize()
+        assert c.device_status() == 0, route
+        assert r_gu.startswith("nvfp4_persist_kernel") == (route == "persistent"), (route, r_gu)
+        assert r_dn.startswith("nvfp4_persist_kernel") == (route == "persistent"), (route, r_dn)
+        for pl in (mid, out, part):
+            assert_inactive_untouched(pl, rows)
+        got[route] = (_u16(mid)[:rows].copy(), _u16(out)[:rows].copy(), host(part)[:rows].copy())
+    oc, osc = oracle.nvfp4_quantize(xb, a_div)
+    dots = oracle.nvfp4_w4a4_dot(oc, osc, a_div, gu_codes, gu_scales, float(gu_div))
+    exp_mid = oracle.silu_mul(dots[:, :inter], dots[:, inter:])
+    assert max_relative_error(got["persistent"][0], exp_mid, 4 * float(np.abs(exp_mid).mean())) <= 1e-2
+    mc, msc = oracle.nvfp4_quantize(got["persistent"][0], m_div)
+    exp_out = oracle.nvfp4_w4a4_dot(mc, msc, m_div, dn_codes, dn_scales, float(dn_div))
+    floor = 4 * float(np.abs(exp_out).mean())
+    assert max_relative_error(got["persistent"][1], exp_out, floor) <= 1e-2
+    assert (np.abs(got["persistent"][2] - exp_out) / np.maximum(np.abs(exp_out), floor)).max() <= 2e-3
+    assert np.array_equal(oracle.f32_to_bf16(got["persistent"][2]), got["persistent"][1])
+    for a, b in zip(got["persistent"], got["plain"]):
+        assert np.array_equal(a, b)
+
+
 def test_full_size_prefill_down_sampled_tiles(tk, ctx, oracle):
     """Configuration 4's down projection at full size (M = 2048, 5120 x 17408: unsplit 128-token
     tiles over 68 k-blocks): first, last and two inner weight tiles x first and last token tile

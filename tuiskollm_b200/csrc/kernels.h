@@ -95,6 +95,21 @@ cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, cons
                                  float nvfp4_divisor = 0.0f);
 
 // ------------------------------------------------------------------ fp8_proj.cu
+// ------------------------------------------------------------------- fp8_mlp.cu
+struct Fp8SwigluParams {
+  int rows;          // active tokens M
+  int intermediate;  // outputs per token I; the weight plane holds gate rows [0, I) then up rows [I, 2I)
+  int k;             // reduction length, multiple of 128
+  const float* act_scales;   // [rows]
+  const uint16_t* w_scales;  // [2 * I] BF16
+  uint16_t* out;             // [rows, I] BF16
+  uint32_t* status;
+};
+cudaError_t fp8_swiglu_prepare();
+// block_tok 32 or 128.
+cudaError_t launch_fp8_swiglu(cudaStream_t stream, int block_tok, const CUtensorMap& tmap_w,
+                              const CUtensorMap& tmap_a, const Fp8SwigluParams& p);
+
 struct ArgmaxPair {
   float value;
   int32_t index;
@@ -236,6 +251,12 @@ cudaError_t nvfp4_pair_prepare();
 cudaError_t launch_nvfp4_pair(cudaStream_t stream, bool gate_up, const CUtensorMap& tmap_w,
                               const CUtensorMap& tmap_a, const CUtensorMap& tmap_wsf,
                               const CUtensorMap& tmap_asf, const Nvfp4Params& p);
+// nvfp4_persist.cu: prefill route on persistent CTA pairs (256-row x 256-token pair tiles, one
+// pair per two SMs walking its share of the tiles).  `max_pairs`: pairs resident at once.
+cudaError_t nvfp4_persist_prepare(int* max_pairs);
+cudaError_t launch_nvfp4_persist(cudaStream_t stream, bool gate_up, int pairs, const CUtensorMap& tmap_w,
+                                 const CUtensorMap& tmap_a, const CUtensorMap& tmap_wsf,
+                                 const CUtensorMap& tmap_asf, const Nvfp4Params& p);
 cudaError_t launch_f32_to_bf16(cudaStream_t stream, long long n, const float* in, uint16_t* out);
 cudaError_t launch_nvfp4_quantize(cudaStream_t stream, int rows, int k, const uint16_t* x,
                                   float divisor, uint8_t* codes, uint8_t* scales);

@@ -40,6 +40,8 @@ Tuning Tuning::from_environment() {
   t.nvfp4_pair = env_int("TK100_PAIR", t.nvfp4_pair);
   t.nvfp4_pair_min_rows = env_int("TK100_PAIR_MIN_ROWS", t.nvfp4_pair_min_rows);
   t.swiglu_pairs = env_int("TK100_SWIGLU_PAIRS", t.swiglu_pairs);
+  t.nvfp4_persist = env_int("TK100_PERSIST", t.nvfp4_persist);
+  t.nvfp4_persist_min_rows = env_int("TK100_PERSIST_MIN_ROWS", t.nvfp4_persist_min_rows);
   t.fused_exchange = env_int("TK100_FUSED_TAIL", t.fused_exchange);
   t.fused_quant = env_int("TK100_FUSED_QUANT", t.fused_quant);
   return t;
@@ -121,6 +123,11 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
     delete ctx;
     return TK100_ERR_MODULE;
   }
+  if ((e = fp8_swiglu_prepare()) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the FP8 SwiGLU routes: ") + cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
   if ((e = fp8_pair_prepare()) != cudaSuccess) {
     *error = std::string("[gpu.module] preparing the FP8 pair route: ") + cudaGetErrorString(e);
     delete ctx;
@@ -128,6 +135,11 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
   }
   if ((e = nvfp4_pair_prepare()) != cudaSuccess) {
     *error = std::string("[gpu.module] preparing the NVFP4 pair routes: ") + cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
+  if ((e = nvfp4_persist_prepare(&ctx->persist_pairs_)) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the persistent NVFP4 routes: ") + cudaGetErrorString(e);
     delete ctx;
     return TK100_ERR_MODULE;
   }
@@ -580,6 +592,48 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
   return TK100_OK;
 }
 
+// ----------------------------------------------------------------- Fp8SwiGluOp
+
+Status Fp8SwiGluOp::launch(cudaStream_t stream, int rows, const uint16_t* input,
+                           uint8_t* activation_codes, float* activation_scales,
+                           const uint8_t* weight_codes, const uint16_t* weight_scales,
+                           uint16_t* output) {
+  const char* name = "FP8 SwiGLU";
+  TK100_TRY(check_rows(ctx_, name, rows));
+  const int hidden = static_cast<int>(ctx_.config().hidden);
+  const int inter = static_cast<int>(ctx_.config().intermediate);
+  if (inter < 128 || inter % 128 != 0) {
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + name + ": intermediate size " +
+                                           std::to_string(inter) + " is not admitted (multiple of 128)");
+  }
+  TK100_TRY(check_plane(ctx_, name, "activation codes", activation_codes, 128));
+  TK100_TRY(check_plane(ctx_, name, "activation scales", activation_scales, 4));
+  TK100_TRY(check_plane(ctx_, name, "weight codes", weight_codes, 128));
+  TK100_TRY(check_plane(ctx_, name, "weight scales", weight_scales, 2));
+  TK100_TRY(check_plane(ctx_, name, "output", output, 2));
+  if (input) {
+    TK100_TRY(Fp8ProjectionOp(ctx_, name).quantize(stream, rows, hidden, input, activation_codes,
+                                                   activation_scales));
+  }
+  const int block_tok = rows <= 32 ? 32 : 128;
+  CUtensorMap map_w, map_a;
+  TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(2) * inter, static_cast<uint64_t>(hidden),
+                            128, &map_w));
+  TK100_TRY(ctx_.tensor_map(activation_codes, static_cast<uint64_t>(rows), static_cast<uint64_t>(hidden),
+                            static_cast<uint32_t>(block_tok), &map_a));
+  Fp8SwigluParams p{};
+  p.rows = rows;
+  p.intermediate = inter;
+  p.k = hidden;
+  p.act_scales = activation_scales;
+  p.w_scales = weight_scales;
+  p.out = output;
+  p.status = ctx_.status_word();
+  ctx_.count_launch();
+  ctx_.note_route("fp8_swiglu_kernel", block_tok, 0, 1, 0);
+  return ctx_.check(launch_fp8_swiglu(stream, block_tok, map_w, map_a, p), "launching the FP8 SwiGLU");
+}
+
 // ------------------------------------------------------------------ Nvfp4MlpOp
 
 Status Nvfp4MlpOp::quantize(cudaStream_t stream, int rows, int columns, const uint16_t* input,
@@ -705,6 +759,40 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
                            "launching the NVFP4 pair projection"));
       return quantise_after();
     }
+  }
+  // Prefill shapes: persistent CTA pairs on 256-row x 256-token pair tiles (halves the operand
+  // bytes per MAC through the SM's L2 port and the scale copies per MAC; the epilogue of one tile
+  // runs under the next tile's MMAs).
+  if (ctx_.tuning().nvfp4_persist != 0 && rows >= ctx_.tuning().nvfp4_persist_min_rows &&
+      ctx_.persist_pairs() > 0 && (gate_up || out_rows % 256 == 0)) {
+    const uint64_t w_rows = static_cast<uint64_t>(out_rows) * (gate_up ? 2 : 1);
+    const uint64_t chunks_per_tile = static_cast<uint64_t>(columns / 64);
+    CUtensorMap map_w, map_a, map_wsf, map_asf;
+    TK100_TRY(ctx_.tensor_map(weight_codes, w_rows, static_cast<uint64_t>(columns / 2), 128, &map_w));
+    TK100_TRY(ctx_.tensor_map(activation_codes, static_cast<uint64_t>(rows),
+                              static_cast<uint64_t>(columns / 2), 128, &map_a));
+    TK100_TRY(ctx_.scale_map(weight_scales, (w_rows / 128) * chunks_per_tile, &map_wsf));
+    TK100_TRY(ctx_.scale_map(activation_scales,
+                             static_cast<uint64_t>((rows + 127) / 128) * chunks_per_tile, &map_asf));
+    Nvfp4Params q{};
+    q.rows = rows;
+    q.out_rows = out_rows;
+    q.k = columns;
+    q.splits = 1;
+    q.up_row_offset = gate_up ? out_rows : 0;
+    q.out_scale = 1.0f / (weight_scale_divisor * input_global_divisor);
+    q.out = output;
+    q.out_f32 = output_f32;
+    q.status = ctx_.status_word();
+    q.debug = debug_flags();
+    q.stamps = debug_stamps();
+    const long long tiles = static_cast<long long>((rows + 255) / 256) * (gate_up ? out_rows / 128 : out_rows / 256);
+    const int pairs = static_cast<int>(tiles < ctx_.persist_pairs() ? tiles : ctx_.persist_pairs());
+    ctx_.count_launch();
+    ctx_.note_route("nvfp4_persist_kernel", gate_up ? 1 : 0, pairs, 1, 1);
+    TK100_TRY(ctx_.check(launch_nvfp4_persist(stream, gate_up, pairs, map_w, map_a, map_wsf, map_asf, q),
+                         "launching the persistent NVFP4 projection"));
+    return quantise_after();
   }
   const int block_tok = rows <= 32 ? 32 : 128;
   const int tiles_n = out_rows / 128;
@@ -945,6 +1033,38 @@ tk100_status tk100_fp8_projection(tk100_ctx* ctx, tk100_stream stream, int rows,
   return tk100::Fp8ProjectionOp(*ctx->impl, "FP8 projection")
       .launch(static_cast<cudaStream_t>(stream), rows, out_rows, columns, input,
               activation_codes, activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_fp8_swiglu(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
+                              uint8_t* activation_codes, float* activation_scales,
+                              const uint8_t* weight_codes, const uint16_t* weight_scales,
+                              uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::Fp8SwiGluOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, input, activation_codes, activation_scales,
+              weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_fp8_down(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
+                            uint8_t* activation_codes, float* activation_scales,
+                            const uint8_t* weight_codes, const uint16_t* weight_scales,
+                            uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  const tk100_config& c = ctx->impl->config();
+  return tk100::Fp8DownOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, static_cast<int>(c.hidden),
+              static_cast<int>(c.intermediate), input, activation_codes, activation_scales,
+              weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream, int rows, int columns,
+                                  const uint16_t* input, uint8_t* activation_codes,
+                                  float* activation_scales, const uint8_t* weight_codes,
+                                  const uint16_t* weight_scales, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::GdnOutputProjectionOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, static_cast<int>(ctx->impl->config().hidden),
+              columns, input, activation_codes, activation_scales, weight_codes, weight_scales, output);
 }
 
 tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,

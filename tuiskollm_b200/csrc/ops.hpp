@@ -38,6 +38,8 @@ struct Tuning {
   int fp8_pair_min_rows = 256;
   int nvfp4_pair = 0;         // TK100_PAIR: 1 down, 2 gate_up too (cta_group::2 variant)
   int nvfp4_pair_min_rows = 1024;
+  int nvfp4_persist = 0;      // TK100_PERSIST=1: persistent CTA-pair route for NVFP4 prefill shapes
+  int nvfp4_persist_min_rows = 512;  // TK100_PERSIST_MIN_ROWS
   int swiglu_pairs = 1;       // TK100_SWIGLU_PAIRS=0: one CTA holds the gate and the up tile
   int fused_exchange = 1;     // TK100_FUSED_TAIL=0: argmax finalize / exchange as launches of their own
   int fused_quant = 0;        // TK100_FUSED_QUANT=1: launches of one wave and at most 4 rows quantise
@@ -68,6 +70,7 @@ class Context {
 
   const tk100_config& config() const { return config_; }
   int sm_count() const { return sm_count_; }
+  int persist_pairs() const { return persist_pairs_; }
   float* partials() const { return partials_; }
   size_t partial_bytes() const { return partial_bytes_; }
   unsigned int* counters() const { return counters_; }
@@ -92,6 +95,7 @@ class Context {
   Context() = default;
   tk100_config config_{};
   int sm_count_ = 0;
+  int persist_pairs_ = 0;  // CTA pairs of the persistent NVFP4 kernel that fit the device at once
   float* partials_ = nullptr;
   size_t partial_bytes_ = 0;
   unsigned int* counters_ = nullptr;
@@ -178,6 +182,18 @@ class Fp8ProjectionOp {
   const char* name_;
 };
 
+// tuisko-kernels-sm120/src/fp8/swiglu.rs:366-376: dense-FP8 gate/up projection + SwiGLU.
+class Fp8SwiGluOp {
+ public:
+  explicit Fp8SwiGluOp(Context& ctx) : ctx_(ctx) {}
+  Status launch(cudaStream_t stream, int rows, const uint16_t* input, uint8_t* activation_codes,
+                float* activation_scales, const uint8_t* weight_codes, const uint16_t* weight_scales,
+                uint16_t* output);
+
+ private:
+  Context& ctx_;
+};
+
 struct FullAttentionQkvOp : Fp8ProjectionOp {
   explicit FullAttentionQkvOp(Context& c) : Fp8ProjectionOp(c, "FP8 QKV") {}
 };
@@ -186,6 +202,14 @@ struct GdnInputProjectionOp : Fp8ProjectionOp {
 };
 struct LmHeadOp : Fp8ProjectionOp {
   explicit LmHeadOp(Context& c) : Fp8ProjectionOp(c, "FP8 LM head") {}
+};
+// tuisko-kernels-sm120/src/fp8/down.rs:197-207 (K = intermediate) and fp8/gdn_output.rs:178
+// (K = the GDN value width): the same projection at other reduction lengths.
+struct Fp8DownOp : Fp8ProjectionOp {
+  explicit Fp8DownOp(Context& c) : Fp8ProjectionOp(c, "FP8 down") {}
+};
+struct GdnOutputProjectionOp : Fp8ProjectionOp {
+  explicit GdnOutputProjectionOp(Context& c) : Fp8ProjectionOp(c, "FP8 GDN output") {}
 };
 
 // tuisko-kernels-sm89/src/nvfp4/swiglu.rs:470-571 and nvfp4/down.rs:455-556, with the

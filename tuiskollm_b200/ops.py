@@ -177,6 +177,45 @@ class GdnInputProjectionOp(FullAttentionQkvOp):
     _entry = "tk100_fp8_gdn_input"
 
 
+class Fp8SwiGluOp:
+    """tuisko-kernels-sm120/src/fp8/swiglu.rs:366-376: dense-FP8 gate/up projection + SwiGLU;
+    weights ``[2 * intermediate, hidden]`` with the gate rows first."""
+
+    _entry = "tk100_fp8_swiglu"
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def launch(self, stream, rows, input, activation_codes, activation_scales, weight_codes,
+               weight_scales, output):
+        c = self.ctx
+        fn = getattr(c._lib, self._entry)
+        c.check(fn(c.handle, _stream(stream), rows, _ptr(input), _ptr(activation_codes),
+                   _ptr(activation_scales), _ptr(weight_codes), _ptr(weight_scales), _ptr(output)))
+
+
+class Fp8DownOp(Fp8SwiGluOp):
+    """tuisko-kernels-sm120/src/fp8/down.rs:197-207: planes ``[rows, intermediate]`` in,
+    ``[rows, hidden]`` out."""
+
+    _entry = "tk100_fp8_down"
+
+
+class GdnOutputProjectionOp:
+    """tuisko-kernels-sm120/src/fp8/gdn_output.rs:178; ``columns`` = the GDN value width."""
+
+    def __init__(self, context: Context, columns: int):
+        self.ctx = context
+        self.columns = columns
+
+    def launch(self, stream, rows, input, activation_codes, activation_scales, weight_codes,
+               weight_scales, output):
+        c = self.ctx
+        c.check(c._lib.tk100_fp8_gdn_output(c.handle, _stream(stream), rows, self.columns, _ptr(input),
+                                            _ptr(activation_codes), _ptr(activation_scales),
+                                            _ptr(weight_codes), _ptr(weight_scales), _ptr(output)))
+
+
 class LmHeadOp:
     """tuisko-kernels-sm120/src/fp8/projection.rs:704-793 plus the fused greedy argmax.
 
