@@ -53,11 +53,17 @@ __global__ void __launch_bounds__(1024)
   const size_t row_off = static_cast<size_t>(row) * hidden;
 
   float v[CHUNKS][8];
+  // The norm weight of this thread's columns is requested together with the row (one memory
+  // latency less on the chain load -> reduce -> scale -> reduce -> store); with three or four
+  // chunks per thread the registers do not allow it and the weight is loaded where it is used.
+  constexpr bool EARLY_WEIGHT = DO_NORM && CHUNKS <= 2;
+  Chunk wreg[EARLY_WEIGHT ? CHUNKS : 1];
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < CHUNKS; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < chunks_per_row) {
+      if constexpr (EARLY_WEIGHT) wreg[i] = *reinterpret_cast<const Chunk*>(weight + c * 8);
       Chunk a = *reinterpret_cast<const Chunk*>(x + row_off + c * 8);
       if (HAS_BRANCH) {
         Chunk b = *reinterpret_cast<const Chunk*>(branch + row_off + c * 8);
@@ -95,7 +101,9 @@ __global__ void __launch_bounds__(1024)
     for (int i = 0; i < CHUNKS; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
       if (c < chunks_per_row) {
-        const Chunk wv = *reinterpret_cast<const Chunk*>(weight + c * 8);
+        Chunk wv;
+        if constexpr (EARLY_WEIGHT) wv = wreg[i];
+        else wv = *reinterpret_cast<const Chunk*>(weight + c * 8);
         Chunk o;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -250,6 +258,28 @@ cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, cons
   const Nvfp4Out nv{nvfp4_codes, nvfp4_scales, nvfp4_divisor};
   int threads = 0, chunks = 0;
   if (!norm_geometry(hidden, &threads, &chunks)) return cudaErrorInvalidValue;
+  // A row per CTA: with one 16-byte chunk per thread (640 threads for 5120 columns) three CTAs
+  // share an SM, so 256 or 512 rows run as one and a bit, or two, waves of CTAs that each sit
+  // through two block reductions.  More chunks per thread = smaller CTAs = more rows in flight per
+  // SM: take the fewest chunks that put all rows into one wave, the most when none does.
+  {
+    static int sms = 0;
+    if (sms == 0) {
+      int device = 0;
+      if (cudaGetDevice(&device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+        sms = 148;
+      }
+    }
+    const int row_chunks = hidden >> 3;
+    while (chunks * 2 <= kMaxChunks && rows > sms * (2048 / threads)) {
+      const int c = chunks * 2;
+      const int t = ((row_chunks + c - 1) / c + 31) & ~31;
+      if (t < 128) break;
+      chunks = c;
+      threads = t;
+    }
+  }
   const bool has_branch = branch != nullptr;
   const bool do_norm = normalized_out != nullptr;
   const bool do_quant = codes != nullptr;
