@@ -633,6 +633,55 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
             keep.append(graph)
         keep.append((gu_planes, dn_planes, go_planes, x, xi, xg, c1, c2, c3, s1, s2, s3, mid, out, out_g))
 
+    # ---- the steps either side of the GDN projections: control mat-vecs + convolution, and the
+    # FP32 state recurrence, at decode batches 1 and 8.  State slots rotate so that the 6.29 MB of
+    # state per token come from HBM, not from L2.
+    qkv_rows, in_rows, slots = 10240, 16384, 48
+    prep_op, rec_op = tk.GdnPrepareOp(ctx), tk.GdnRecurrenceOp(ctx)
+    g_x = synth.torch_normal_bf16(SEED, 400, (8, HIDDEN), dev)
+    g_cw = synth.torch_normal_bf16(SEED, 401, (96, HIDDEN), dev, std=0.02)
+    g_alog = synth.torch_normal_bf16(SEED, 402, (48,), dev)
+    g_dt = synth.torch_normal_bf16(SEED, 403, (48,), dev)
+    g_proj = synth.torch_normal_bf16(SEED, 404, (8, in_rows), dev)
+    g_convw = synth.torch_normal_bf16(SEED, 405, (qkv_rows, 4), dev, std=0.5)
+    g_hist = synth.torch_normal_bf16(SEED, 406, (slots, qkv_rows, 3), dev)
+    g_state = torch.zeros((slots, 48, 128, 128), dtype=torch.float32, device=dev)
+    g_state.normal_(0.0, 0.05, generator=torch.Generator(device=dev).manual_seed(SEED + 407))
+    g_norm = synth.torch_normal_bf16(SEED, 408, (128,), dev)
+    g_decay = torch.empty((8, 48), dtype=torch.float32, device=dev)
+    g_beta = torch.empty((8, 48), dtype=torch.float32, device=dev)
+    g_conv = torch.empty((8, qkv_rows), dtype=torch.bfloat16, device=dev)
+    g_out = torch.empty((8, 6144), dtype=torch.bfloat16, device=dev)
+    for b in (1, 8):
+        groups = slots // b
+        rows = [torch.arange(g * b, (g + 1) * b, dtype=torch.int32, device=dev) for g in range(groups)]
+        st = {"p": 0, "r": 0}
+
+        def prep(b=b, rows=rows, st=st, groups=groups):
+            prep_op.launch(None, b, g_x, g_cw, g_alog, g_dt, g_proj, g_convw, rows[st["p"] % groups],
+                           g_hist, g_decay, g_beta, g_conv)
+            st["p"] += 1
+
+        def rec(b=b, rows=rows, st=st, groups=groups):
+            rec_op.launch(None, b, g_conv, g_proj, g_decay, g_beta, g_norm, rows[st["r"] % groups],
+                          g_state, g_out)
+            st["r"] += 1
+
+        prep()
+        rec()
+        for nm, fn, by in (
+                ("gdn_prepare", prep, 2 * 96 * HIDDEN + b * (2 * HIDDEN + qkv_rows * (2 + 6 + 6 + 2) + 2 * 48 * 4)
+                 + 8 * qkv_rows),
+                ("gdn_recurrence", rec, b * (2 * 48 * 128 * 128 * 4 + 2 * (qkv_rows + 2 * 6144) + 2 * 48 * 4))):
+            graph = capture(torch, fn, groups)
+            case = f"{nm}:B{b}"
+            proto.add(case, graph.replay, groups)
+            meta[case] = {"config": "next", "op": nm, "M": b, "kernel": nm + "_kernel", "kind": "hbm",
+                          "bytes": by, "cpu": None}
+            keep.append(graph)
+    keep.append((g_x, g_cw, g_alog, g_dt, g_proj, g_convw, g_hist, g_state, g_norm, g_decay, g_beta,
+                 g_conv, g_out))
+
     # ---- fused residual + RMSNorm + quantise (configurations 1 and 5, and the metric's M = 512)
     normop = tk.ResidualNormOp(ctx)
     nw = synth.torch_normal_bf16(SEED, 5, (HIDDEN,), dev, std=0.1)

@@ -39,6 +39,24 @@ pub struct Tk100ArgmaxPair {
     pub index: i32,
 }
 
+/// `tk100_sampling_options`: one request's controls and stop-token pair.
+#[repr(C)]
+#[derive(Clone, Copy, Debug, PartialEq)]
+pub struct Tk100SamplingOptions {
+    pub temperature: f32,
+    pub top_p: f32,
+    pub top_k: u32,
+    pub stop_ids: [u32; 2],
+}
+
+/// `tk100_sample_decision`.
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default, Eq, PartialEq)]
+pub struct Tk100SampleDecision {
+    pub token_id: u32,
+    pub stopped: u32,
+}
+
 #[repr(C)]
 pub struct Tk100Ctx {
     _opaque: [u8; 0],
@@ -106,6 +124,24 @@ unsafe extern "C" {
         ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, columns: c_int, input: *const u16,
         activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
         weight_scales: *const u16, output: *mut u16,
+    ) -> Tk100Status;
+    pub fn tk100_sample(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, vocab: c_int, logits: *const u16,
+        options: *const Tk100SamplingOptions, rng_state: *mut u64, scratch: *mut u64,
+        decisions: *mut Tk100SampleDecision, top_out: *mut u32,
+    ) -> Tk100Status;
+    pub fn tk100_sampler_initial_state(seed: u64) -> u64;
+    pub fn tk100_sampler_scratch_bytes(rows: c_int, vocab: c_int) -> usize;
+    pub fn tk100_gdn_prepare(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, batch: c_int, input: *const u16,
+        control_weights: *const u16, a_log: *const u16, dt_bias: *const u16,
+        projected: *const u16, convolution_weights: *const u16, state_rows: *const u32,
+        history: *mut u16, log_decay: *mut f32, beta: *mut f32, convolved: *mut u16,
+    ) -> Tk100Status;
+    pub fn tk100_gdn_recurrence(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, batch: c_int, qkv: *const u16,
+        projected: *const u16, log_decay: *const f32, beta: *const f32, norm_weight: *const u16,
+        state_rows: *const u32, state: *mut f32, output: *mut u16,
     ) -> Tk100Status;
     pub fn tk100_fp8_lm_head(
         ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, vocab_rows: c_int, vocab_offset: c_int,

@@ -13,10 +13,12 @@ const SOURCES: &[&str] = &[
     "fp8_proj.cu",
     "fp8_pair.cu",
     "fp8_mlp.cu",
+    "gdn.cu",
     "nvfp4.cu",
     "nvfp4_pair.cu",
     "nvfp4_persist.cu",
     "peer_reduce.cu",
+    "sampler.cu",
     "ops.cu",
     "static_entry.cu",
 ];

@@ -252,6 +252,105 @@ impl<A: Sm100Arch> GdnOutputProjectionOp<A> {
     }
 }
 
+/// Device counterpart of the engine's host `Sampler` (`tuisko-engine/src/sampling.rs:56-101`)
+/// for a decode batch: the BF16 logit rows stay in device memory, one launch selects every
+/// request's token.  The caller owns the generator states (`[rows]` u64, started from
+/// [`DeviceSamplerOp::initial_state`]), the scratch ([`DeviceSamplerOp::scratch_bytes`], zeroed
+/// once) and the decision plane.
+pub struct DeviceSamplerOp {
+    ctx: Arc<Sm100Context>,
+}
+
+impl DeviceSamplerOp {
+    pub fn new(ctx: &Arc<Sm100Context>) -> GpuResult<Self> {
+        Ok(Self { ctx: Arc::clone(ctx) })
+    }
+
+    /// `XorShift64::new` (`sampling.rs:247-250`).
+    pub fn initial_state(seed: u64) -> u64 {
+        unsafe { ffi::tk100_sampler_initial_state(seed) }
+    }
+
+    pub fn scratch_bytes(rows: usize, vocab: usize) -> usize {
+        unsafe { ffi::tk100_sampler_scratch_bytes(rows_i32(rows), vocab as i32) }
+    }
+
+    /// `options` holds one entry per request and is validated with the reference's rules
+    /// before the launch; `top_out` may be null.
+    #[allow(clippy::too_many_arguments)]
+    pub unsafe fn launch(
+        &self, stream: &CudaStream, vocab: usize, logits: *const u16,
+        options: &[ffi::Tk100SamplingOptions], rng_state: *mut u64, scratch: *mut u64,
+        decisions: *mut ffi::Tk100SampleDecision, top_out: *mut u32,
+    ) -> GpuResult<()> {
+        self.ctx.check(unsafe {
+            ffi::tk100_sample(
+                self.ctx.raw, stream.cu_stream().cast(), rows_i32(options.len()), vocab as i32,
+                logits, options.as_ptr(), rng_state, scratch, decisions, top_out,
+            )
+        })
+    }
+}
+
+/// `GdnPrepareOp` (`tuisko-kernels-sm120/src/gdn/prepare.rs:176-290`): control mat-vecs and the
+/// width-4 causal convolution of a decode batch of 1..=8 tokens, one launch.
+pub struct GdnPrepareOp<A: Sm100Arch = Qwen38_27B> {
+    ctx: Arc<Sm100Context>,
+    _arch: PhantomData<A>,
+}
+
+impl<A: Sm100Arch> GdnPrepareOp<A> {
+    /// Replaces the module load and the eight prepared routes of the sm_120 operator.
+    pub fn new(ctx: &Arc<Sm100Context>) -> GpuResult<Self> {
+        Ok(Self { ctx: Arc::clone(ctx), _arch: PhantomData })
+    }
+
+    /// Same argument order and safety contract as the sm_120 `launch`.
+    #[allow(clippy::too_many_arguments)]
+    pub unsafe fn launch(
+        &self, stream: &CudaStream, batch: usize, input: *const u16, control_weights: *const u16,
+        a_log: *const u16, dt_bias: *const u16, projected: *const u16,
+        convolution_weights: *const u16, state_rows: *const u32, history: *mut u16,
+        log_decay: *mut f32, beta: *mut f32, convolved: *mut u16,
+    ) -> GpuResult<()> {
+        self.ctx.check(unsafe {
+            ffi::tk100_gdn_prepare(
+                self.ctx.raw, stream.cu_stream().cast(), rows_i32(batch), input, control_weights,
+                a_log, dt_bias, projected, convolution_weights, state_rows, history, log_decay,
+                beta, convolved,
+            )
+        })
+    }
+}
+
+/// `GdnRecurrenceOp` (`tuisko-kernels-sm120/src/gdn/recurrence.rs:137-236`).
+pub struct GdnRecurrenceOp<A: Sm100Arch = Qwen38_27B> {
+    ctx: Arc<Sm100Context>,
+    _arch: PhantomData<A>,
+}
+
+impl<A: Sm100Arch> GdnRecurrenceOp<A> {
+    /// Replaces the module load and the eight prepared routes of the sm_120 operator.
+    pub fn new(ctx: &Arc<Sm100Context>) -> GpuResult<Self> {
+        Ok(Self { ctx: Arc::clone(ctx), _arch: PhantomData })
+    }
+
+    /// Same argument order and safety contract as the sm_120 `launch`.
+    #[allow(clippy::too_many_arguments)]
+    pub unsafe fn launch(
+        &self, stream: &CudaStream, batch: usize, qkv: *const u16, projected: *const u16,
+        log_decay: *const f32, beta: *const f32, norm_weight: *const u16,
+        state_rows: *const u32, state: *mut f32, output: *mut u16,
+    ) -> GpuResult<()> {
+        self.ctx.check(unsafe {
+            ffi::tk100_gdn_recurrence(
+                self.ctx.raw, stream.cu_stream().cast(), rows_i32(batch), qkv, projected,
+                log_decay, beta, norm_weight, state_rows, state, output,
+            )
+        })
+    }
+}
+
 macro_rules! fp8_mlp_op {
     ($(#[$doc:meta])* $name:ident, $entry:ident) => {
         $(#[$doc])*

@@ -187,6 +187,68 @@ TK100_API tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream,
                                             float* activation_scales, const uint8_t* weight_codes,
                                             const uint16_t* weight_scales, uint16_t* output);
 
+/* Per-request sampling controls (tuisko-engine/src/sampling.rs:11-22 SamplingOptions, plus the
+ * request's two stop-token identifiers, :57-60). */
+typedef struct tk100_sampling_options {
+  float temperature;    /* 0 selects greedy decoding */
+  float top_p;          /* cumulative probability kept after top-k, 0..=1 */
+  uint32_t top_k;       /* 1..=32 on the device (the generation contract's default is 20) */
+  uint32_t stop_ids[2]; /* distinct, below `vocab` */
+} tk100_sampling_options;
+
+/* tuisko-engine/src/sampling.rs:47-53 SampleDecision. */
+typedef struct tk100_sample_decision {
+  uint32_t token_id;
+  uint32_t stopped; /* 1 when token_id is one of the request's stop identifiers */
+} tk100_sample_decision;
+
+/* Sampler::sample (tuisko-engine/src/sampling.rs:76-95) for `rows` (1..=8) requests at once, on
+ * the device: `logits` is BF16 [rows, vocab] in device memory (the LM head's output plane), so the
+ * row never travels to the host.  `options` is a HOST array of `rows` entries, validated with the
+ * reference's rules and messages (:110-148) before anything is launched; a top_k above 32 is
+ * refused (the host sampler remains for it).  `rng_state` [rows] holds each request's xorshift64
+ * state in device memory -- start it from tk100_sampler_initial_state(seed); it advances once per
+ * sampled (non-greedy) token, like the reference's.  `scratch` is
+ * tk100_sampler_scratch_bytes(rows, vocab) bytes of device memory, zero before the first call.
+ * `top_out`, when not NULL, receives the top_k survivors of each row as [rows, 32, 2] words
+ * (f32 value bits, token index) in the reference's order.  A non-finite logit sets
+ * TK100 status bit 1 (see tk100_device_status) where the reference returns an error. */
+TK100_API tk100_status tk100_sample(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab,
+                                    const uint16_t* logits, const tk100_sampling_options* options,
+                                    uint64_t* rng_state, uint64_t* scratch,
+                                    tk100_sample_decision* decisions, uint32_t* top_out);
+/* XorShift64::new (tuisko-engine/src/sampling.rs:247-250); host arithmetic only. */
+TK100_API uint64_t tk100_sampler_initial_state(uint64_t seed);
+TK100_API size_t tk100_sampler_scratch_bytes(int rows, int vocab);
+
+/* GdnPrepareOp::launch (tuisko-kernels-sm120/src/gdn/prepare.rs:226-290): for a decode batch of
+ * 1..=8 tokens, (a) the fused control mat-vecs -- rows [0,48) of `control_weights` give
+ * log_decay = -exp(a_log) * softplus(x.w + dt_bias), rows [48,96) give beta = sigmoid(x.w) --
+ * and (b) the width-4 causal convolution + SiLU over the first 10240 channels of `projected`
+ * ([batch,16384] BF16), which also shifts each token's 3-tap history
+ * (`history[state_rows[token], channel, 0..3]`, BF16) in place.  One launch where the reference
+ * has two.  Outputs: log_decay, beta FP32 [batch,48]; convolved BF16 [batch,10240].  State rows of
+ * one batch must be distinct.  Same argument order as the reference. */
+TK100_API tk100_status tk100_gdn_prepare(tk100_ctx* ctx, tk100_stream stream, int batch,
+                                         const uint16_t* input, const uint16_t* control_weights,
+                                         const uint16_t* a_log, const uint16_t* dt_bias,
+                                         const uint16_t* projected,
+                                         const uint16_t* convolution_weights,
+                                         const uint32_t* state_rows, uint16_t* history,
+                                         float* log_decay, float* beta, uint16_t* convolved);
+
+/* GdnRecurrenceOp::launch (tuisko-kernels-sm120/src/gdn/recurrence.rs:184-236): gated delta
+ * rule on the FP32 state `[state rows, 48, 128, 128]` (updated in place at
+ * `state_rows[token]`), then RMSNorm over each head's 128 outputs times `norm_weight`, times
+ * SiLU of the gate (`projected[token, 10240 + ...]`), BF16 `[batch, 6144]`.  qkv is the
+ * convolved plane `[batch,10240]`: 16 query heads, 16 key heads, 48 value heads of 128. */
+TK100_API tk100_status tk100_gdn_recurrence(tk100_ctx* ctx, tk100_stream stream, int batch,
+                                            const uint16_t* qkv, const uint16_t* projected,
+                                            const float* log_decay, const float* beta,
+                                            const uint16_t* norm_weight,
+                                            const uint32_t* state_rows, float* state,
+                                            uint16_t* output);
+
 /* LmHeadOp::launch (tuisko-kernels-sm120/src/fp8/projection.rs:751-793) with the greedy
  * selection of tuisko-engine/src/sampling.rs:162-173 folded into the same kernel.
  * vocab_rows / vocab_offset describe this rank's contiguous shard of the vocabulary

@@ -15,9 +15,11 @@
  * definition, written by symmetry with the pinned weight convention, and is
  * labelled "parity unpinned" wherever it is used.
  */
+#include <float.h>
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #ifdef _OPENMP
@@ -333,6 +335,108 @@ TKO_API long tko_greedy_index(const uint16_t* logits, size_t n) {
     }
   }
   return best;
+}
+
+/* tuisko-engine/src/sampling.rs:212-231 (top_k_select): `k` best (index, value) pairs, value
+ * descending under the IEEE total order, ties by ascending index -- a candidate displaces a
+ * retained one only when strictly greater.  Returns the count kept, or -1 - index of the first
+ * non-finite logit. */
+static int32_t tko_total_key(float v) {
+  int32_t key;
+  memcpy(&key, &v, 4);
+  key ^= (int32_t)(((uint32_t)(key >> 31)) >> 1);
+  return key;
+}
+
+TKO_API long tko_top_k_select(const uint16_t* logits, size_t n, size_t k, uint32_t* top_index,
+                              float* top_value) {
+  size_t kept = 0;
+  for (size_t token = 0; token < n; ++token) {
+    uint32_t bits = (uint32_t)logits[token] << 16;
+    if ((bits & 0x7f800000u) == 0x7f800000u) return -1 - (long)token;
+    float value;
+    memcpy(&value, &bits, 4);
+    int32_t key = tko_total_key(value);
+    if (kept == k && !(key > tko_total_key(top_value[kept - 1]))) continue;
+    /* partition point: first position whose retained value is below `value` */
+    size_t at = 0;
+    while (at < kept && tko_total_key(top_value[at]) >= key) ++at;
+    size_t last = kept < k ? kept : k - 1;
+    for (size_t i = last; i > at; --i) {
+      top_value[i] = top_value[i - 1];
+      top_index[i] = top_index[i - 1];
+    }
+    top_value[at] = value;
+    top_index[at] = (uint32_t)token;
+    if (kept < k) ++kept;
+  }
+  return (long)kept;
+}
+
+/* tuisko-engine/src/sampling.rs:244-260 (XorShift64). */
+TKO_API uint64_t tko_xorshift_new(uint64_t seed) {
+  const uint64_t scramble = 0x9e3779b97f4a7c15ull;
+  uint64_t state = seed ^ scramble;
+  return state == 0 ? scramble : state;
+}
+
+TKO_API double tko_xorshift_unit(uint64_t* state) {
+  uint64_t value = *state;
+  value ^= value << 13;
+  value ^= value >> 7;
+  value ^= value << 17;
+  *state = value;
+  return (double)(value >> 11) * (1.0 / 9007199254740992.0);
+}
+
+/* tuisko-engine/src/sampling.rs:76-95 and :175-210 (Sampler::sample): one token from a BF16
+ * logit row; the generator state advances only on the sampled route.  Returns the token, or
+ * -1 - index of a non-finite logit, or -(n + 2) when the distribution has no finite mass. */
+TKO_API long tko_sample(const uint16_t* logits, size_t n, float temperature, float top_p,
+                        size_t top_k, uint64_t* rng_state) {
+  if (temperature == 0.0f || top_k == 1) return tko_greedy_index(logits, n);
+  uint32_t* index = (uint32_t*)malloc(top_k * sizeof(uint32_t));
+  float* value = (float*)malloc(top_k * sizeof(float));
+  double* weight = (double*)malloc(top_k * sizeof(double));
+  long result;
+  long kept = tko_top_k_select(logits, n, top_k, index, value);
+  if (kept < 0) {
+    result = kept;
+  } else {
+    float maximum = value[0];
+    double total = 0.0;
+    for (long i = 0; i < kept; ++i) {
+      weight[i] = (double)expf((value[i] - maximum) / temperature);
+      total += weight[i];
+    }
+    float floor_p = top_p > FLT_MIN ? top_p : FLT_MIN;
+    double cutoff = (double)floor_p * total;
+    double retained_total = 0.0;
+    long retained = 0;
+    for (long i = 0; i < kept; ++i) {
+      retained_total += weight[i];
+      ++retained;
+      if (retained_total >= cutoff) break;
+    }
+    if (retained == 0 || !isfinite(retained_total) || retained_total <= 0.0) {
+      result = -((long)n + 2);
+    } else {
+      double threshold = tko_xorshift_unit(rng_state) * retained_total;
+      double cumulative = 0.0;
+      result = (long)index[retained - 1];
+      for (long i = 0; i < retained; ++i) {
+        cumulative += weight[i];
+        if (cumulative >= threshold) {
+          result = (long)index[i];
+          break;
+        }
+      }
+    }
+  }
+  free(index);
+  free(value);
+  free(weight);
+  return result;
 }
 
 /* ------------------------------------------------------------- NVFP4 */

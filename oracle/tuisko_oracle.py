@@ -76,6 +76,14 @@ def lib() -> C.CDLL:
         L.tko_nvfp4_quantize_rows.argtypes = [u16p, sz, sz, C.c_float, u8p, u8p]
         L.tko_nvfp4_w4a4_dot.restype = C.c_int
         L.tko_nvfp4_w4a4_dot.argtypes = [u8p, u8p, C.c_float, sz, sz, u8p, u8p, C.c_float, sz, f64p]
+        L.tko_top_k_select.restype = C.c_long
+        L.tko_top_k_select.argtypes = [u16p, sz, sz, C.POINTER(C.c_uint32), f32p]
+        L.tko_xorshift_new.restype = C.c_uint64
+        L.tko_xorshift_new.argtypes = [C.c_uint64]
+        L.tko_xorshift_unit.restype = C.c_double
+        L.tko_xorshift_unit.argtypes = [C.POINTER(C.c_uint64)]
+        L.tko_sample.restype = C.c_long
+        L.tko_sample.argtypes = [u16p, sz, C.c_float, C.c_float, sz, C.POINTER(C.c_uint64)]
         L.tko_num_threads.restype = C.c_int
         L.tko_set_num_threads.restype = None
         L.tko_set_num_threads.argtypes = [C.c_int]
@@ -217,6 +225,36 @@ def greedy_index(logits_bf16) -> int:
 
 
 # ------------------------------------------------------------------ NVFP4
+
+def top_k_select(logits_bf16, k: int):
+    """tuisko-engine/src/sampling.rs:212-231: (indices uint32, values float32) of the k best, or
+    raises on a non-finite logit."""
+    logits = _u16(logits_bf16)
+    index = np.zeros(k, dtype=np.uint32)
+    value = np.zeros(k, dtype=np.float32)
+    kept = lib().tko_top_k_select(_p(logits, C.c_uint16), logits.size, k,
+                                  _p(index, C.c_uint32), _p(value, C.c_float))
+    if kept < 0:
+        raise ValueError(f"sampling received a non-finite logit at token {-1 - kept}")
+    return index[:kept], value[:kept]
+
+
+class Sampler:
+    """tuisko-engine/src/sampling.rs:56-101: one request's sampler with its xorshift64 state."""
+
+    def __init__(self, temperature=1.0, top_p=0.95, top_k=20, seed=0, stop_ids=(0, 1)):
+        self.temperature, self.top_p, self.top_k = temperature, top_p, top_k
+        self.stop_ids = tuple(stop_ids)
+        self.state = C.c_uint64(lib().tko_xorshift_new(seed))
+
+    def sample(self, logits_bf16):
+        logits = _u16(logits_bf16)
+        token = lib().tko_sample(_p(logits, C.c_uint16), logits.size, self.temperature, self.top_p,
+                                 self.top_k, C.byref(self.state))
+        if token < 0:
+            raise ValueError(f"sampling failed ({token})")
+        return int(token), int(token) in self.stop_ids
+
 
 def nvfp4_a16_dot(x_bf16, w_codes, w_scales_swz, weight_scale_divisor: float) -> np.ndarray:
     x = _u16(x_bf16)

@@ -184,3 +184,70 @@ def gdn_output_weights(hidden: int, columns: int, device):
     codes = torch.from_numpy(WEIGHT_CODES).to(device)[r & 3][:, None].expand(-1, columns).contiguous()
     scales = torch.from_numpy(O.f32_to_bf16(SCALE_VALUES).view(np.int16)).to(device)[r & 3].contiguous()
     return codes, scales
+
+
+# ----------------------------------------------------------------- gated delta net
+# qual/src/gdn_prepare.rs:10-29 and qual/src/gdn_recurrence.rs:10-20
+GDN_MAX_BATCH = 8
+GDN_STATE_ROWS = np.array([7, 0, 5, 2, 6, 1, 4, 3], dtype=np.uint32)
+GDN_INPUT_PATTERN = np.array([0.25, -0.125, 0.0625, -0.03125, 0.1875, -0.09375, 0.046875, 0.0],
+                             dtype=np.float32)
+GDN_WEIGHT_PATTERN = np.array([0.00390625, -0.001953125, 0.0009765625, 0.001953125, -0.00390625,
+                               0.00048828125, 0.0014648438, -0.0009765625], dtype=np.float32)
+GDN_CONV_PATTERN = np.array([0.5, -0.25, 0.125, 0.25], dtype=np.float32)
+
+
+def gdn_prepare_fixture(hidden=5120, control_rows=48, qkv_rows=10240, input_rows=16384):
+    """qual/src/gdn_prepare.rs:187-230 (fixture): every plane for the maximum batch, BF16 bits."""
+    batch = GDN_MAX_BATCH
+    idx = np.arange(batch * hidden)
+    token = idx // hidden
+    inp = O.f32_to_bf16(GDN_INPUT_PATTERN[(idx + token) & 7]
+                        * (np.float32(1.0) + token.astype(np.float32) / np.float32(8.0)))
+    idx = np.arange(2 * control_rows * hidden)
+    row, column = idx // hidden, idx % hidden
+    control_weights = O.f32_to_bf16(GDN_WEIGHT_PATTERN[(column + 3 * row) & 7])
+    rows = np.arange(control_rows)
+    a_log = O.f32_to_bf16(np.float32(-2.0) + (rows & 3).astype(np.float32) * np.float32(0.125))
+    dt_bias = O.f32_to_bf16((rows.astype(np.float32) - np.float32(23.5)) / np.float32(256.0))
+    idx = np.arange(batch * input_rows)
+    token = idx // input_rows
+    projected = O.f32_to_bf16(GDN_INPUT_PATTERN[(3 * idx + token) & 7]
+                              * (np.float32(1.0) + token.astype(np.float32) / np.float32(16.0)))
+    convolution_weights = O.f32_to_bf16(GDN_CONV_PATTERN[np.arange(qkv_rows * 4) & 3])
+    idx = np.arange(batch * qkv_rows * 3)
+    history = O.f32_to_bf16(GDN_INPUT_PATTERN[(5 * idx + idx // 3) & 7] * np.float32(0.5))
+    return dict(input=inp.reshape(batch, hidden),
+                control_weights=control_weights.reshape(2 * control_rows, hidden),
+                a_log=a_log, dt_bias=dt_bias, projected=projected.reshape(batch, input_rows),
+                convolution_weights=convolution_weights.reshape(qkv_rows, 4),
+                history=history.reshape(batch, qkv_rows, 3), state_rows=GDN_STATE_ROWS.copy())
+
+
+def gdn_recurrence_fixture():
+    """qual/src/gdn_recurrence.rs:158-198 (fixture)."""
+    qk = np.array([0.75, -0.625, 0.5, -0.375, 0.25, -0.1875, 0.125, -0.0625], dtype=np.float32)
+    value = np.array([0.5, -0.375, 0.25, -0.125, 0.0625, -0.03125, 0.1875, -0.25], dtype=np.float32)
+    gate = np.array([-1.0, -0.5, -0.25, 0.0, 0.25, 0.5, 0.75, 1.0], dtype=np.float32)
+    norm = np.array([0.75, 0.875, 1.0, 1.125, 0.625, 1.25, 0.5, 1.5], dtype=np.float32)
+    batch, head, heads_k, heads_v = GDN_MAX_BATCH, 128, 16, 48
+    qk_width, value_width = heads_k * head, heads_v * head
+    qkv_rows, input_rows = 2 * qk_width + value_width, 2 * qk_width + 2 * value_width
+    qkv = np.zeros((batch, qkv_rows), dtype=np.uint16)
+    projected = np.zeros((batch, input_rows), dtype=np.uint16)
+    iq, iv = np.arange(qk_width), np.arange(value_width)
+    for token in range(batch):
+        qkv[token, :qk_width] = O.f32_to_bf16(qk[(iq + token) & 7])
+        qkv[token, qk_width:2 * qk_width] = O.f32_to_bf16(qk[(3 * iq + token + 1) & 7])
+        qkv[token, 2 * qk_width:] = O.f32_to_bf16(value[(5 * iv + token) & 7])
+        projected[token, qkv_rows:] = O.f32_to_bf16(gate[(iv + iv // head + token) & 7])
+    ic = np.arange(batch * heads_v)
+    log_decay = (np.float32(-0.125) - (ic & 7).astype(np.float32) * np.float32(0.03125)).astype(np.float32)
+    beta = (np.float32(0.25) + (ic & 3).astype(np.float32) * np.float32(0.125)).astype(np.float32)
+    norm_weight = O.f32_to_bf16(norm[np.arange(head) & 7])
+    istate = np.arange(batch * heads_v * head * head, dtype=np.uint64)
+    state = ((((istate * 13) & 31).astype(np.float32) - np.float32(15.5)) / np.float32(2048.0))
+    return dict(qkv=qkv, projected=projected, log_decay=log_decay.reshape(batch, heads_v),
+                beta=beta.reshape(batch, heads_v), norm_weight=norm_weight,
+                state=state.astype(np.float32).reshape(batch, heads_v, head, head),
+                state_rows=GDN_STATE_ROWS.copy())

@@ -31,6 +31,11 @@ class ArgmaxPair(C.Structure):
     _fields_ = [("value", C.c_float), ("index", C.c_int32)]
 
 
+class SamplingOptions(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_uint32),
+                ("stop_ids", C.c_uint32 * 2)]
+
+
 _vp = C.c_void_p
 _i = C.c_int
 
@@ -54,6 +59,11 @@ SIGNATURES = {
     "tk100_fp8_swiglu": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_down": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_gdn_output": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tk100_sample": (_i, [_vp, _vp, _i, _i, _vp, C.POINTER(SamplingOptions), _vp, _vp, _vp, _vp]),
+    "tk100_sampler_initial_state": (C.c_uint64, [C.c_uint64]),
+    "tk100_sampler_scratch_bytes": (C.c_size_t, [_i, _i]),
+    "tk100_gdn_prepare": (_i, [_vp, _vp, _i] + [_vp] * 11),
+    "tk100_gdn_recurrence": (_i, [_vp, _vp, _i] + [_vp] * 8),
     "tk100_fp8_lm_head": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_lm_head_sharded": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                        _i, _i, C.POINTER(C.c_uint64), _vp]),

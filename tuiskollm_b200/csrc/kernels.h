@@ -94,6 +94,66 @@ cudaError_t launch_resnorm_quant(cudaStream_t stream, int rows, int hidden, cons
                                  uint8_t* nvfp4_codes = nullptr, uint8_t* nvfp4_scales = nullptr,
                                  float nvfp4_divisor = 0.0f);
 
+// ----------------------------------------------------------------------- gdn.cu
+// Decode batches the gated-delta-net steps admit (tuisko-kernels-sm120/src/gdn/prepare.rs:13-24).
+constexpr int kGdnMaxBatch = 8;
+struct GdnPrepareParams {
+  int batch;
+  int hidden;        // 5120
+  int control_rows;  // 48 decay rows followed by 48 beta rows in `control_weights`
+  int qkv_rows;      // 10240 convolved channels
+  int input_rows;    // 16384 = row stride of `projected`
+  const uint16_t* input;                // [batch, hidden] BF16
+  const uint16_t* control_weights;      // [2 * control_rows, hidden] BF16
+  const uint16_t* a_log;                // [control_rows] BF16
+  const uint16_t* dt_bias;              // [control_rows] BF16
+  const uint16_t* projected;            // [batch, input_rows] BF16
+  const uint16_t* convolution_weights;  // [qkv_rows, 4] BF16
+  const uint32_t* state_rows;           // [batch]
+  uint16_t* history;                    // [state rows, qkv_rows, 3] BF16, updated in place
+  float* log_decay;                     // [batch, control_rows]
+  float* beta;                          // [batch, control_rows]
+  uint16_t* convolved;                  // [batch, qkv_rows] BF16
+};
+struct GdnRecurrenceParams {
+  int batch;
+  int qkv_rows;
+  int input_rows;
+  const uint16_t* qkv;          // [batch, qkv_rows] BF16: q (16 x 128), k (16 x 128), v (48 x 128)
+  const uint16_t* projected;    // [batch, input_rows] BF16; the gate follows the qkv rows
+  const float* log_decay;       // [batch, 48]
+  const float* beta;            // [batch, 48]
+  const uint16_t* norm_weight;  // [128] BF16
+  const uint32_t* state_rows;   // [batch]
+  float* state;                 // [state rows, 48, 128, 128] FP32, updated in place
+  uint16_t* output;             // [batch, 48 * 128] BF16
+};
+// True for the one geometry the kernels are written for (16 key heads, 48 value heads of 128).
+bool gdn_geometry_ok(int hidden, int control_rows, int qkv_rows, int input_rows);
+cudaError_t launch_gdn_prepare(cudaStream_t stream, const GdnPrepareParams& p);
+cudaError_t launch_gdn_recurrence(cudaStream_t stream, const GdnRecurrenceParams& p);
+
+// ------------------------------------------------------------------- sampler.cu
+constexpr int kSamplerMaxRows = 8;
+constexpr int kSamplerMaxTopK = 32;
+struct SamplerParams {
+  int rows;   // 1..=8 requests of a decode batch
+  int vocab;  // values per row, a multiple of 8
+  const uint16_t* logits;  // [rows, vocab] BF16
+  float temperature[kSamplerMaxRows];
+  float top_p[kSamplerMaxRows];
+  int top_k[kSamplerMaxRows];  // 1..=32
+  uint32_t stop_ids[2 * kSamplerMaxRows];
+  uint64_t* rng_state;  // [rows] xorshift64 states, advanced in place
+  uint64_t* scratch;    // sampler_scratch_bytes(rows, vocab), zero before the first launch
+  uint32_t* decisions;  // [rows, 2]: token id, stopped flag
+  uint32_t* top_out;    // optional [rows, 32, 2]: value bits (f32) and index of the survivors
+  uint32_t* status;
+};
+int sampler_slices(int vocab);
+size_t sampler_scratch_bytes(int rows, int vocab);
+cudaError_t launch_sampler(cudaStream_t stream, const SamplerParams& p);
+
 // ------------------------------------------------------------------ fp8_proj.cu
 // ------------------------------------------------------------------- fp8_mlp.cu
 struct Fp8SwigluParams {

@@ -281,6 +281,158 @@ Status check_plane(Context& ctx, const char* what, const char* plane, const void
 
 }  // namespace
 
+// ------------------------------------------------------------------- SamplerOp
+
+Status SamplerOp::launch(cudaStream_t stream, int rows, int vocab, const uint16_t* logits,
+                         const tk100_sampling_options* options, uint64_t* rng_state,
+                         uint64_t* scratch, tk100_sample_decision* decisions, uint32_t* top_out) {
+  const char* what = "sampler";
+  auto refuse = [&](const std::string& message) {
+    return ctx_.fail(TK100_ERR_LAUNCH, "[engine.sampling] " + message);
+  };
+  if (rows < 1 || rows > kSamplerMaxRows)
+    return refuse("batch " + std::to_string(rows) + " is outside the admitted range 1..=" +
+                  std::to_string(kSamplerMaxRows));
+  if (vocab < kSamplerMaxTopK || vocab % 8 != 0)
+    return refuse("sampling requires a BF16 logit row of a multiple of 8 values, at least " +
+                  std::to_string(kSamplerMaxTopK) + ", got " + std::to_string(vocab));
+  if (options == nullptr) return refuse("options are null");
+  TK100_TRY(check_plane(ctx_, what, "logit", logits, 16));
+  TK100_TRY(check_plane(ctx_, what, "generator state", rng_state, 8));
+  TK100_TRY(check_plane(ctx_, what, "scratch", scratch, 8));
+  TK100_TRY(check_plane(ctx_, what, "decision", decisions, 8));
+  SamplerParams p{};
+  p.rows = rows;
+  p.vocab = vocab;
+  p.logits = logits;
+  for (int r = 0; r < rows; ++r) {
+    const tk100_sampling_options& o = options[r];
+    // tuisko-engine/src/sampling.rs:110-128 and :130-148
+    if (!std::isfinite(o.temperature) || o.temperature < 0.0f)
+      return refuse("temperature must be finite and non-negative");
+    if (!std::isfinite(o.top_p) || o.top_p < 0.0f || o.top_p > 1.0f)
+      return refuse("top_p must be finite and in 0..=1");
+    if (o.top_k < 1 || o.top_k > static_cast<uint32_t>(vocab))
+      return refuse("top_k must be in 1..=" + std::to_string(vocab));
+    if (o.top_k > static_cast<uint32_t>(kSamplerMaxTopK))
+      return refuse("top_k " + std::to_string(o.top_k) + " exceeds the device sampler's " +
+                    std::to_string(kSamplerMaxTopK) + " candidates");
+    if (o.stop_ids[0] == o.stop_ids[1])
+      return refuse("generation stop-token identifiers must be distinct");
+    for (uint32_t token : o.stop_ids)
+      if (token >= static_cast<uint32_t>(vocab))
+        return refuse("generation stop token " + std::to_string(token) + " is outside vocabulary 0.." +
+                      std::to_string(vocab));
+    p.temperature[r] = o.temperature;
+    p.top_p[r] = o.top_p;
+    p.top_k[r] = static_cast<int>(o.top_k);
+    p.stop_ids[2 * r] = o.stop_ids[0];
+    p.stop_ids[2 * r + 1] = o.stop_ids[1];
+  }
+  p.rng_state = rng_state;
+  p.scratch = scratch;
+  p.decisions = reinterpret_cast<uint32_t*>(decisions);
+  p.top_out = top_out;
+  p.status = ctx_.status_word();
+  ctx_.count_launch();
+  return ctx_.check(launch_sampler(stream, p), "launching the sampler");
+}
+
+// ------------------------------------------------------- GdnPrepareOp / GdnRecurrenceOp
+
+namespace {
+// Qwen3.8-27B gated-delta-net geometry (tuisko-model/src/lib.rs, Arch constants).
+constexpr int kGdnControlRows = 48;
+constexpr int kGdnQkvRows = 10240;
+constexpr int kGdnInputRows = 16384;
+
+Status check_gdn_batch(Context& ctx, const char* what, int batch) {
+  if (batch < 1 || batch > kGdnMaxBatch) {
+    return ctx.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + what + " batch " +
+                                          std::to_string(batch) +
+                                          " is outside the admitted range 1..=" +
+                                          std::to_string(kGdnMaxBatch));
+  }
+  if (!gdn_geometry_ok(static_cast<int>(ctx.config().hidden), kGdnControlRows, kGdnQkvRows,
+                       kGdnInputRows)) {
+    return ctx.fail(TK100_ERR_LAUNCH,
+                    std::string("[gpu.launch] architecture geometry is incompatible with the ") +
+                        what + " schedule");
+  }
+  return TK100_OK;
+}
+}  // namespace
+
+Status GdnPrepareOp::launch(cudaStream_t stream, int batch, const uint16_t* input,
+                            const uint16_t* control_weights, const uint16_t* a_log,
+                            const uint16_t* dt_bias, const uint16_t* projected,
+                            const uint16_t* convolution_weights, const uint32_t* state_rows,
+                            uint16_t* history, float* log_decay, float* beta,
+                            uint16_t* convolved) {
+  const char* what = "GDN prepare";
+  TK100_TRY(check_gdn_batch(ctx_, what, batch));
+  TK100_TRY(check_plane(ctx_, what, "input", input, 16));
+  TK100_TRY(check_plane(ctx_, what, "control weight", control_weights, 16));
+  TK100_TRY(check_plane(ctx_, what, "a_log", a_log, 2));
+  TK100_TRY(check_plane(ctx_, what, "dt_bias", dt_bias, 2));
+  TK100_TRY(check_plane(ctx_, what, "projected", projected, 16));
+  TK100_TRY(check_plane(ctx_, what, "convolution weight", convolution_weights, 16));
+  TK100_TRY(check_plane(ctx_, what, "state row", state_rows, 4));
+  TK100_TRY(check_plane(ctx_, what, "history", history, 16));
+  TK100_TRY(check_plane(ctx_, what, "log_decay", log_decay, 4));
+  TK100_TRY(check_plane(ctx_, what, "beta", beta, 4));
+  TK100_TRY(check_plane(ctx_, what, "convolved", convolved, 16));
+  GdnPrepareParams p{};
+  p.batch = batch;
+  p.hidden = static_cast<int>(ctx_.config().hidden);
+  p.control_rows = kGdnControlRows;
+  p.qkv_rows = kGdnQkvRows;
+  p.input_rows = kGdnInputRows;
+  p.input = input;
+  p.control_weights = control_weights;
+  p.a_log = a_log;
+  p.dt_bias = dt_bias;
+  p.projected = projected;
+  p.convolution_weights = convolution_weights;
+  p.state_rows = state_rows;
+  p.history = history;
+  p.log_decay = log_decay;
+  p.beta = beta;
+  p.convolved = convolved;
+  ctx_.count_launch();
+  return ctx_.check(launch_gdn_prepare(stream, p), "launching GDN prepare");
+}
+
+Status GdnRecurrenceOp::launch(cudaStream_t stream, int batch, const uint16_t* qkv,
+                               const uint16_t* projected, const float* log_decay,
+                               const float* beta, const uint16_t* norm_weight,
+                               const uint32_t* state_rows, float* state, uint16_t* output) {
+  const char* what = "GDN recurrence";
+  TK100_TRY(check_gdn_batch(ctx_, what, batch));
+  TK100_TRY(check_plane(ctx_, what, "qkv", qkv, 16));
+  TK100_TRY(check_plane(ctx_, what, "projected", projected, 16));
+  TK100_TRY(check_plane(ctx_, what, "log_decay", log_decay, 4));
+  TK100_TRY(check_plane(ctx_, what, "beta", beta, 4));
+  TK100_TRY(check_plane(ctx_, what, "norm weight", norm_weight, 2));
+  TK100_TRY(check_plane(ctx_, what, "state row", state_rows, 4));
+  TK100_TRY(check_plane(ctx_, what, "state", state, 16));
+  TK100_TRY(check_plane(ctx_, what, "output", output, 16));
+  GdnRecurrenceParams p{};
+  p.batch = batch;
+  p.qkv_rows = kGdnQkvRows;
+  p.input_rows = kGdnInputRows;
+  p.qkv = qkv;
+  p.projected = projected;
+  p.log_decay = log_decay;
+  p.beta = beta;
+  p.norm_weight = norm_weight;
+  p.state_rows = state_rows;
+  p.state = state;
+  p.output = output;
+  ctx_.count_launch();
+  return ctx_.check(launch_gdn_recurrence(stream, p), "launching GDN recurrence");
+}
+
 Status ResidualNormOp::launch_plain(cudaStream_t stream, int batch, const uint16_t* input,
                                     const uint16_t* weight, uint16_t* output) {
   TK100_TRY(check_rows(ctx_, "residual norm", batch));
@@ -1065,6 +1217,50 @@ tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream, int rows,
   return tk100::GdnOutputProjectionOp(*ctx->impl)
       .launch(static_cast<cudaStream_t>(stream), rows, static_cast<int>(ctx->impl->config().hidden),
               columns, input, activation_codes, activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_sample(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab,
+                          const uint16_t* logits, const tk100_sampling_options* options,
+                          uint64_t* rng_state, uint64_t* scratch, tk100_sample_decision* decisions,
+                          uint32_t* top_out) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::SamplerOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), rows, vocab, logits, options, rng_state, scratch,
+              decisions, top_out);
+}
+
+uint64_t tk100_sampler_initial_state(uint64_t seed) {
+  // tuisko-engine/src/sampling.rs:247-250
+  const uint64_t scramble = 0x9e3779b97f4a7c15ull;
+  const uint64_t state = seed ^ scramble;
+  return state == 0 ? scramble : state;
+}
+
+size_t tk100_sampler_scratch_bytes(int rows, int vocab) {
+  return tk100::sampler_scratch_bytes(rows, vocab);
+}
+
+tk100_status tk100_gdn_prepare(tk100_ctx* ctx, tk100_stream stream, int batch,
+                               const uint16_t* input, const uint16_t* control_weights,
+                               const uint16_t* a_log, const uint16_t* dt_bias,
+                               const uint16_t* projected, const uint16_t* convolution_weights,
+                               const uint32_t* state_rows, uint16_t* history, float* log_decay,
+                               float* beta, uint16_t* convolved) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::GdnPrepareOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), batch, input, control_weights, a_log, dt_bias,
+              projected, convolution_weights, state_rows, history, log_decay, beta, convolved);
+}
+
+tk100_status tk100_gdn_recurrence(tk100_ctx* ctx, tk100_stream stream, int batch,
+                                  const uint16_t* qkv, const uint16_t* projected,
+                                  const float* log_decay, const float* beta,
+                                  const uint16_t* norm_weight, const uint32_t* state_rows,
+                                  float* state, uint16_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::GdnRecurrenceOp(*ctx->impl)
+      .launch(static_cast<cudaStream_t>(stream), batch, qkv, projected, log_decay, beta,
+              norm_weight, state_rows, state, output);
 }
 
 tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,

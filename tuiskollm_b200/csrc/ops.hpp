@@ -156,6 +156,46 @@ class ResidualNormOp {
   Context& ctx_;
 };
 
+// tuisko-engine/src/sampling.rs:56-95 (Sampler::new / Sampler::sample) for a decode batch of
+// requests, on the device: option validation as the reference's, selection in one launch.
+class SamplerOp {
+ public:
+  explicit SamplerOp(Context& ctx) : ctx_(ctx) {}
+  Status launch(cudaStream_t stream, int rows, int vocab, const uint16_t* logits,
+                const tk100_sampling_options* options, uint64_t* rng_state, uint64_t* scratch,
+                tk100_sample_decision* decisions, uint32_t* top_out);
+
+ private:
+  Context& ctx_;
+};
+
+// tuisko-kernels-sm120/src/gdn/prepare.rs:176-290 (GdnPrepareOp::launch): control mat-vecs
+// and the width-4 causal convolution of a decode batch of 1..=8 tokens, one launch.
+class GdnPrepareOp {
+ public:
+  explicit GdnPrepareOp(Context& ctx) : ctx_(ctx) {}
+  Status launch(cudaStream_t stream, int batch, const uint16_t* input,
+                const uint16_t* control_weights, const uint16_t* a_log, const uint16_t* dt_bias,
+                const uint16_t* projected, const uint16_t* convolution_weights,
+                const uint32_t* state_rows, uint16_t* history, float* log_decay, float* beta,
+                uint16_t* convolved);
+
+ private:
+  Context& ctx_;
+};
+
+// tuisko-kernels-sm120/src/gdn/recurrence.rs:171-236 (GdnRecurrenceOp::launch).
+class GdnRecurrenceOp {
+ public:
+  explicit GdnRecurrenceOp(Context& ctx) : ctx_(ctx) {}
+  Status launch(cudaStream_t stream, int batch, const uint16_t* qkv, const uint16_t* projected,
+                const float* log_decay, const float* beta, const uint16_t* norm_weight,
+                const uint32_t* state_rows, float* state, uint16_t* output);
+
+ private:
+  Context& ctx_;
+};
+
 // tuisko-kernels-sm120/src/fp8/projection.rs:510-794: one class serves the three planes;
 // `name` only labels error messages ("FP8 QKV", "FP8 GDN input", "FP8 LM head", ...).
 // How the LM head's per-shard maxima leave the projection: merged with the peers' over NVLink

@@ -1,0 +1,201 @@
+// Device-side token sampler: top-k / top-p selection with a per-request xorshift64 generator,
+// replacing the host `Sampler` (tuisko-engine/src/sampling.rs:76-231) and the device -> host copy
+// of a 248 320-wide logit row that feeds it.
+//
+// One launch for a decode batch of up to 8 rows.  A row of BF16 logits (0.5 MB) is cut into
+// slices, one CTA each; every warp streams its share with 16-byte loads and keeps the 32 best
+// (value, index) keys it has seen, one per lane, sorted -- a candidate enters by a ballot, a
+// population count and one shuffle.  The CTAs leave their lists in a caller-owned scratch and
+// take a ticket; the CTA that draws a row's last ticket merges the lists and runs the reference's
+// scalar selection on the k survivors (same float / double operations in the same order), so no
+// second launch and no host hop follow.
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tk100 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kList = 32;  // keys a warp keeps = the largest admitted top_k
+
+// Larger key = earlier in the reference's order: value descending under the IEEE total order
+// (+0 above -0), then index ascending (sampling.rs:219-224: only a strictly greater value
+// displaces a retained one).
+__device__ __forceinline__ uint64_t make_key(uint32_t bf16_bits, uint32_t index) {
+  const uint32_t ord = (bf16_bits & 0x8000u) ? (~bf16_bits & 0xffffu) : (bf16_bits | 0x8000u);
+  return (static_cast<uint64_t>(ord) << 32) | static_cast<uint64_t>(~index);
+}
+__device__ __forceinline__ uint32_t key_index(uint64_t key) { return ~static_cast<uint32_t>(key); }
+__device__ __forceinline__ float key_value(uint64_t key) {
+  const uint32_t ord = static_cast<uint32_t>(key >> 32);
+  const uint32_t bits = (ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu);
+  return __uint_as_float(bits << 16);
+}
+
+__device__ __forceinline__ uint64_t shfl64(uint64_t v, int src) {
+  return __shfl_sync(0xffffffffu, v, src);
+}
+
+// The warp's sorted list lives one key per lane (`held`, lane 0 the best).  Offers `cand` of
+// every lane whose `want` is set; `kth` is the key at position top_k - 1 (0 while the list is short).
+__device__ __forceinline__ void offer(uint64_t& held, uint64_t& kth, uint64_t cand, bool want,
+                                      int lane, int top_k) {
+  unsigned pending = __ballot_sync(0xffffffffu, want);
+  while (pending) {
+    const int src = __ffs(pending) - 1;
+    pending &= pending - 1;
+    const uint64_t c = shfl64(cand, src);
+    if (c > kth) {  // uniform across the warp: c and kth are
+      const int pos = __popc(__ballot_sync(0xffffffffu, held > c));
+      const uint64_t up = __shfl_up_sync(0xffffffffu, held, 1);
+      if (lane > pos) held = up;
+      else if (lane == pos) held = c;
+      kth = shfl64(held, top_k - 1);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams p) {
+  __shared__ uint64_t lists[kWarps][kList];
+  __shared__ int is_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.y, slice = blockIdx.x, slices = gridDim.x;
+  const int top_k = p.top_k[row];
+  const uint16_t* logits = p.logits + static_cast<size_t>(row) * p.vocab;
+  uint64_t* row_scratch = p.scratch + static_cast<size_t>(row) * (slices * kList);
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(p.scratch + static_cast<size_t>(p.rows) * slices * kList) + row;
+
+  pdl_wait();
+  pdl_trigger();
+
+  // 8-value chunks of the row, dealt to (slice, warp) in contiguous runs.
+  const int chunks = p.vocab / 8;
+  const int parts = slices * kWarps;
+  const int part = slice * kWarps + warp;
+  const int begin = static_cast<int>(static_cast<long long>(chunks) * part / parts);
+  const int end = static_cast<int>(static_cast<long long>(chunks) * (part + 1) / parts);
+
+  uint64_t held = 0, kth = 0;
+  bool nonfinite = false;
+  for (int base = begin; base < end; base += 32) {
+    const int chunk = base + lane;
+    uint32_t w[4] = {0, 0, 0, 0};
+    const bool live = chunk < end;
+    if (live) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(logits) + chunk);
+      w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t bits = (w[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      nonfinite |= live && (bits & 0x7f80u) == 0x7f80u;
+      const uint64_t cand = live ? make_key(bits, static_cast<uint32_t>(chunk * 8 + j)) : 0;
+      offer(held, kth, cand, cand > kth, lane, top_k);
+    }
+  }
+  if (nonfinite) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
+
+  lists[warp][lane] = held;
+  __syncthreads();
+  if (warp != 0) return;
+  // Warp 0 folds the other warps' lists into its own; each is sorted, so a list is done at its
+  // first key that does not enter.
+  for (int other = 1; other < kWarps; ++other) {
+    const uint64_t cand = lists[other][lane];
+    offer(held, kth, cand, cand > kth, lane, top_k);
+  }
+  row_scratch[slice * kList + lane] = held;
+  __threadfence();
+  __syncwarp();
+  if (lane == 0) is_last = atomicAdd(ticket, 1u) == static_cast<unsigned int>(slices - 1);
+  __syncwarp();
+  if (!is_last) return;
+  __threadfence();
+
+  // The row's last CTA: merge every slice's list (its own included, already in `held`).
+  for (int s = 0; s < slices; ++s) {
+    if (s == slice) continue;
+    const uint64_t cand = *reinterpret_cast<volatile uint64_t*>(row_scratch + s * kList + lane);
+    offer(held, kth, cand, cand > kth, lane, top_k);
+  }
+  if (lane == 0) *ticket = 0;  // ready for the next launch
+
+  if (p.top_out != nullptr && lane < top_k) {
+    p.top_out[(row * kList + lane) * 2] = __float_as_uint(key_value(held));
+    p.top_out[(row * kList + lane) * 2 + 1] = key_index(held);
+  }
+
+  // sampling.rs:102-108: temperature 0 or top_k 1 is the greedy route and draws no random number.
+  const float temperature = p.temperature[row];
+  uint32_t token = key_index(shfl64(held, 0));
+  if (!(temperature == 0.0f || top_k == 1)) {
+    // sampling.rs:175-210, evaluated by every lane on the same values.
+    const float maximum = key_value(shfl64(held, 0));
+    double weights[kList];
+    double total = 0.0;
+#pragma unroll 1
+    for (int i = 0; i < top_k; ++i) {
+      const float v = key_value(shfl64(held, i));
+      const float scaled = __fdiv_rn(v - maximum, temperature);
+      weights[i] = static_cast<double>(static_cast<float>(exp(static_cast<double>(scaled))));
+      total += weights[i];
+    }
+    const double cutoff = static_cast<double>(fmaxf(p.top_p[row], 1.17549435e-38f)) * total;
+    double retained_total = 0.0;
+    int retained = 0;
+#pragma unroll 1
+    for (int i = 0; i < top_k; ++i) {
+      retained_total += weights[i];
+      ++retained;
+      if (retained_total >= cutoff) break;
+    }
+    // xorshift64 (sampling.rs:244-260); the state advances once per sampled token.
+    uint64_t state = p.rng_state[row];
+    state ^= state << 13;
+    state ^= state >> 7;
+    state ^= state << 17;
+    const double unit = static_cast<double>(state >> 11) * (1.0 / 9007199254740992.0);
+    const double threshold = unit * retained_total;
+    double cumulative = 0.0;
+    int chosen = retained - 1;
+#pragma unroll 1
+    for (int i = 0; i < retained; ++i) {
+      cumulative += weights[i];
+      if (cumulative >= threshold) {
+        chosen = i;
+        break;
+      }
+    }
+    token = key_index(shfl64(held, chosen));
+    if (lane == 0) p.rng_state[row] = state;
+    if (!(retained_total > 0.0) || isinf(retained_total)) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
+  }
+  if (lane == 0) {
+    p.decisions[row * 2] = token;
+    p.decisions[row * 2 + 1] = (token == p.stop_ids[row * 2] || token == p.stop_ids[row * 2 + 1]) ? 1u : 0u;
+  }
+}
+
+}  // namespace
+
+int sampler_slices(int vocab) {
+  // About 2000 values per warp: 16 slices at the 248 320-wide vocabulary, fewer for small rows.
+  int slices = (vocab + 8 * 2048 - 1) / (8 * 2048);
+  return slices < 1 ? 1 : slices > 32 ? 32 : slices;
+}
+
+size_t sampler_scratch_bytes(int rows, int vocab) {
+  return static_cast<size_t>(rows) * sampler_slices(vocab) * kList * sizeof(uint64_t) +
+         static_cast<size_t>(rows) * sizeof(unsigned int) + 8;
+}
+
+cudaError_t launch_sampler(cudaStream_t stream, const SamplerParams& p) {
+  return launch_kernel(sampler_kernel, dim3(sampler_slices(p.vocab), p.rows), dim3(kThreads), 0,
+                       stream, p);
+}
+
+}  // namespace tk100

@@ -216,6 +216,84 @@ class GdnOutputProjectionOp:
                                             _ptr(weight_codes), _ptr(weight_scales), _ptr(output)))
 
 
+class SamplingOptions:
+    """tuisko-engine/src/sampling.rs:11-45: per-request controls; ``greedy()`` and the defaults of
+    the checkpoint's generation contract (temperature 1, top-p 0.95, top-k 20)."""
+
+    def __init__(self, temperature=1.0, top_p=0.95, top_k=20, seed=0):
+        self.temperature, self.top_p, self.top_k, self.seed = temperature, top_p, top_k, seed
+
+    @classmethod
+    def greedy(cls):
+        return cls(temperature=0.0, top_p=1.0, top_k=1, seed=0)
+
+
+class Sampler:
+    """Device counterpart of the reference's ``Sampler`` (tuisko-engine/src/sampling.rs:56-101) for a
+    decode batch: one entry of ``options`` / ``stop_ids`` per request.  The generator states and the
+    scratch live in device memory owned by this object; ``sample`` leaves the decisions
+    ``[rows, 2]`` (token id, stopped) in ``self.decisions`` without a host round trip."""
+
+    MAX_TOP_K = 32
+
+    def __init__(self, context: Context, vocab: int, options, stop_ids):
+        import torch
+
+        self.ctx, self.vocab = context, vocab
+        self.rows = len(options)
+        lib = context._lib
+        self._options = (_lib.SamplingOptions * self.rows)()
+        for i, (o, stops) in enumerate(zip(options, stop_ids)):
+            self._options[i].temperature = o.temperature
+            self._options[i].top_p = o.top_p
+            self._options[i].top_k = o.top_k
+            self._options[i].stop_ids[0], self._options[i].stop_ids[1] = stops
+        states = [lib.tk100_sampler_initial_state(o.seed) for o in options]
+        self.rng_state = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in states],
+                                      dtype=torch.int64, device="cuda")
+        nbytes = lib.tk100_sampler_scratch_bytes(self.rows, vocab)
+        self.scratch = torch.zeros((nbytes + 7) // 8, dtype=torch.int64, device="cuda")
+        self.decisions = torch.zeros((self.rows, 2), dtype=torch.int32, device="cuda")
+        self.top = torch.zeros((self.rows, self.MAX_TOP_K, 2), dtype=torch.int32, device="cuda")
+
+    def sample(self, stream, logits, want_top: bool = False):
+        c = self.ctx
+        c.check(c._lib.tk100_sample(c.handle, _stream(stream), self.rows, self.vocab, _ptr(logits),
+                                    self._options, _ptr(self.rng_state), _ptr(self.scratch),
+                                    _ptr(self.decisions), _ptr(self.top) if want_top else None))
+
+
+class GdnPrepareOp:
+    """tuisko-kernels-sm120/src/gdn/prepare.rs:226-290: control mat-vecs and the width-4 causal
+    convolution (with its in-place history shift) of a decode batch of 1..=8 tokens."""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def launch(self, stream, batch, input, control_weights, a_log, dt_bias, projected,
+               convolution_weights, state_rows, history, log_decay, beta, convolved):
+        c = self.ctx
+        c.check(c._lib.tk100_gdn_prepare(
+            c.handle, _stream(stream), batch, _ptr(input), _ptr(control_weights), _ptr(a_log),
+            _ptr(dt_bias), _ptr(projected), _ptr(convolution_weights), _ptr(state_rows),
+            _ptr(history), _ptr(log_decay), _ptr(beta), _ptr(convolved)))
+
+
+class GdnRecurrenceOp:
+    """tuisko-kernels-sm120/src/gdn/recurrence.rs:184-236: gated delta rule on the FP32 state
+    (in place) and the gated RMSNorm of its outputs."""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def launch(self, stream, batch, qkv, projected, log_decay, beta, norm_weight, state_rows,
+               state, output):
+        c = self.ctx
+        c.check(c._lib.tk100_gdn_recurrence(
+            c.handle, _stream(stream), batch, _ptr(qkv), _ptr(projected), _ptr(log_decay),
+            _ptr(beta), _ptr(norm_weight), _ptr(state_rows), _ptr(state), _ptr(output)))
+
+
 class LmHeadOp:
     """tuisko-kernels-sm120/src/fp8/projection.rs:704-793 plus the fused greedy argmax.
 

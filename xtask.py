@@ -43,11 +43,13 @@ SUITES = {
     "fp8-swiglu": ["tests/test_gpu_fp8_mlp.py"],
     "fp8-down": ["tests/test_gpu_fp8_mlp.py"],
     "gdn-output": ["tests/test_gpu_fp8_mlp.py"],
+    "gdn-prepare": ["tests/test_gpu_gdn.py"],
+    "gdn-recurrence": ["tests/test_gpu_gdn.py"],
     "nvfp4-swiglu": ["tests/test_gpu_nvfp4.py"],
     "nvfp4-down": ["tests/test_gpu_nvfp4.py"],
     "peer-exchange": ["tests/test_gpu_peer_sum.py", "tests/test_gpu_multi.py"],
     "static-entry": ["tests/test_zz_no_alloc.py"],
-    "host-codecs": ["tests/test_oracle_kat.py"],
+    "host-codecs": ["tests/test_oracle_kat.py", "tests/test_oracle_gdn.py"],
 }
 
 
