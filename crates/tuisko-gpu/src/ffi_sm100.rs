@@ -125,6 +125,14 @@ unsafe extern "C" {
         activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
         weight_scales: *const u16, output: *mut u16,
     ) -> Tk100Status;
+    pub fn tk100_materialize_gather(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, planes: c_int, sources: *const *const c_void,
+        bytes: *const u64, output: *mut c_void,
+    ) -> Tk100Status;
+    pub fn tk100_materialize_nvfp4_scales(
+        ctx: *mut Tk100Ctx, stream: Tk100Stream, planes: c_int, sources: *const *const u8,
+        rows_per_plane: u64, groups_per_row: u64, output: *mut u8,
+    ) -> Tk100Status;
     pub fn tk100_sample(
         ctx: *mut Tk100Ctx, stream: Tk100Stream, rows: c_int, vocab: c_int, logits: *const u16,
         options: *const Tk100SamplingOptions, rng_state: *mut u64, scratch: *mut u64,

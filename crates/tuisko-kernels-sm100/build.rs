@@ -14,6 +14,7 @@ const SOURCES: &[&str] = &[
     "fp8_pair.cu",
     "fp8_mlp.cu",
     "gdn.cu",
+    "materialize.cu",
     "nvfp4.cu",
     "nvfp4_pair.cu",
     "nvfp4_persist.cu",

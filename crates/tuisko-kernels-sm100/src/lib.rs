@@ -252,6 +252,47 @@ impl<A: Sm100Arch> GdnOutputProjectionOp<A> {
     }
 }
 
+/// Device counterpart of `tuisko-model/src/materialize.rs`: the fused QKV gather
+/// (`gather_source_planes`, `:295-314`) and the NVFP4 block-scale permutation
+/// (`swizzle_scale_planes`, `:353-408`) on planes that were uploaded as the checkpoint stores them.
+pub struct MaterializeOp {
+    ctx: Arc<Sm100Context>,
+}
+
+impl MaterializeOp {
+    pub fn new(ctx: &Arc<Sm100Context>) -> GpuResult<Self> {
+        Ok(Self { ctx: Arc::clone(ctx) })
+    }
+
+    /// Concatenates up to three device planes (`(address, bytes)` pairs) into `output`.
+    pub unsafe fn gather(
+        &self, stream: &CudaStream, planes: &[(*const u8, u64)], output: *mut u8,
+    ) -> GpuResult<()> {
+        let sources = planes.iter().map(|plane| plane.0.cast()).collect::<Vec<*const std::ffi::c_void>>();
+        let bytes = planes.iter().map(|plane| plane.1).collect::<Vec<u64>>();
+        self.ctx.check(unsafe {
+            ffi::tk100_materialize_gather(
+                self.ctx.raw, stream.cu_stream().cast(), rows_i32(planes.len()), sources.as_ptr(),
+                bytes.as_ptr(), output.cast(),
+            )
+        })
+    }
+
+    /// One (down) or two (gate, up) row-major `[rows_per_plane, groups_per_row]` E4M3 planes
+    /// into the `BlockScaleK16M128x4` order.
+    pub unsafe fn swizzle_scales(
+        &self, stream: &CudaStream, planes: &[*const u8], rows_per_plane: usize,
+        groups_per_row: usize, output: *mut u8,
+    ) -> GpuResult<()> {
+        self.ctx.check(unsafe {
+            ffi::tk100_materialize_nvfp4_scales(
+                self.ctx.raw, stream.cu_stream().cast(), rows_i32(planes.len()), planes.as_ptr(),
+                rows_per_plane as u64, groups_per_row as u64, output,
+            )
+        })
+    }
+}
+
 /// Device counterpart of the engine's host `Sampler` (`tuisko-engine/src/sampling.rs:56-101`)
 /// for a decode batch: the BF16 logit rows stay in device memory, one launch selects every
 /// request's token.  The caller owns the generator states (`[rows]` u64, started from

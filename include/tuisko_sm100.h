@@ -187,6 +187,26 @@ TK100_API tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream,
                                             float* activation_scales, const uint8_t* weight_codes,
                                             const uint16_t* weight_scales, uint16_t* output);
 
+/* gather_source_planes (tuisko-model/src/materialize.rs:295-314), the body of
+ * FullAttentionQkvBindings::materialize (:33-103) and MtpBindings::materialize_qkv (:119-152):
+ * concatenates `planes` (1..=3) device planes of `bytes[i]` bytes each into `output`, in order,
+ * without changing a byte.  `sources` and `bytes` are HOST arrays; the planes are device memory
+ * (the checkpoint's query/gate, key and value tensors as uploaded). */
+TK100_API tk100_status tk100_materialize_gather(tk100_ctx* ctx, tk100_stream stream, int planes,
+                                                const void* const* sources, const uint64_t* bytes,
+                                                void* output);
+
+/* swizzle_scale_planes (tuisko-model/src/materialize.rs:353-408): permutes 1 (down) or 2 (gate
+ * rows, then up rows) row-major E4M3 block-scale planes `[rows_per_plane, groups_per_row]` into
+ * the 128-row x 4-group tile order of nvfp4_scale_offset (:410-422) that the NVFP4 kernels
+ * consume.  Geometry is refused with the reference's messages (rows tiled by 128, groups by 4);
+ * a negative or NaN scale code (validate_nvfp4_scales, bindings.rs:1105-1120) sets device status
+ * bit 3.  `sources` is a HOST array of device pointers. */
+TK100_API tk100_status tk100_materialize_nvfp4_scales(tk100_ctx* ctx, tk100_stream stream,
+                                                      int planes, const uint8_t* const* sources,
+                                                      uint64_t rows_per_plane,
+                                                      uint64_t groups_per_row, uint8_t* output);
+
 /* Per-request sampling controls (tuisko-engine/src/sampling.rs:11-22 SamplingOptions, plus the
  * request's two stop-token identifiers, :57-60). */
 typedef struct tk100_sampling_options {

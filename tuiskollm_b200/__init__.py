@@ -6,8 +6,8 @@ operator interface over that ABI (device memory comes from torch tensors).
 """
 from .ops import (Context, FullAttentionQkvOp, GdnInputProjectionOp, GpuError, LmHeadOp,  # noqa: F401
                   Nvfp4DownOp, Nvfp4SwiGluOp, ResidualNormOp, Fp8ProjectionOp, Fp8SwiGluOp, Fp8DownOp,
-                  GdnOutputProjectionOp, GdnPrepareOp, GdnRecurrenceOp, Sampler, SamplingOptions)
+                  GdnOutputProjectionOp, GdnPrepareOp, GdnRecurrenceOp, Sampler, SamplingOptions, Materializer)
 
 __all__ = ["Context", "GpuError", "ResidualNormOp", "FullAttentionQkvOp", "GdnInputProjectionOp",
            "LmHeadOp", "Fp8ProjectionOp", "Nvfp4SwiGluOp", "Nvfp4DownOp", "Fp8SwiGluOp", "Fp8DownOp",
-           "GdnOutputProjectionOp", "GdnPrepareOp", "GdnRecurrenceOp", "Sampler", "SamplingOptions"]
+           "GdnOutputProjectionOp", "GdnPrepareOp", "GdnRecurrenceOp", "Sampler", "SamplingOptions", "Materializer"]

@@ -133,6 +133,26 @@ bool gdn_geometry_ok(int hidden, int control_rows, int qkv_rows, int input_rows)
 cudaError_t launch_gdn_prepare(cudaStream_t stream, const GdnPrepareParams& p);
 cudaError_t launch_gdn_recurrence(cudaStream_t stream, const GdnRecurrenceParams& p);
 
+// --------------------------------------------------------------- materialize.cu
+constexpr int kMaterializeMaxPlanes = 3;
+struct GatherParams {
+  int planes;                                    // 1..=3
+  const uint8_t* source[kMaterializeMaxPlanes];  // device planes, concatenated in this order
+  size_t offset[kMaterializeMaxPlanes + 1];      // byte offset of each plane in `output`; [planes] = total
+  uint8_t* output;
+};
+struct SwizzleParams {
+  int planes;                // 1 (down) or 2 (gate rows then up rows)
+  const uint8_t* source[2];  // [rows_per_plane, groups_per_row] E4M3 codes, row-major
+  size_t rows_per_plane;
+  size_t groups_per_row;     // multiple of 4
+  int vector_loads;          // sources 16-byte aligned and groups_per_row a multiple of 16
+  uint8_t* output;           // [planes * rows_per_plane * groups_per_row] in 128 x 4 tiles
+  uint32_t* status;
+};
+cudaError_t launch_gather_planes(cudaStream_t stream, const GatherParams& p, bool vector_words);
+cudaError_t launch_swizzle_scales(cudaStream_t stream, const SwizzleParams& p);
+
 // ------------------------------------------------------------------- sampler.cu
 constexpr int kSamplerMaxRows = 8;
 constexpr int kSamplerMaxTopK = 32;

@@ -281,6 +281,67 @@ Status check_plane(Context& ctx, const char* what, const char* plane, const void
 
 }  // namespace
 
+// --------------------------------------------------------------- MaterializeOp
+
+Status MaterializeOp::gather(cudaStream_t stream, int planes, const void* const* sources,
+                             const uint64_t* bytes, void* output) {
+  const char* what = "materialize gather";
+  if (planes < 1 || planes > kMaterializeMaxPlanes || sources == nullptr || bytes == nullptr)
+    return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + what + ": 1..=" +
+                                           std::to_string(kMaterializeMaxPlanes) +
+                                           " source planes are admitted");
+  TK100_TRY(check_plane(ctx_, what, "output", output, 1));
+  GatherParams p{};
+  p.planes = planes;
+  p.output = static_cast<uint8_t*>(output);
+  bool vector_words = aligned(output, 16);
+  size_t total = 0;
+  for (int i = 0; i < planes; ++i) {
+    if (bytes[i] != 0) TK100_TRY(check_plane(ctx_, what, "source", sources[i], 1));
+    p.source[i] = static_cast<const uint8_t*>(sources[i]);
+    p.offset[i] = total;
+    if (total + bytes[i] < total)
+      return ctx_.fail(TK100_ERR_LAUNCH, std::string("[gpu.launch] ") + what + ": length overflows");
+    total += bytes[i];
+    vector_words = vector_words && bytes[i] % 16 == 0 && aligned(sources[i], 16);
+  }
+  p.offset[planes] = total;
+  if (total == 0) return TK100_OK;
+  ctx_.count_launch();
+  return ctx_.check(launch_gather_planes(stream, p, vector_words), "launching the plane gather");
+}
+
+Status MaterializeOp::swizzle_scales(cudaStream_t stream, int planes,
+                                     const uint8_t* const* sources, uint64_t rows_per_plane,
+                                     uint64_t groups_per_row, uint8_t* output) {
+  const char* what = "NVFP4 scale layout";
+  auto refuse = [&](const std::string& message) {
+    return ctx_.fail(TK100_ERR_LAUNCH, "[checkpoint.source_binding] NVFP4 " + message);
+  };
+  if (planes < 1 || planes > 2 || sources == nullptr) return refuse("scale planes: 1 or 2 are admitted");
+  const uint64_t rows = rows_per_plane * static_cast<uint64_t>(planes);
+  // tuisko-model/src/materialize.rs:366-376
+  if (rows == 0 || rows % 128 != 0)
+    return refuse("scale rows " + std::to_string(rows) + " are not tiled by 128");
+  if (groups_per_row == 0 || groups_per_row % 4 != 0)
+    return refuse("scale groups " + std::to_string(groups_per_row) + " are not tiled by 4");
+  TK100_TRY(check_plane(ctx_, what, "output", output, 16));
+  SwizzleParams p{};
+  p.planes = planes;
+  p.rows_per_plane = rows_per_plane;
+  p.groups_per_row = groups_per_row;
+  p.vector_loads = groups_per_row % 16 == 0;
+  for (int i = 0; i < planes; ++i) {
+    TK100_TRY(check_plane(ctx_, what, "source", sources[i], 1));
+    p.source[i] = sources[i];
+    p.vector_loads = p.vector_loads && aligned(sources[i], 16);
+  }
+  p.output = output;
+  p.status = ctx_.status_word();
+  ctx_.count_launch();
+  return ctx_.check(launch_swizzle_scales(stream, p), "launching the NVFP4 scale layout");
+}
+
 // ------------------------------------------------------------------- SamplerOp
 
 Status SamplerOp::launch(cudaStream_t stream, int rows, int vocab, const uint16_t* logits,
@@ -1217,6 +1278,24 @@ tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream, int rows,
   return tk100::GdnOutputProjectionOp(*ctx->impl)
       .launch(static_cast<cudaStream_t>(stream), rows, static_cast<int>(ctx->impl->config().hidden),
               columns, input, activation_codes, activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_materialize_gather(tk100_ctx* ctx, tk100_stream stream, int planes,
+                                      const void* const* sources, const uint64_t* bytes,
+                                      void* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::MaterializeOp(*ctx->impl)
+      .gather(static_cast<cudaStream_t>(stream), planes, sources, bytes, output);
+}
+
+tk100_status tk100_materialize_nvfp4_scales(tk100_ctx* ctx, tk100_stream stream, int planes,
+                                            const uint8_t* const* sources,
+                                            uint64_t rows_per_plane, uint64_t groups_per_row,
+                                            uint8_t* output) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return tk100::MaterializeOp(*ctx->impl)
+      .swizzle_scales(static_cast<cudaStream_t>(stream), planes, sources, rows_per_plane,
+                      groups_per_row, output);
 }
 
 tk100_status tk100_sample(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab,

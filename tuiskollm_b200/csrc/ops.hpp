@@ -156,6 +156,21 @@ class ResidualNormOp {
   Context& ctx_;
 };
 
+// tuisko-model/src/materialize.rs: checkpoint planes -> run-time planes, on the device.
+class MaterializeOp {
+ public:
+  explicit MaterializeOp(Context& ctx) : ctx_(ctx) {}
+  // gather_source_planes (:295-314): `planes` device planes concatenated into `output`.
+  Status gather(cudaStream_t stream, int planes, const void* const* sources,
+                const uint64_t* bytes, void* output);
+  // swizzle_scale_planes (:353-408) with validate_nvfp4_scales of every code.
+  Status swizzle_scales(cudaStream_t stream, int planes, const uint8_t* const* sources,
+                        uint64_t rows_per_plane, uint64_t groups_per_row, uint8_t* output);
+
+ private:
+  Context& ctx_;
+};
+
 // tuisko-engine/src/sampling.rs:56-95 (Sampler::new / Sampler::sample) for a decode batch of
 // requests, on the device: option validation as the reference's, selection in one launch.
 class SamplerOp {

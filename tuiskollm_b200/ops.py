@@ -216,6 +216,61 @@ class GdnOutputProjectionOp:
                                             _ptr(weight_codes), _ptr(weight_scales), _ptr(output)))
 
 
+class Materializer:
+    """Device counterpart of tuisko-model/src/materialize.rs: checkpoint planes, uploaded as stored,
+    become the run-time planes without a host pass over their bytes."""
+
+    def __init__(self, context: Context):
+        self.ctx = context
+
+    def gather(self, stream, planes, output=None):
+        """``gather_source_planes`` (:295-314): the planes (1-D uint8 CUDA tensors) concatenated."""
+        total = sum(p.numel() * p.element_size() for p in planes)
+        if output is None:
+            output = torch.empty(total, dtype=torch.uint8, device="cuda")
+        c = self.ctx
+        pointers = (C.c_void_p * len(planes))(*[_ptr(p) for p in planes])
+        sizes = (C.c_uint64 * len(planes))(*[p.numel() * p.element_size() for p in planes])
+        c.check(c._lib.tk100_materialize_gather(c.handle, _stream(stream), len(planes), pointers, sizes,
+                                                _ptr(output)))
+        return output
+
+    def full_attention_qkv(self, stream, query_gate, key, value):
+        """``FullAttentionQkvBindings::materialize`` (:33-103): each argument is a
+        ``(weight_e4m3 [rows, columns] uint8, scale_bf16 [rows, 1])`` pair; returns the fused
+        ``(weight, scale)`` planes in query/gate, key, value row order."""
+        (qw, qs), (kw, ks), (vw, vs) = query_gate, key, value
+        shapes_ok = (kw.shape[0] == vw.shape[0] and qw.shape[1] == kw.shape[1] == vw.shape[1]
+                     and tuple(qs.shape) == (qw.shape[0], 1) and tuple(ks.shape) == (kw.shape[0], 1)
+                     and tuple(vs.shape) == (vw.shape[0], 1))
+        if not shapes_ok:
+            raise GpuError(5, "[checkpoint.source_binding] full-attention QKV source planes have "
+                              "incompatible shapes")
+        rows = qw.shape[0] + kw.shape[0] + vw.shape[0]
+        weight = self.gather(stream, [qw.reshape(-1), kw.reshape(-1), vw.reshape(-1)])
+        scale = self.gather(stream, [t.reshape(-1).view(torch.uint8) for t in (qs, ks, vs)])
+        return weight.view(rows, qw.shape[1]), scale.view(torch.int16).view(rows, 1)
+
+    def nvfp4_scales(self, stream, planes, output=None):
+        """``swizzle_scale_planes`` (:353-408): 1 or 2 row-major ``[rows, groups]`` uint8 planes ->
+        one plane in 128 x 4 tiles.  Raises on a negative or NaN scale code like
+        ``validate_nvfp4_scales`` (reads the device status word, so it synchronises)."""
+        rows, groups = planes[0].shape
+        if any(tuple(p.shape) != (rows, groups) for p in planes):
+            raise GpuError(5, "[checkpoint.source_binding] NVFP4 source scale plane length does not "
+                              "match its shape")
+        if output is None:
+            output = torch.empty(len(planes) * rows * groups, dtype=torch.uint8, device="cuda")
+        c = self.ctx
+        pointers = (C.c_void_p * len(planes))(*[_ptr(p) for p in planes])
+        c.check(c._lib.tk100_materialize_nvfp4_scales(c.handle, _stream(stream), len(planes), pointers,
+                                                      rows, groups, _ptr(output)))
+        if c.device_status(stream) & _lib.DEVICE_BAD_ARGUMENT:
+            raise GpuError(5, "[checkpoint.source_binding] NVFP4 scale plane contains a negative or "
+                              "NaN E4M3FN code")
+        return output
+
+
 class SamplingOptions:
     """tuisko-engine/src/sampling.rs:11-45: per-request controls; ``greedy()`` and the defaults of
     the checkpoint's generation contract (temperature 1, top-p 0.95, top-k 20)."""
