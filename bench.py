@@ -655,6 +655,7 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
     for b in (1, 8):
         groups = slots // b
         rows = [torch.arange(g * b, (g + 1) * b, dtype=torch.int32, device=dev) for g in range(groups)]
+        keep.append(rows)  # the captured launches read their slot indices from these tensors
         st = {"p": 0, "r": 0}
 
         def prep(b=b, rows=rows, st=st, groups=groups):

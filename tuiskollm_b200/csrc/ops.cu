@@ -1024,7 +1024,9 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
     if (splits > 8) splits = 8;
     if (splits > kb_total) splits = kb_total;
     if (splits < 1) splits = 1;
-    while (splits > 1 &&
+    // Only the reduction through global scratch (TK100_CLUSTER=0) needs room for the partial
+    // tiles and a ticket per tile; clusters reduce in shared memory.
+    while (ctx_.tuning().cluster == 0 && splits > 1 &&
            (static_cast<size_t>(splits) * tiles * block_tok * 128 * sizeof(float) >
                 ctx_.partial_bytes() ||
             static_cast<size_t>(tiles) > ctx_.counter_count())) {
