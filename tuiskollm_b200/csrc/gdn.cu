@@ -89,19 +89,28 @@ __global__ void __launch_bounds__(kPrepThreads) gdn_prepare_kernel(GdnPreparePar
     }
     pdl_wait();
     pdl_trigger();
+    // Two chunk columns at a time: all tokens' loads of a column pair are requested before the
+    // first FMA on them, so a batch of 8 costs one round trip to L2 per pair, not eight.
     float acc[kGdnMaxBatch];
 #pragma unroll
-    for (int t = 0; t < kGdnMaxBatch; ++t) {
-      acc[t] = 0.0f;
-      if (t < p.batch) {
+    for (int t = 0; t < kGdnMaxBatch; ++t) acc[t] = 0.0f;
 #pragma unroll
-        for (int c = 0; c < kMaxChunksPerThread; ++c) {
-          const int chunk = tid + c * kPrepThreads;
-          if (chunk < chunks) {
-            const uint4 x = ldg16(p.input + static_cast<size_t>(t) * p.hidden + chunk * 8);
-            acc[t] = dot8(x, w[c], acc[t]);
-          }
+    for (int c0 = 0; c0 < kMaxChunksPerThread; c0 += 2) {
+      uint4 x[kGdnMaxBatch][2];
+#pragma unroll
+      for (int t = 0; t < kGdnMaxBatch; ++t) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int chunk = tid + (c0 + c) * kPrepThreads;
+          x[t][c] = (t < p.batch && chunk < chunks)
+                        ? ldg16(p.input + static_cast<size_t>(t) * p.hidden + chunk * 8)
+                        : make_uint4(0, 0, 0, 0);
         }
+      }
+#pragma unroll
+      for (int t = 0; t < kGdnMaxBatch; ++t) {
+        acc[t] = dot8(x[t][0], w[c0], acc[t]);
+        acc[t] = dot8(x[t][1], w[c0 + 1], acc[t]);
       }
     }
 #pragma unroll
@@ -189,11 +198,8 @@ constexpr int kHeadDim = 128;
 constexpr int kKeyHeads = 16;
 constexpr int kValueHeads = 48;
 constexpr int kQkWidth = kKeyHeads * kHeadDim;
-constexpr int kRecSplit = 4;                       // CTAs (one cluster) per (token, value head)
 constexpr int kRecThreads = 256;
 constexpr int kRecWarps = kRecThreads / 32;
-constexpr int kRowsPerCta = kHeadDim / kRecSplit;  // 32
-constexpr int kRowsPerWarp = kRowsPerCta / kRecWarps;  // 4
 constexpr float kRmsEpsilon = 1.0e-6f;
 constexpr float kDeltaScale = 0.08838835f;  // 1 / sqrt(128)
 
@@ -207,8 +213,14 @@ __device__ __forceinline__ float4 load_bf16x4(const uint16_t* p) {
   return make_float4(bf16x2_lo(w.x), bf16x2_hi(w.x), bf16x2_lo(w.y), bf16x2_hi(w.y));
 }
 
-__global__ void __cluster_dims__(kRecSplit, 1, 1) __launch_bounds__(kRecThreads)
+// SPLIT = CTAs (one cluster) per (token, value head): 4 up to batch 4 (at most 768 CTAs of 32 state
+// rows), 2 beyond (at most 768 CTAs of 64 rows), so that every batch runs as one wave.
+template <int SPLIT>
+__global__ void __cluster_dims__(SPLIT, 1, 1) __launch_bounds__(kRecThreads)
     gdn_recurrence_kernel(GdnRecurrenceParams p) {
+  constexpr int kRecSplit = SPLIT;
+  constexpr int kRowsPerCta = kHeadDim / kRecSplit;
+  constexpr int kRowsPerWarp = kRowsPerCta / kRecWarps;
   // Every CTA of the cluster holds all partial sums of squares (pushed by their owners) and
   // its own 32 recurrent outputs.
   __shared__ float squares[kRecSplit * kRecWarps];
@@ -328,8 +340,11 @@ cudaError_t launch_gdn_prepare(cudaStream_t stream, const GdnPrepareParams& p) {
 
 cudaError_t launch_gdn_recurrence(cudaStream_t stream, const GdnRecurrenceParams& p) {
   // The cluster shape is compiled into the kernel (__cluster_dims__).
-  return launch_kernel(gdn_recurrence_kernel, dim3(p.batch * kValueHeads * kRecSplit),
-                       dim3(kRecThreads), 0, stream, p);
+  if (p.batch <= 4)
+    return launch_kernel(gdn_recurrence_kernel<4>, dim3(p.batch * kValueHeads * 4), dim3(kRecThreads),
+                         0, stream, p);
+  return launch_kernel(gdn_recurrence_kernel<2>, dim3(p.batch * kValueHeads * 2), dim3(kRecThreads), 0,
+                       stream, p);
 }
 
 }  // namespace tk100
