@@ -125,6 +125,10 @@ unsafe extern "C" {
         activation_codes: *mut u8, activation_scales: *mut f32, weight_codes: *const u8,
         weight_scales: *const u16, output: *mut u16,
     ) -> Tk100Status;
+    pub fn tk100_register_plane(
+        ctx: *mut Tk100Ctx, weight_codes: *const c_void, rows: u64, row_bytes: u64,
+    ) -> Tk100Status;
+    pub fn tk100_tensor_map_counts(ctx: *const Tk100Ctx, registered: *mut u64, transient: *mut u64);
     pub fn tk100_materialize_gather(
         ctx: *mut Tk100Ctx, stream: Tk100Stream, planes: c_int, sources: *const *const c_void,
         bytes: *const u64, output: *mut c_void,

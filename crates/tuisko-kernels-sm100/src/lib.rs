@@ -82,6 +82,18 @@ impl Sm100Context {
         self.check(unsafe { ffi::tk100_device_status(self.raw, stream.cu_stream().cast(), &mut word) })?;
         Ok(word)
     }
+
+    /// Encodes the TMA tensor map of a weight-code plane at load time (`tk100_register_plane`);
+    /// the counterpart of the sm_120 operators' route preparation in `*Op::new`.
+    ///
+    /// # Safety
+    ///
+    /// `weight_codes` is a live device plane of `rows * row_bytes` bytes, 128-byte aligned.
+    pub unsafe fn register_plane(&self, weight_codes: *const u8, rows: usize, row_bytes: usize) -> GpuResult<()> {
+        self.check(unsafe {
+            ffi::tk100_register_plane(self.raw, weight_codes.cast(), rows as u64, row_bytes as u64)
+        })
+    }
 }
 
 impl Drop for Sm100Context {

@@ -99,6 +99,18 @@ TK100_API uint64_t tk100_launch_count(const tk100_ctx* ctx);
  * tests; valid until the next call.  No counterpart in the reference. */
 TK100_API const char* tk100_last_kernel(tk100_ctx* ctx);
 
+/* Declares a weight-code plane (`rows` x `row_bytes` bytes, 128-byte aligned: an FP8 plane has
+ * row_bytes = K, a packed NVFP4 plane K / 2) so that its TMA tensor map is encoded now, at load
+ * time, instead of on the plane's first launch; registered maps are never evicted.  Replaces the
+ * per-operator `prepare` step of the reference (`*Op::new`, e.g.
+ * tuisko-kernels-sm120/src/fp8/projection.rs:525-545).  Optional: an undeclared plane is encoded
+ * on first use and cached.  Not stream-ordered, host work only. */
+TK100_API tk100_status tk100_register_plane(tk100_ctx* ctx, const void* weight_codes, uint64_t rows,
+                                            uint64_t row_bytes);
+/* Number of registered and of lazily cached tensor maps (for tests and reports). */
+TK100_API void tk100_tensor_map_counts(const tk100_ctx* ctx, uint64_t* registered,
+                                       uint64_t* transient);
+
 /* ResidualNormOp::launch_plain (tuisko-kernels-sm120/src/residual_norm.rs:425-456). */
 TK100_API tk100_status tk100_rms_norm(tk100_ctx* ctx, tk100_stream stream, int rows, const uint16_t* input,
                             const uint16_t* weight, uint16_t* output);

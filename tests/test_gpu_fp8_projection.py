@@ -325,3 +325,34 @@ def test_rejected_launches(tk, ctx):
         tk.Fp8ProjectionOp(ctx).launch(None, 1, out_rows, 5000, x, codes, scales, w, ws, out)
     assert "multiple of 128" in str(info.value)
     torch.cuda.synchronize()
+
+
+def test_registered_plane_is_not_encoded_again(tk, ctx, oracle):
+    """A plane declared with tk100_register_plane gets its tensor map at load time: its launches add
+    no weight map to the lazy cache (only the activation plane's), and the result is the one an
+    undeclared plane gives."""
+    import tuiskollm_b200.synth as synth
+    rows, n, k = 3, 1024, HIDDEN
+    w, s = synth.fp8_weights(7, 61, n, k)
+    x = synth.normal_bf16(7, 62, (rows, k))
+    wd, sd, xd = dev(w), dev(s.view(np.int16)), dev(x.view(np.int16))
+    wd2 = wd.clone()
+    codes = torch.empty((rows, k), dtype=torch.uint8, device="cuda")
+    scales = torch.empty((rows,), dtype=torch.float32, device="cuda")
+    out_a = torch.empty((rows, n), dtype=torch.int16, device="cuda")
+    out_b = torch.empty_like(out_a)
+    op = tk.FullAttentionQkvOp(ctx, n)
+    registered0, _ = ctx.tensor_map_counts
+    ctx.register_plane(wd)
+    registered1, transient1 = ctx.tensor_map_counts
+    assert registered1 == registered0 + 1
+    op.launch(None, rows, xd, codes, scales, wd, sd, out_a)
+    _, transient2 = ctx.tensor_map_counts
+    assert transient2 <= transient1 + 1            # the activation plane only
+    op.launch(None, rows, xd, codes, scales, wd2, sd, out_b)   # undeclared copy of the same plane
+    _, transient3 = ctx.tensor_map_counts
+    assert transient3 == transient2 + 1            # its weight map is encoded on first use
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b)
+    with pytest.raises(tk.GpuError, match="register plane"):
+        ctx.register_plane(wd.view(-1)[1:1 + 1024 * 64].view(1024, 64))   # not 128-byte aligned

@@ -59,6 +59,8 @@ SIGNATURES = {
     "tk100_fp8_swiglu": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_down": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_gdn_output": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tk100_register_plane": (_i, [_vp, _vp, C.c_uint64, C.c_uint64]),
+    "tk100_tensor_map_counts": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "tk100_materialize_gather": (_i, [_vp, _vp, _i, C.POINTER(_vp), C.POINTER(C.c_uint64), _vp]),
     "tk100_materialize_nvfp4_scales": (_i, [_vp, _vp, _i, C.POINTER(_vp), C.c_uint64, C.c_uint64, _vp]),
     "tk100_sample": (_i, [_vp, _vp, _i, _i, _vp, C.POINTER(SamplingOptions), _vp, _vp, _vp, _vp]),

@@ -190,21 +190,13 @@ const char* Context::last_kernel() {
   return route_text_.c_str();
 }
 
-Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
-                           CUtensorMap* out) {
-  const MapKey key{base, rows, row_bytes, box_rows, 0u};
-  auto it = maps_.find(key);
-  if (it != maps_.end()) {
-    *out = it->second;
-    return TK100_OK;
-  }
+Status Context::encode_map(const MapKey& key, CUtensorMap* out) {
   auto encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(encode_fn_);
-  CUtensorMap map;
-  const cuuint64_t dims[2] = {row_bytes, rows};
-  const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {128u, box_rows};
+  const cuuint64_t dims[2] = {key.row_bytes, key.rows};
+  const cuuint64_t strides[1] = {key.row_bytes};
+  const cuuint32_t box[2] = {128u, key.box_rows};
   const cuuint32_t elem[2] = {1u, 1u};
-  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(key.base), dims,
                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -212,9 +204,44 @@ Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, 
     return fail(TK100_ERR_DRIVER, "[gpu.driver] cuTensorMapEncodeTiled failed with CUresult " +
                                       std::to_string(static_cast<int>(r)));
   }
+  return TK100_OK;
+}
+
+Status Context::tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                           CUtensorMap* out) {
+  const MapKey key{base, rows, row_bytes, box_rows, 0u};
+  if (box_rows == 128u && !pinned_maps_.empty()) {
+    auto pinned = pinned_maps_.find(key);
+    if (pinned != pinned_maps_.end()) {
+      *out = pinned->second;
+      return TK100_OK;
+    }
+  }
+  auto it = maps_.find(key);
+  if (it != maps_.end()) {
+    *out = it->second;
+    return TK100_OK;
+  }
+  CUtensorMap map;
+  Status s = encode_map(key, &map);
+  if (s != TK100_OK) return s;
   if (maps_.size() > 4096) maps_.clear();
   maps_.emplace(key, map);
   *out = map;
+  return TK100_OK;
+}
+
+Status Context::register_plane(const void* base, uint64_t rows, uint64_t row_bytes) {
+  if (base == nullptr || !aligned(base, 128) || rows == 0 || row_bytes == 0 || row_bytes % 16 != 0) {
+    return fail(TK100_ERR_LAUNCH,
+                "[gpu.launch] register plane: a 128-byte aligned plane of rows x row_bytes "
+                "(row_bytes a multiple of 16) is required");
+  }
+  const MapKey key{base, rows, row_bytes, 128u, 0u};
+  CUtensorMap map;
+  Status s = encode_map(key, &map);
+  if (s != TK100_OK) return s;
+  pinned_maps_[key] = map;
   return TK100_OK;
 }
 
@@ -1280,6 +1307,17 @@ tk100_status tk100_fp8_gdn_output(tk100_ctx* ctx, tk100_stream stream, int rows,
   return tk100::GdnOutputProjectionOp(*ctx->impl)
       .launch(static_cast<cudaStream_t>(stream), rows, static_cast<int>(ctx->impl->config().hidden),
               columns, input, activation_codes, activation_scales, weight_codes, weight_scales, output);
+}
+
+tk100_status tk100_register_plane(tk100_ctx* ctx, const void* weight_codes, uint64_t rows,
+                                  uint64_t row_bytes) {
+  if (!ctx) return TK100_ERR_CONTEXT;
+  return ctx->impl->register_plane(weight_codes, rows, row_bytes);
+}
+
+void tk100_tensor_map_counts(const tk100_ctx* ctx, uint64_t* registered, uint64_t* transient) {
+  if (registered) *registered = ctx ? ctx->impl->pinned_map_count() : 0;
+  if (transient) *transient = ctx ? ctx->impl->transient_map_count() : 0;
 }
 
 tk100_status tk100_materialize_gather(tk100_ctx* ctx, tk100_stream stream, int planes,

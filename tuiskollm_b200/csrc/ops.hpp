@@ -133,6 +133,15 @@ class Context {
     }
   };
   std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps_;
+  // Maps of declared weight planes: encoded once by tk100_register_plane, never evicted.
+  std::unordered_map<MapKey, CUtensorMap, MapKeyHash> pinned_maps_;
+  Status encode_map(const MapKey& key, CUtensorMap* out);
+
+ public:
+  // Encodes the 128-row-box map of a weight-code plane ahead of its first launch.
+  Status register_plane(const void* base, uint64_t rows, uint64_t row_bytes);
+  size_t pinned_map_count() const { return pinned_maps_.size(); }
+  size_t transient_map_count() const { return maps_.size(); }
 };
 
 // tuisko-kernels-sm120/src/residual_norm.rs:382-508

@@ -83,6 +83,18 @@ class Context:
         self.check(self._lib.tk100_device_status(self.handle, _stream(stream), C.byref(word)))
         return word.value
 
+    def register_plane(self, weight_codes) -> None:
+        """Encodes the TMA tensor map of a 2-D weight-code plane now (tk100_register_plane)."""
+        rows, row_bytes = weight_codes.shape[0], weight_codes.shape[1] * weight_codes.element_size()
+        self.check(self._lib.tk100_register_plane(self.handle, _ptr(weight_codes), rows, row_bytes))
+
+    @property
+    def tensor_map_counts(self):
+        """(registered, lazily cached) tensor maps."""
+        registered, transient = C.c_uint64(0), C.c_uint64(0)
+        self._lib.tk100_tensor_map_counts(self.handle, C.byref(registered), C.byref(transient))
+        return registered.value, transient.value
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.tk100_launch_count(self.handle))
