@@ -332,7 +332,7 @@ def test_registered_plane_is_not_encoded_again(tk, ctx, oracle):
     no weight map to the lazy cache (only the activation plane's), and the result is the one an
     undeclared plane gives."""
     import tuiskollm_b200.synth as synth
-    rows, n, k = 3, 1024, HIDDEN
+    rows, n, k = 3, 1024, 5120
     w, s = synth.fp8_weights(7, 61, n, k)
     x = synth.normal_bf16(7, 62, (rows, k))
     wd, sd, xd = dev(w), dev(s.view(np.int16)), dev(x.view(np.int16))
