@@ -1044,7 +1044,8 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local, nccl_reduce=False):
 
 def run_case(args):
     """One small side case on one GPU (for profiling): `nvfp4:M`, `fp8:N:M`, `norm:M`,
-    `exchange`, or `issue` (the tcgen05 issue-rate micro-benchmark beside this file)."""
+    `exchange`, `stamps:N:M` (per-CTA time stamps, experiment build) or `issue` (the tcgen05
+    issue-rate micro-benchmark beside this file)."""
     if args.case == "issue":
         src = os.path.join(ROOT, "bench_tcgen05_issue.cu")
         exe = os.path.join(ROOT, "bench_tcgen05_issue")
@@ -1058,14 +1059,62 @@ def run_case(args):
 
     import torch
 
+    parts = args.case.split(":")
+    stamps = None
+    if parts[0] == "stamps":
+        # the plane's address has to be in the environment before the library reads its switches
+        torch.cuda.set_device(0)
+        stamps = torch.zeros(8192 * 8, dtype=torch.int64, device="cuda")
+        os.environ["TK100_STAMPS_PTR"] = hex(stamps.data_ptr())
+
     import tuiskollm_b200 as tk
     from tuiskollm_b200 import ops, synth
 
     torch.cuda.set_device(0)
     ctx = tk.Context(device=0)
-    parts = args.case.split(":")
     reps = args.case_reps
-    if parts[0] == "nvfp4":
+    if parts[0] == "stamps":
+        # Where a decode CTA's time goes: %globaltimer stamps of every CTA of the FP8 projection
+        # kernel (entry, set-up done, predecessor complete, first stage full, last MMA issued,
+        # accumulator complete, epilogue done, exit), taken from the last launch of a back-to-back
+        # sequence over rotating weight copies.  Needs a library built with TK100_EXPERIMENT=1.
+        import numpy as np
+        n_rows, m = int(parts[1]), int(parts[2])
+        copies = max(4, int(3 * 126e6 / (n_rows * HIDDEN)) + 1)
+        planes = [synth.torch_fp8_weights(SEED, 50 + c, n_rows, HIDDEN, "cuda") for c in range(copies)]
+        x = synth.torch_normal_bf16(SEED, 7, (m, HIDDEN), "cuda")
+        codes = torch.empty((m, HIDDEN), dtype=torch.uint8, device="cuda")
+        scales = torch.empty((m,), dtype=torch.float32, device="cuda")
+        out = torch.empty((m, n_rows), dtype=torch.bfloat16, device="cuda")
+        op = tk.GdnInputProjectionOp(ctx, n_rows)
+        op.launch(None, m, x, codes, scales, planes[0][0], planes[0][1], out)
+        for _ in range(3):
+            for c in range(copies):
+                op.launch(None, m, None, codes, scales, planes[c][0], planes[c][1], out)
+        torch.cuda.synchronize()
+        stamps.zero_()
+        for c in range(copies):
+            op.launch(None, m, None, codes, scales, planes[c][0], planes[c][1], out)
+        torch.cuda.synchronize()
+        kernel = ctx.last_kernel
+        splits = int(kernel.split("splits=")[1].split()[0])
+        ctas = ((n_rows + 127) // 128) * splits * ((m + 127) // 128)
+        st = stamps[: ctas * 8].cpu().numpy().reshape(ctas, 8).astype(np.float64)
+        if not st.any():
+            print(json.dumps({"case": args.case, "error": "no stamps: build the library with "
+                              "TK100_EXPERIMENT=1 python -m tuiskollm_b200.build"}), flush=True)
+            return 1
+        d = (st - st[:, 0].min()) / 1e3
+        med = lambda v: round(float(np.median(v)), 2)
+        rows = [{"kernel": kernel, "ctas": ctas,
+                 "us_median_per_cta": {"entry_to_setup_done": med(d[:, 1] - d[:, 0]),
+                                       "entry_to_first_stage_full": med(d[:, 3] - d[:, 0]),
+                                       "first_full_to_last_mma": med(d[:, 4] - d[:, 3]),
+                                       "accumulator_complete_to_epilogue_done": med(d[:, 6] - d[:, 5]),
+                                       "epilogue_done_to_exit": med(d[:, 7] - d[:, 6])},
+                 "us_spread_of_cta_entries": round(float(d[:, 0].max()), 2),
+                 "us_first_entry_to_last_exit": round(float(d[:, 7].max()), 2)}]
+    elif parts[0] == "nvfp4":
         m = int(parts[1])
         which = parts[2] if len(parts) > 2 else "all"
         pl = MlpPlanes(torch, ops, synth, m, mlp_weights(synth))

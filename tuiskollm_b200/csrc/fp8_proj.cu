@@ -207,7 +207,20 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     mbar_init(&ctl->go, 1);
     mbar_init(&ctl->done, on_leader ? static_cast<uint32_t>(p.splits - 1) * 4u : 1u);
     fence_mbar_init();
-    prefetch_tensormap(&tmap_w);
+    // The first pass of weight tiles over the ring is requested here, before the TMEM allocation
+    // and the CTA barrier below are through: the weights depend on nothing, and the sooner the
+    // first request leaves the sooner the stream starts (the ramp is a third of a decode launch).
+    {
+      const uint64_t pol_w = l2_policy_evict_first();  // weights are streamed once
+      const bool load_a = !TK100_DBG(p, DBG_NO_ACT) && !fused_quant;
+      const uint32_t tx_bytes = load_a ? STAGE_BYTES : kWStageBytes;
+      const int pre = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&ctl->full[i], tx_bytes);
+        tma_load_2d(smem + i * STAGE_BYTES, &tmap_w, &ctl->full[i], (kb_begin + i) * kTileKBytes,
+                    tile_n * kTileRows, pol_w);
+      }
+    }
     if (!fused_quant) prefetch_tensormap(&tmap_a);
   }
   if (warp == 1) {
@@ -229,17 +242,12 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     if (lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();  // weights are streamed once
       const uint64_t pol_a = l2_policy_evict_last();   // activation codes are re-read by every CTA
-      // First pass over the ring: the weight tiles do not depend on the predecessor kernel,
-      // so they are requested before pdl_wait(); the activation-code tiles of the same
-      // stages follow once the predecessor (the quantiser) is known to be complete.
+      // The weight tiles of the first pass over the ring are already on their way (requested
+      // during set-up, they do not depend on the predecessor kernel); the activation-code tiles
+      // of the same stages follow once the predecessor (the quantiser) is known to be complete.
       const bool load_a = !TK100_DBG(p, DBG_NO_ACT) && !fused_quant;
       const uint32_t tx_bytes = load_a ? STAGE_BYTES : kWStageBytes;
       const int pre = nkb < STAGES ? nkb : STAGES;
-      for (int i = 0; i < pre; ++i) {
-        mbar_arrive_expect_tx(&ctl->full[i], tx_bytes);
-        tma_load_2d(smem + i * STAGE_BYTES, &tmap_w, &ctl->full[i], (kb_begin + i) * kTileKBytes,
-                    tile_n * kTileRows, pol_w);
-      }
       pdl_wait();
       TK100_STAMP(p, 2);
       for (int i = 0; i < pre && load_a; ++i) {

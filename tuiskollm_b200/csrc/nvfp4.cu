@@ -167,6 +167,49 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
   // cluster barriers around remote loads.
   const bool pushed = !GATE_UP && p.cluster == 2 && (clustered || pair_swiglu);
 
+  // The producer's loads (thread 0 issues all of them).
+  const uint64_t pol_a = l2_policy_evict_last();
+  // weights are streamed once when there is a single token tile, shared otherwise
+  const uint64_t pol_w = tiles_m == 1 ? l2_policy_evict_first() : pol_a;
+  // Scale tiles: chunk (tile, kb) of a plane with G = K/16 groups per row starts at
+  // ((tile * G/4) + 4 * kb) * 512 bytes and is 2 KB long (4 consecutive 512-byte chunks).
+  const size_t chunks_per_tile = static_cast<size_t>(p.k / 64);
+  const uint8_t* sfa0 = p.w_scales + (static_cast<size_t>(w_tile) * chunks_per_tile) * kSfChunk;
+  const uint8_t* sfa1 =
+      p.w_scales + (static_cast<size_t>(p.up_row_offset / kRows + tile_n) * chunks_per_tile) * kSfChunk;
+  const uint8_t* sfb = p.a_scales + (static_cast<size_t>(tok0 / kRows) * chunks_per_tile) * kSfChunk;
+  auto load_weights = [&](int i, int s) {
+    uint8_t* stage = smem + s * STAGE_BYTES;
+    const int kb = kb_begin + i;
+    const int kbyte = kb * kStageKBytes;
+    const size_t sf_off = static_cast<size_t>(kb) * kSfStage;
+    // scale bytes of this stage: 512 per 64-element step that exists (the code tiles always
+    // arrive as full boxes, zero-filled beyond the end of the row)
+    const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
+    const uint32_t code_bytes = NW * kWTile + BLOCK_TOK * kStageKBytes;
+    mbar_arrive_expect_tx(&ctl->full[s],
+                          TK100_DBG(p, DBG_NO_ACT)
+                              ? NW * (kWTile + sf_bytes)
+                              : code_bytes + (NW + 1) * sf_bytes);
+    tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, w_tile * kRows, pol_w);
+    bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, sf_bytes, &ctl->full[s], pol_w);
+    if (GATE_UP) {
+      tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
+                  p.up_row_offset + tile_n * kRows, pol_w);
+      bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, sf_bytes, &ctl->full[s], pol_w);
+    }
+  };
+  auto load_activations = [&](int i, int s) {
+    if (TK100_DBG(p, DBG_NO_ACT)) return;
+    uint8_t* stage = smem + s * STAGE_BYTES;
+    const int kb = kb_begin + i;
+    tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kb * kStageKBytes, tok0, pol_a);
+    const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
+    bulk_load_1d(stage + OFF_SFB, sfb + static_cast<size_t>(kb) * kSfStage, sf_bytes,
+                 &ctl->full[s], pol_a);
+  };
+  const int pre = nkb < STAGES ? nkb : STAGES;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&ctl->full[s], 1);
@@ -178,7 +221,9 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
     mbar_init(&ctl->done, pushed ? static_cast<uint32_t>(pair_swiglu ? 1 : p.splits - 1) * (kEpilogueThreads / 32) : 1u);
     ctl->flag = 0u;
     fence_mbar_init();
-    prefetch_tensormap(&tmap_w);
+    // Weights of the first ring pass leave now, ahead of the TMEM allocation and the CTA barrier:
+    // they depend on nothing (the activation operands follow after pdl_wait()).
+    for (int i = 0; i < pre; ++i) load_weights(i, i);
     prefetch_tensormap(&tmap_a);
   }
   if (warp == 1) {
@@ -196,49 +241,7 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint64_t pol_a = l2_policy_evict_last();
-      // weights are streamed once when there is a single token tile, shared otherwise
-      const uint64_t pol_w = tiles_m == 1 ? l2_policy_evict_first() : pol_a;
-      // Scale tiles: chunk (tile, kb) of a plane with G = K/16 groups per row starts at
-      // ((tile * G/4) + 4 * kb) * 512 bytes and is 2 KB long (4 consecutive 512-byte chunks).
-      const size_t chunks_per_tile = static_cast<size_t>(p.k / 64);
-      const uint8_t* sfa0 = p.w_scales + (static_cast<size_t>(w_tile) * chunks_per_tile) * kSfChunk;
-      const uint8_t* sfa1 =
-          p.w_scales + (static_cast<size_t>(p.up_row_offset / kRows + tile_n) * chunks_per_tile) * kSfChunk;
-      const uint8_t* sfb = p.a_scales + (static_cast<size_t>(tok0 / kRows) * chunks_per_tile) * kSfChunk;
-      auto load_weights = [&](int i, int s) {
-        uint8_t* stage = smem + s * STAGE_BYTES;
-        const int kb = kb_begin + i;
-        const int kbyte = kb * kStageKBytes;
-        const size_t sf_off = static_cast<size_t>(kb) * kSfStage;
-        // scale bytes of this stage: 512 per 64-element step that exists (the code tiles always
-        // arrive as full boxes, zero-filled beyond the end of the row)
-        const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
-        const uint32_t code_bytes = NW * kWTile + BLOCK_TOK * kStageKBytes;
-        mbar_arrive_expect_tx(&ctl->full[s],
-                              TK100_DBG(p, DBG_NO_ACT)
-                                  ? NW * (kWTile + sf_bytes)
-                                  : code_bytes + (NW + 1) * sf_bytes);
-        tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, w_tile * kRows, pol_w);
-        bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, sf_bytes, &ctl->full[s], pol_w);
-        if (GATE_UP) {
-          tma_load_2d(stage + kWTile, &tmap_w, &ctl->full[s], kbyte,
-                      p.up_row_offset + tile_n * kRows, pol_w);
-          bulk_load_1d(stage + OFF_SFA + kSfStage, sfa1 + sf_off, sf_bytes, &ctl->full[s], pol_w);
-        }
-      };
-      auto load_activations = [&](int i, int s) {
-        if (TK100_DBG(p, DBG_NO_ACT)) return;
-        uint8_t* stage = smem + s * STAGE_BYTES;
-        const int kb = kb_begin + i;
-        tma_load_2d(stage + OFF_A, &tmap_a, &ctl->full[s], kb * kStageKBytes, tok0, pol_a);
-        const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
-        bulk_load_1d(stage + OFF_SFB, sfb + static_cast<size_t>(kb) * kSfStage, sf_bytes,
-                     &ctl->full[s], pol_a);
-      };
-      // weights of the first ring pass before pdl_wait(), activation operands after it
-      const int pre = nkb < STAGES ? nkb : STAGES;
-      for (int i = 0; i < pre; ++i) load_weights(i, i);
+      // the weights of the first ring pass were requested during set-up
       pdl_wait();
       for (int i = 0; i < pre; ++i) load_activations(i, i);
       bool ok = true;
