@@ -31,6 +31,7 @@ neither be built nor run here).
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -682,6 +683,43 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
             keep.append(graph)
     keep.append((g_x, g_cw, g_alog, g_dt, g_proj, g_convw, g_hist, g_state, g_norm, g_decay, g_beta,
                  g_conv, g_out))
+
+    # ---- device sampler on BF16 logit rows of the full vocabulary (top-k 20, top-p 0.95), and the
+    # load-time NVFP4 scale permutation of the gate/up planes
+    vocab_s = lm["vocab"]
+    for b in (1, 8):
+        copies_s = max(2, int(3 * 126e6 / (b * vocab_s * 2)) + 1)
+        rows_s = [synth.torch_normal_bf16(SEED, 500 + c, (b, vocab_s), dev, std=3.0) for c in range(copies_s)]
+        samp = tk.Sampler(ctx, vocab_s, [tk.SamplingOptions(seed=i) for i in range(b)], [(1, 2)] * b)
+        st_s = {"i": 0}
+
+        def draw(samp=samp, rows_s=rows_s, st_s=st_s, copies_s=copies_s):
+            samp.sample(None, rows_s[st_s["i"] % copies_s])
+            st_s["i"] += 1
+
+        draw()
+        graph = capture(torch, draw, copies_s)
+        case = f"device_sampler:B{b}"
+        proto.add(case, graph.replay, copies_s)
+        meta[case] = {"config": "next", "op": "device_sampler_top20_p95", "M": b, "kernel": "sampler_kernel",
+                      "kind": "hbm", "bytes": b * vocab_s * 2 + b * 16, "cpu": None}
+        keep.append((graph, rows_s, samp))
+    mat = tk.Materializer(ctx)
+    sc_src = [torch.randint(0, 0x7F, (inter, HIDDEN // 16), dtype=torch.uint8, device=dev) for _ in range(2)]
+    sc_out = torch.empty(2 * inter * (HIDDEN // 16), dtype=torch.uint8, device=dev)
+    sc_ptrs = (ctypes.c_void_p * 2)(sc_src[0].data_ptr(), sc_src[1].data_ptr())
+
+    def swizzle():
+        ctx.check(ctx._lib.tk100_materialize_nvfp4_scales(ctx.handle, ops._stream(None), 2, sc_ptrs, inter,
+                                                          HIDDEN // 16, sc_out.data_ptr()))
+
+    swizzle()
+    graph = capture(torch, swizzle, 4)
+    proto.add("nvfp4_scale_layout", graph.replay, 4)
+    meta["nvfp4_scale_layout"] = {"config": "next", "op": "materialize_nvfp4_scales_gate_up", "M": 0,
+                                  "kernel": "swizzle_scales_kernel", "kind": "hbm",
+                                  "bytes": 2 * 2 * inter * (HIDDEN // 16), "cpu": None}
+    keep.append((graph, sc_src, sc_out, sc_ptrs, mat))
 
     # ---- fused residual + RMSNorm + quantise (configurations 1 and 5, and the metric's M = 512)
     normop = tk.ResidualNormOp(ctx)

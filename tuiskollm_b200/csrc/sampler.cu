@@ -4,11 +4,12 @@
 //
 // One launch for a decode batch of up to 8 rows.  A row of BF16 logits (0.5 MB) is cut into
 // slices, one CTA each; every warp streams its share with 16-byte loads and keeps the 32 best
-// (value, index) keys it has seen, one per lane, sorted -- a candidate enters by a ballot, a
-// population count and one shuffle.  The CTAs leave their lists in a caller-owned scratch and
-// take a ticket; the CTA that draws a row's last ticket merges the lists and runs the reference's
-// scalar selection on the k survivors (same float / double operations in the same order), so no
-// second launch and no host hop follow.
+// (value, index) keys it has seen, one per lane, sorted -- a few candidates enter one by one (a
+// ballot, a population count and one shuffle each), many at once through a bitonic sort and
+// merge across the lanes.  Lists fold pairwise (warp -> CTA through shared memory); the CTAs leave
+// theirs in a caller-owned scratch and take a ticket; the CTA that draws a row's last ticket
+// merges them and runs the reference's scalar selection on the k survivors (same float / double
+// operations in the same order), so no second launch and no host hop follow.
 #include <math.h>
 
 #include "common.cuh"
@@ -36,15 +37,81 @@ __device__ __forceinline__ float key_value(uint64_t key) {
   return __uint_as_float(bits << 16);
 }
 
+// exp of a non-positive f32 argument as the f32 nearest to the exact value, returned as a double:
+// the reference's `((v - max) / temperature).exp() as f64`.  Evaluated in double (argument
+// reduction by ln 2 in two pieces, degree-13 Taylor polynomial on |r| <= 0.347: relative error
+// below 1e-16), so the rounding to f32 is the correctly rounded result except within 1e-9 of a
+// rounding boundary.  Written out here rather than calling the library exponential, whose slow
+// path is a function call.
+__device__ __forceinline__ double softmax_weight(float scaled) {
+  const double x = static_cast<double>(scaled);
+  if (!(x >= -104.0)) return 0.0;  // below half of the smallest f32 denormal (e^-103.97)
+  const double n = rint(x * 1.4426950408889634);
+  double r = fma(n, -6.93147180369123816490e-01, x);
+  r = fma(n, -1.90821492927058770002e-10, r);
+  double p = 1.0 / 6227020800.0;
+  p = fma(p, r, 1.0 / 479001600.0);
+  p = fma(p, r, 1.0 / 39916800.0);
+  p = fma(p, r, 1.0 / 3628800.0);
+  p = fma(p, r, 1.0 / 362880.0);
+  p = fma(p, r, 1.0 / 40320.0);
+  p = fma(p, r, 1.0 / 5040.0);
+  p = fma(p, r, 1.0 / 720.0);
+  p = fma(p, r, 1.0 / 120.0);
+  p = fma(p, r, 1.0 / 24.0);
+  p = fma(p, r, 1.0 / 6.0);
+  p = fma(p, r, 0.5);
+  p = fma(p, r, 1.0);
+  p = fma(p, r, 1.0);
+  const double scale = __longlong_as_double((static_cast<long long>(n) + 1023) << 52);  // 2^n, n >= -151
+  return static_cast<double>(static_cast<float>(p * scale));
+}
+
 __device__ __forceinline__ uint64_t shfl64(uint64_t v, int src) {
   return __shfl_sync(0xffffffffu, v, src);
 }
 
+__device__ __forceinline__ uint64_t max64(uint64_t a, uint64_t b) { return a > b ? a : b; }
+__device__ __forceinline__ uint64_t min64(uint64_t a, uint64_t b) { return a < b ? a : b; }
+
+// Bitonic sort of one key per lane into descending order (lane 0 the largest): 15 exchanges.
+__device__ __forceinline__ uint64_t sort_descending(uint64_t v, int lane) {
+#pragma unroll
+  for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const uint64_t other = __shfl_xor_sync(0xffffffffu, v, j);
+      const bool keep_max = ((lane & j) == 0) == ((lane & k) == 0);
+      v = keep_max ? max64(v, other) : min64(v, other);
+    }
+  }
+  return v;
+}
+
+// The 32 largest of two descending lists (one key per lane each), descending: reversing one list
+// makes the lane-wise maxima a bitonic sequence of exactly those keys; 5 exchanges sort it.
+__device__ __forceinline__ uint64_t merge_descending(uint64_t a, uint64_t b, int lane) {
+  uint64_t v = max64(a, __shfl_sync(0xffffffffu, b, 31 - lane));
+#pragma unroll
+  for (int j = 16; j > 0; j >>= 1) {
+    const uint64_t other = __shfl_xor_sync(0xffffffffu, v, j);
+    v = ((lane & j) == 0) ? max64(v, other) : min64(v, other);
+  }
+  return v;
+}
+
 // The warp's sorted list lives one key per lane (`held`, lane 0 the best).  Offers `cand` of
 // every lane whose `want` is set; `kth` is the key at position top_k - 1 (0 while the list is short).
+// Many candidates at once (the first batches of a scan) go through a sort and a merge; a few
+// enter one by one, each by a ballot, a population count and one shuffle.
 __device__ __forceinline__ void offer(uint64_t& held, uint64_t& kth, uint64_t cand, bool want,
                                       int lane, int top_k) {
   unsigned pending = __ballot_sync(0xffffffffu, want);
+  if (__popc(pending) >= 6) {
+    held = merge_descending(held, sort_descending(want ? cand : 0ull, lane), lane);
+    kth = shfl64(held, top_k - 1);
+    return;
+  }
   while (pending) {
     const int src = __ffs(pending) - 1;
     pending &= pending - 1;
@@ -59,7 +126,7 @@ __device__ __forceinline__ void offer(uint64_t& held, uint64_t& kth, uint64_t ca
   }
 }
 
-__global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams p) {
+__global__ void __launch_bounds__(kThreads, 1) sampler_kernel(SamplerParams p) {
   __shared__ uint64_t lists[kWarps][kList];
   __shared__ int is_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -89,39 +156,72 @@ __global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams p) {
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(logits) + chunk);
       w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     }
+    uint64_t cand[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const uint32_t bits = (w[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
       nonfinite |= live && (bits & 0x7f80u) == 0x7f80u;
-      const uint64_t cand = live ? make_key(bits, static_cast<uint32_t>(chunk * 8 + j)) : 0;
-      offer(held, kth, cand, cand > kth, lane, top_k);
+      cand[j] = live ? make_key(bits, static_cast<uint32_t>(chunk * 8 + j)) : 0;
+    }
+    if (kth == 0) {
+      // The list is not full yet (the first 256 values of the warp's share): sort the eight
+      // batches side by side -- independent exchange chains hide each other's shuffle latency --
+      // and fold them as a tree, instead of eight sort-and-merge rounds one after the other.
+#pragma unroll
+      for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int jj = k >> 1; jj > 0; jj >>= 1) {
+          const bool keep_max = ((lane & jj) == 0) == ((lane & k) == 0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint64_t other = __shfl_xor_sync(0xffffffffu, cand[j], jj);
+            cand[j] = keep_max ? max64(cand[j], other) : min64(cand[j], other);
+          }
+        }
+      }
+#pragma unroll
+      for (int span = 4; span > 0; span >>= 1) {
+#pragma unroll
+        for (int j = 0; j < span; ++j) cand[j] = merge_descending(cand[j], cand[j + span], lane);
+      }
+      held = merge_descending(held, cand[0], lane);
+      kth = shfl64(held, top_k - 1);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) offer(held, kth, cand[j], cand[j] > kth, lane, top_k);
     }
   }
   if (nonfinite) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
 
-  lists[warp][lane] = held;
-  __syncthreads();
-  if (warp != 0) return;
-  // Warp 0 folds the other warps' lists into its own; each is sorted, so a list is done at its
-  // first key that does not enter.
-  for (int other = 1; other < kWarps; ++other) {
-    const uint64_t cand = lists[other][lane];
-    offer(held, kth, cand, cand > kth, lane, top_k);
+  // The CTA's eight lists fold into warp 0's as a tree of merges through shared memory.
+  auto fold_warps = [&]() {
+#pragma unroll
+    for (int half = kWarps / 2; half > 0; half >>= 1) {
+      if (warp >= half && warp < 2 * half) lists[warp][lane] = held;
+      __syncthreads();
+      if (warp < half) held = merge_descending(held, lists[warp + half][lane], lane);
+      __syncthreads();
+    }
+  };
+  fold_warps();
+  if (warp == 0) {
+    row_scratch[slice * kList + lane] = held;
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) is_last = atomicAdd(ticket, 1u) == static_cast<unsigned int>(slices - 1);
   }
-  row_scratch[slice * kList + lane] = held;
-  __threadfence();
-  __syncwarp();
-  if (lane == 0) is_last = atomicAdd(ticket, 1u) == static_cast<unsigned int>(slices - 1);
-  __syncwarp();
+  __syncthreads();
   if (!is_last) return;
   __threadfence();
 
-  // The row's last CTA: merge every slice's list (its own included, already in `held`).
-  for (int s = 0; s < slices; ++s) {
-    if (s == slice) continue;
-    const uint64_t cand = *reinterpret_cast<volatile uint64_t*>(row_scratch + s * kList + lane);
-    offer(held, kth, cand, cand > kth, lane, top_k);
+  // The row's last CTA: every warp merges its share of the slices' lists, then the same tree.
+  held = 0;
+  for (int s = warp; s < slices; s += kWarps) {
+    const uint64_t other = *reinterpret_cast<volatile uint64_t*>(row_scratch + s * kList + lane);
+    held = merge_descending(held, other, lane);
   }
+  fold_warps();
+  if (warp != 0) return;
   if (lane == 0) *ticket = 0;  // ready for the next launch
 
   if (p.top_out != nullptr && lane < top_k) {
@@ -134,22 +234,20 @@ __global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams p) {
   uint32_t token = key_index(shfl64(held, 0));
   if (!(temperature == 0.0f || top_k == 1)) {
     // sampling.rs:175-210, evaluated by every lane on the same values.
+    // Lane i evaluates the weight of survivor i (the exponentials run side by side); the sums
+    // below then walk the lanes in the reference's order.
     const float maximum = key_value(shfl64(held, 0));
-    double weights[kList];
+    const float scaled = __fdiv_rn(key_value(held) - maximum, temperature);
+    const double my_weight = lane < top_k ? softmax_weight(scaled) : 0.0;
     double total = 0.0;
 #pragma unroll 1
-    for (int i = 0; i < top_k; ++i) {
-      const float v = key_value(shfl64(held, i));
-      const float scaled = __fdiv_rn(v - maximum, temperature);
-      weights[i] = static_cast<double>(static_cast<float>(exp(static_cast<double>(scaled))));
-      total += weights[i];
-    }
+    for (int i = 0; i < top_k; ++i) total += __shfl_sync(0xffffffffu, my_weight, i);
     const double cutoff = static_cast<double>(fmaxf(p.top_p[row], 1.17549435e-38f)) * total;
     double retained_total = 0.0;
     int retained = 0;
 #pragma unroll 1
     for (int i = 0; i < top_k; ++i) {
-      retained_total += weights[i];
+      retained_total += __shfl_sync(0xffffffffu, my_weight, i);
       ++retained;
       if (retained_total >= cutoff) break;
     }
@@ -164,7 +262,7 @@ __global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams p) {
     int chosen = retained - 1;
 #pragma unroll 1
     for (int i = 0; i < retained; ++i) {
-      cumulative += weights[i];
+      cumulative += __shfl_sync(0xffffffffu, my_weight, i);
       if (cumulative >= threshold) {
         chosen = i;
         break;
@@ -183,8 +281,8 @@ __global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams p) {
 }  // namespace
 
 int sampler_slices(int vocab) {
-  // About 2000 values per warp: 16 slices at the 248 320-wide vocabulary, fewer for small rows.
-  int slices = (vocab + 8 * 2048 - 1) / (8 * 2048);
+  // About 1000 values per warp: 31 slices at the 248 320-wide vocabulary, fewer for small rows.
+  int slices = (vocab + 8 * 1024 - 1) / (8 * 1024);
   return slices < 1 ? 1 : slices > 32 ? 32 : slices;
 }
 
