@@ -216,9 +216,16 @@ __global__ void __launch_bounds__(kThreads, 1) sampler_kernel(SamplerParams p) {
 
   // The row's last CTA: every warp merges its share of the slices' lists, then the same tree.
   held = 0;
-  for (int s = warp; s < slices; s += kWarps) {
-    const uint64_t other = *reinterpret_cast<volatile uint64_t*>(row_scratch + s * kList + lane);
-    held = merge_descending(held, other, lane);
+  {
+    // at most 32 slices: four lists per warp, all requested before the first merge
+    uint64_t other[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int s = warp + i * kWarps;
+      other[i] = s < slices ? *reinterpret_cast<volatile uint64_t*>(row_scratch + s * kList + lane) : 0ull;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) held = merge_descending(held, other[i], lane);
   }
   fold_warps();
   if (warp != 0) return;
@@ -239,18 +246,20 @@ __global__ void __launch_bounds__(kThreads, 1) sampler_kernel(SamplerParams p) {
     const float maximum = key_value(shfl64(held, 0));
     const float scaled = __fdiv_rn(key_value(held) - maximum, temperature);
     const double my_weight = lane < top_k ? softmax_weight(scaled) : 0.0;
-    double total = 0.0;
-#pragma unroll 1
-    for (int i = 0; i < top_k; ++i) total += __shfl_sync(0xffffffffu, my_weight, i);
-    const double cutoff = static_cast<double>(fmaxf(p.top_p[row], 1.17549435e-38f)) * total;
-    double retained_total = 0.0;
-    int retained = 0;
+    // Lane i ends with the running sum over survivors 0..i, added in survivor order (the
+    // reference's three loops walk this same sequence).
+    double running = 0.0;
 #pragma unroll 1
     for (int i = 0; i < top_k; ++i) {
-      retained_total += __shfl_sync(0xffffffffu, my_weight, i);
-      ++retained;
-      if (retained_total >= cutoff) break;
+      const double w = __shfl_sync(0xffffffffu, my_weight, i);
+      if (i <= lane) running += w;
     }
+    const double total = __shfl_sync(0xffffffffu, running, top_k - 1);
+    const double cutoff = static_cast<double>(fmaxf(p.top_p[row], 1.17549435e-38f)) * total;
+    // first survivor whose running sum reaches the cut-off (all of them if none does)
+    int retained = __popc(__ballot_sync(0xffffffffu, lane < top_k && !(running >= cutoff))) + 1;
+    retained = retained > top_k ? top_k : retained;
+    const double retained_total = __shfl_sync(0xffffffffu, running, retained - 1);
     // xorshift64 (sampling.rs:244-260); the state advances once per sampled token.
     uint64_t state = p.rng_state[row];
     state ^= state << 13;
@@ -258,16 +267,8 @@ __global__ void __launch_bounds__(kThreads, 1) sampler_kernel(SamplerParams p) {
     state ^= state << 17;
     const double unit = static_cast<double>(state >> 11) * (1.0 / 9007199254740992.0);
     const double threshold = unit * retained_total;
-    double cumulative = 0.0;
-    int chosen = retained - 1;
-#pragma unroll 1
-    for (int i = 0; i < retained; ++i) {
-      cumulative += __shfl_sync(0xffffffffu, my_weight, i);
-      if (cumulative >= threshold) {
-        chosen = i;
-        break;
-      }
-    }
+    int chosen = __popc(__ballot_sync(0xffffffffu, lane < retained && !(running >= threshold)));
+    chosen = chosen >= retained ? retained - 1 : chosen;
     token = key_index(shfl64(held, chosen));
     if (lane == 0) p.rng_state[row] = state;
     if (!(retained_total > 0.0) || isinf(retained_total)) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
