@@ -285,6 +285,61 @@ def cpu_norm_quant(rows: int, gpu_us: float):
                       + ("" if sample == rows else "; extrapolated")}
 
 
+def cpu_gdn(which: str, batch: int, gpu_us: float):
+    """FP64 oracle (numpy, one thread) of one gated-delta-net decode step on the same shapes."""
+    import numpy as np
+
+    from oracle import gdn_oracle as G
+    from tuiskollm_b200 import synth
+
+    rows = np.arange(batch, dtype=np.uint32)
+    proj = synth.normal_bf16(SEED, 404, (batch, G.INPUT_ROWS))
+    if which == "prepare":
+        x = synth.normal_bf16(SEED, 400, (batch, HIDDEN))
+        cw = synth.normal_bf16(SEED, 401, (2 * G.CONTROL_ROWS, HIDDEN), std=0.02)
+        a_log, dt_bias = synth.normal_bf16(SEED, 402, (G.CONTROL_ROWS,)), synth.normal_bf16(SEED, 403, (G.CONTROL_ROWS,))
+        convw = synth.normal_bf16(SEED, 405, (G.QKV_ROWS, 4), std=0.5)
+        hist = synth.normal_bf16(SEED, 406, (batch, G.QKV_ROWS, 3))
+
+        def fn():
+            G.gdn_controls(x, cw, a_log, dt_bias)
+            G.gdn_convolution(proj, convw, rows, hist)
+    else:
+        qkv = synth.normal_bf16(SEED, 409, (batch, G.QKV_ROWS))
+        norm = synth.normal_bf16(SEED, 408, (G.HEAD_DIM,))
+        decay = -np.abs(np.random.default_rng(SEED).normal(0.5, 0.2, (batch, G.VALUE_HEADS))).astype(np.float32)
+        beta = np.full((batch, G.VALUE_HEADS), 0.5, dtype=np.float32)
+        state = np.zeros((batch, G.VALUE_HEADS, G.HEAD_DIM, G.HEAD_DIM), dtype=np.float32)
+
+        def fn():
+            G.gdn_recurrence(qkv, proj, decay, beta, norm, rows, state)
+
+    dt = cpu_time(fn, 0.4)
+    return {"value": dt * 1e6, "unit": "us per step", "cores": 1, "kind": "port",
+            "us_full_shape": dt * 1e6, "gpu_speedup": dt * 1e6 / gpu_us,
+            "sample": f"GDN {which}, batch {batch}: the FP64 formulas of the reference's qualification in numpy"}
+
+
+def cpu_sampler(batch: int, vocab: int, gpu_us: float):
+    """The C oracle of the host sampler (top-k 20, top-p 0.95) on `batch` full-vocabulary rows,
+    one thread -- what the reference's engine does per token after copying the row to the host."""
+    from oracle import tuisko_oracle as O
+    from tuiskollm_b200 import synth
+
+    rows = [synth.normal_bf16(SEED, 500 + i, (vocab,), std=3.0) for i in range(batch)]
+    samplers = [O.Sampler(1.0, 0.95, 20, i, (1, 2)) for i in range(batch)]
+
+    def fn():
+        for sampler, row in zip(samplers, rows):
+            sampler.sample(row)
+
+    dt = cpu_time(fn, 0.4)
+    return {"value": dt * 1e6, "unit": "us per batch", "cores": 1, "kind": "port",
+            "us_full_shape": dt * 1e6, "gpu_speedup": dt * 1e6 / gpu_us,
+            "sample": f"{batch} rows x {vocab} BF16 logits: top-k select, softmax weights, top-p, xorshift64 draw "
+                      "(the host copy of the rows is not included)"}
+
+
 def cpu_nvfp4(rows: int, out_rows: int, k: int, gate_up: bool, gpu_us: float):
     """Oracle port of one NVFP4 projection on a stratified sample (64 tokens x 512 weight rows),
     reported per output element and extrapolated to the full shape, labelled as such."""
@@ -679,7 +734,7 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
             case = f"{nm}:B{b}"
             proto.add(case, graph.replay, groups)
             meta[case] = {"config": "next", "op": nm, "M": b, "kernel": nm + "_kernel", "kind": "hbm",
-                          "bytes": by, "cpu": None}
+                          "bytes": by, "cpu": ("gdn", nm.split("_")[1], b)}
             keep.append(graph)
     keep.append((g_x, g_cw, g_alog, g_dt, g_proj, g_convw, g_hist, g_state, g_norm, g_decay, g_beta,
                  g_conv, g_out))
@@ -702,7 +757,7 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
         case = f"device_sampler:B{b}"
         proto.add(case, graph.replay, copies_s)
         meta[case] = {"config": "next", "op": "device_sampler_top20_p95", "M": b, "kernel": "sampler_kernel",
-                      "kind": "hbm", "bytes": b * vocab_s * 2 + b * 16, "cpu": None}
+                      "kind": "hbm", "bytes": b * vocab_s * 2 + b * 16, "cpu": ("sampler", b, vocab_s)}
         keep.append((graph, rows_s, samp))
     mat = tk.Materializer(ctx)
     sc_src = [torch.randint(0, 0x7F, (inter, HIDDEN // 16), dtype=torch.uint8, device=dev) for _ in range(2)]
@@ -930,6 +985,10 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
                     row["cpu_baseline"] = cpu_norm_quant(c[1], us)
                 elif c[0] == "nvfp4":
                     row["cpu_baseline"] = cpu_nvfp4(c[1], c[2], c[3], c[4], us)
+                elif c[0] == "gdn":
+                    row["cpu_baseline"] = cpu_gdn(c[1], c[2], us)
+                elif c[0] == "sampler":
+                    row["cpu_baseline"] = cpu_sampler(c[1], c[2], us)
                 elif c[0] == "slice":
                     row["cpu_baseline"] = None  # filled below from the operators' own rows
             except Exception as exc:  # the row stays, the baseline says why it is absent
