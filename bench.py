@@ -1435,6 +1435,24 @@ def run_native(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def meet():
+        """barrier + synchronize, after which all ranks leave at the same instant of the host's
+        monotonic clock (one box, one clock): rank 0 names an instant 2 ms ahead before the
+        barrier and everybody spins up to it.  Without this the ranks leave the barrier tens of
+        microseconds apart and a short timed region measures that scatter in its first exchange."""
+        if world == 1:
+            torch.cuda.synchronize()
+            return
+        when = torch.zeros(1, dtype=torch.int64, device=dev)
+        if rank == 0:
+            when[0] = time.monotonic_ns() + 2_000_000
+        dist.broadcast(when, 0)
+        dist.barrier()
+        torch.cuda.synchronize()
+        target = int(when.item())
+        while time.monotonic_ns() < target:
+            pass
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -1465,6 +1483,7 @@ def run_native(args):
     barrier()
     first_clock_sample = sampler.mark()
     launches0 = ctx.launch_count
+    meet()
     ms = time_region(torch, run_step, args.steps)
     launches = (launches_per_step * args.steps if launches_per_step is not None
                 else ctx.launch_count - launches0)
@@ -1478,8 +1497,7 @@ def run_native(args):
     inner = max(1, min(256, int(0.5e3 / SAMPLES / max(float(ms_all.item()) / args.steps, 1e-3)) + 1))
     sample_us = []
     for _ in range(SAMPLES):
-        if world > 1:
-            dist.barrier()
+        meet()
         sample_us.append(time_region(torch, run_step, inner) * 1e3 / inner)
     st = torch.tensor(sample_us, dtype=torch.float64, device=dev)
     if world > 1:
@@ -1498,14 +1516,14 @@ def run_native(args):
             torch.cuda.synchronize()
     for _ in range(3):
         run_e2e()
-    barrier()
+    meet()
     ms_e2e = time_region(torch, run_e2e, args.steps, sync_each=True)
     barrier()
     # ... and without a graph: every operator call made from the host, per step (C-ABI cost)
     for _ in range(3):
         step_e2e()
         torch.cuda.synchronize()
-    barrier()
+    meet()
     ms_e2e_eager = time_region(torch, step_e2e, args.steps, sync_each=True)
     barrier()
     for _ in range(3):
