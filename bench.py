@@ -724,21 +724,19 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
                           g_state, g_out)
             st["r"] += 1
 
-        def step(b=b, rows=rows, st=st, groups=groups, warm=False):
+        def step(b=b, rows=rows, st=st, groups=groups):
             # one decode step: prepare, then the recurrence on the same slots
             r = rows[st["s"] % groups]
             st["s"] += 1
-            prep_op.launch(None, b, g_x, g_cw, g_alog, g_dt, g_proj, g_convw, r, g_hist, g_decay, g_beta,
-                           g_conv, warm_state=g_state if warm else None)
+            prep_op.launch(None, b, g_x, g_cw, g_alog, g_dt, g_proj, g_convw, r, g_hist, g_decay, g_beta, g_conv)
             rec_op.launch(None, b, g_conv, g_proj, g_decay, g_beta, g_norm, r, g_state, g_out)
 
         st["s"] = 0
         state_bytes = b * (2 * 48 * 128 * 128 * 4 + 2 * (qkv_rows + 2 * 6144) + 2 * 48 * 4)
         prep_bytes = 2 * 96 * HIDDEN + b * (2 * HIDDEN + qkv_rows * (2 + 6 + 6 + 2) + 2 * 48 * 4) + 8 * qkv_rows
-        for nm, warm in (("gdn_step", False), ("gdn_step_state_hint", True)):
-            fn2 = (lambda warm=warm, step=step: step(warm=warm))
-            fn2()
-            graph = capture(torch, fn2, groups)
+        for nm in ("gdn_step",):
+            step()
+            graph = capture(torch, step, groups)
             case = f"{nm}:B{b}"
             proto.add(case, graph.replay, groups)
             meta[case] = {"config": "next", "op": nm, "M": b, "kernel": "gdn_prepare_kernel + gdn_recurrence_kernel",

@@ -150,13 +150,6 @@ unsafe extern "C" {
         projected: *const u16, convolution_weights: *const u16, state_rows: *const u32,
         history: *mut u16, log_decay: *mut f32, beta: *mut f32, convolved: *mut u16,
     ) -> Tk100Status;
-    pub fn tk100_gdn_prepare_warm(
-        ctx: *mut Tk100Ctx, stream: Tk100Stream, batch: c_int, input: *const u16,
-        control_weights: *const u16, a_log: *const u16, dt_bias: *const u16,
-        projected: *const u16, convolution_weights: *const u16, state_rows: *const u32,
-        history: *mut u16, log_decay: *mut f32, beta: *mut f32, convolved: *mut u16,
-        state: *const f32,
-    ) -> Tk100Status;
     pub fn tk100_gdn_recurrence(
         ctx: *mut Tk100Ctx, stream: Tk100Stream, batch: c_int, qkv: *const u16,
         projected: *const u16, log_decay: *const f32, beta: *const f32, norm_weight: *const u16,

@@ -376,26 +376,6 @@ impl<A: Sm100Arch> GdnPrepareOp<A> {
     }
 }
 
-impl<A: Sm100Arch> GdnPrepareOp<A> {
-    /// [`GdnPrepareOp::launch`] plus a hint: the slots of `state` that the following recurrence
-    /// updates are queued at L2 while this kernel runs (`tk100_gdn_prepare_warm`).
-    #[allow(clippy::too_many_arguments)]
-    pub unsafe fn launch_warm(
-        &self, stream: &CudaStream, batch: usize, input: *const u16, control_weights: *const u16,
-        a_log: *const u16, dt_bias: *const u16, projected: *const u16,
-        convolution_weights: *const u16, state_rows: *const u32, history: *mut u16,
-        log_decay: *mut f32, beta: *mut f32, convolved: *mut u16, state: *const f32,
-    ) -> GpuResult<()> {
-        self.ctx.check(unsafe {
-            ffi::tk100_gdn_prepare_warm(
-                self.ctx.raw, stream.cu_stream().cast(), rows_i32(batch), input, control_weights,
-                a_log, dt_bias, projected, convolution_weights, state_rows, history, log_decay,
-                beta, convolved, state,
-            )
-        })
-    }
-}
-
 /// `GdnRecurrenceOp` (`tuisko-kernels-sm120/src/gdn/recurrence.rs:137-236`).
 pub struct GdnRecurrenceOp<A: Sm100Arch = Qwen38_27B> {
     ctx: Arc<Sm100Context>,

@@ -269,19 +269,6 @@ TK100_API tk100_status tk100_gdn_prepare(tk100_ctx* ctx, tk100_stream stream, in
                                          const uint32_t* state_rows, uint16_t* history,
                                          float* log_decay, float* beta, uint16_t* convolved);
 
-/* tk100_gdn_prepare plus a hint: `state` is the FP32 recurrent state the tk100_gdn_recurrence call
- * that follows will update; the slots `state_rows[0..batch)` (3.1 MB each) are queued at L2 while
- * this latency-bound kernel runs, so the recurrence finds them there.  Results are those of
- * tk100_gdn_prepare; `state` is not read or written by this call.  No reference counterpart. */
-TK100_API tk100_status tk100_gdn_prepare_warm(tk100_ctx* ctx, tk100_stream stream, int batch,
-                                              const uint16_t* input, const uint16_t* control_weights,
-                                              const uint16_t* a_log, const uint16_t* dt_bias,
-                                              const uint16_t* projected,
-                                              const uint16_t* convolution_weights,
-                                              const uint32_t* state_rows, uint16_t* history,
-                                              float* log_decay, float* beta, uint16_t* convolved,
-                                              const float* state);
-
 /* GdnRecurrenceOp::launch (tuisko-kernels-sm120/src/gdn/recurrence.rs:184-236): gated delta
  * rule on the FP32 state `[state rows, 48, 128, 128]` (updated in place at
  * `state_rows[token]`), then RMSNorm over each head's 128 outputs times `norm_weight`, times

@@ -232,23 +232,3 @@ def test_batch_outside_the_admitted_range_is_refused(tk, ctx):
         with pytest.raises(tk.GpuError, match="outside the admitted range"):
             prep.launch(tk.GdnPrepareOp(ctx), batch)
 
-
-def test_prepare_with_state_hint_gives_the_same_results(tk, ctx):
-    """tk100_gdn_prepare_warm only queues the following recurrence's state slots at L2: controls,
-    convolution, history and the state itself are bit for bit those of the plain call."""
-    f = F.gdn_prepare_fixture()
-    r = F.gdn_recurrence_fixture()
-    plain, warm = PreparePlanes(f), PreparePlanes(f)
-    state = dev(r["state"])
-    op = tk.GdnPrepareOp(ctx)
-    for batch in (1, 5, 8):
-        plain.reset()
-        warm.reset()
-        plain.launch(op, batch)
-        op.launch(None, batch, warm.input, warm.control_weights, warm.a_log, warm.dt_bias, warm.projected,
-                  warm.convolution_weights, warm.state_rows, warm.history, warm.log_decay, warm.beta,
-                  warm.convolved, warm_state=state)
-        for a, b in zip(plain.observe(), warm.observe()):
-            assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
-        assert np.array_equal(host(state), r["state"])
-    assert ctx.device_status(None) == 0

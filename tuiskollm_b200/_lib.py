@@ -67,7 +67,6 @@ SIGNATURES = {
     "tk100_sampler_initial_state": (C.c_uint64, [C.c_uint64]),
     "tk100_sampler_scratch_bytes": (C.c_size_t, [_i, _i]),
     "tk100_gdn_prepare": (_i, [_vp, _vp, _i] + [_vp] * 11),
-    "tk100_gdn_prepare_warm": (_i, [_vp, _vp, _i] + [_vp] * 12),
     "tk100_gdn_recurrence": (_i, [_vp, _vp, _i] + [_vp] * 8),
     "tk100_fp8_lm_head": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tk100_fp8_lm_head_sharded": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

@@ -145,19 +145,6 @@ __global__ void __launch_bounds__(kPrepThreads) gdn_prepare_kernel(GdnPreparePar
   const int token = index / groups;
   const int channel = (index - token * groups) * 8;
   const size_t state_row = p.state_rows[token];
-  if (p.warm_state != nullptr) {
-    // The recurrence that follows reads this token's 3.1 MB of state: ask L2 for it now, in
-    // 16 KB pieces, so that HBM works while this latency-bound kernel and the next one's ramp
-    // run.  A hint only: nothing here depends on it.
-    constexpr size_t kStateBytes = static_cast<size_t>(48) * 128 * 128 * sizeof(float);
-    constexpr size_t kPiece = 16384;
-    const size_t piece = static_cast<size_t>(index - token * groups);
-    if (piece < kStateBytes / kPiece) {
-      bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.warm_state) + state_row * kStateBytes +
-                           piece * kPiece,
-                       static_cast<uint32_t>(kPiece));
-    }
-  }
   uint16_t* hist = p.history + (state_row * p.qkv_rows + channel) * 3;  // 48 bytes, 16-aligned
   const uint4 cur4 = ldg16(p.projected + static_cast<size_t>(token) * p.input_rows + channel);
   const uint4 h4[3] = {*reinterpret_cast<const uint4*>(hist), *reinterpret_cast<const uint4*>(hist + 8),

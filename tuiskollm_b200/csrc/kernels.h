@@ -114,7 +114,6 @@ struct GdnPrepareParams {
   float* log_decay;                     // [batch, control_rows]
   float* beta;                          // [batch, control_rows]
   uint16_t* convolved;                  // [batch, qkv_rows] BF16
-  const float* warm_state;              // optional: recurrent state whose slots are queued at L2
 };
 struct GdnRecurrenceParams {
   int batch;

@@ -456,7 +456,7 @@ Status GdnPrepareOp::launch(cudaStream_t stream, int batch, const uint16_t* inpu
                             const uint16_t* dt_bias, const uint16_t* projected,
                             const uint16_t* convolution_weights, const uint32_t* state_rows,
                             uint16_t* history, float* log_decay, float* beta,
-                            uint16_t* convolved, const float* warm_state) {
+                            uint16_t* convolved) {
   const char* what = "GDN prepare";
   TK100_TRY(check_gdn_batch(ctx_, what, batch));
   TK100_TRY(check_plane(ctx_, what, "input", input, 16));
@@ -487,8 +487,6 @@ Status GdnPrepareOp::launch(cudaStream_t stream, int batch, const uint16_t* inpu
   p.log_decay = log_decay;
   p.beta = beta;
   p.convolved = convolved;
-  if (warm_state != nullptr) TK100_TRY(check_plane(ctx_, what, "state", warm_state, 16));
-  p.warm_state = warm_state;
   ctx_.count_launch();
   return ctx_.check(launch_gdn_prepare(stream, p), "launching GDN prepare");
 }
@@ -1371,18 +1369,6 @@ tk100_status tk100_gdn_prepare(tk100_ctx* ctx, tk100_stream stream, int batch,
   return tk100::GdnPrepareOp(*ctx->impl)
       .launch(static_cast<cudaStream_t>(stream), batch, input, control_weights, a_log, dt_bias,
               projected, convolution_weights, state_rows, history, log_decay, beta, convolved);
-}
-
-tk100_status tk100_gdn_prepare_warm(tk100_ctx* ctx, tk100_stream stream, int batch,
-                                    const uint16_t* input, const uint16_t* control_weights,
-                                    const uint16_t* a_log, const uint16_t* dt_bias,
-                                    const uint16_t* projected, const uint16_t* convolution_weights,
-                                    const uint32_t* state_rows, uint16_t* history, float* log_decay,
-                                    float* beta, uint16_t* convolved, const float* state) {
-  if (!ctx) return TK100_ERR_CONTEXT;
-  return tk100::GdnPrepareOp(*ctx->impl)
-      .launch(static_cast<cudaStream_t>(stream), batch, input, control_weights, a_log, dt_bias,
-              projected, convolution_weights, state_rows, history, log_decay, beta, convolved, state);
 }
 
 tk100_status tk100_gdn_recurrence(tk100_ctx* ctx, tk100_stream stream, int batch,

@@ -202,7 +202,7 @@ class GdnPrepareOp {
                 const uint16_t* control_weights, const uint16_t* a_log, const uint16_t* dt_bias,
                 const uint16_t* projected, const uint16_t* convolution_weights,
                 const uint32_t* state_rows, uint16_t* history, float* log_decay, float* beta,
-                uint16_t* convolved, const float* warm_state = nullptr);
+                uint16_t* convolved);
 
  private:
   Context& ctx_;

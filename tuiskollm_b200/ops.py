@@ -338,17 +338,12 @@ class GdnPrepareOp:
         self.ctx = context
 
     def launch(self, stream, batch, input, control_weights, a_log, dt_bias, projected,
-               convolution_weights, state_rows, history, log_decay, beta, convolved, warm_state=None):
-        """``warm_state``: the recurrent state the following recurrence will update; its slots are
-        queued at L2 meanwhile (tk100_gdn_prepare_warm)."""
+               convolution_weights, state_rows, history, log_decay, beta, convolved):
         c = self.ctx
-        args = (c.handle, _stream(stream), batch, _ptr(input), _ptr(control_weights), _ptr(a_log),
-                _ptr(dt_bias), _ptr(projected), _ptr(convolution_weights), _ptr(state_rows),
-                _ptr(history), _ptr(log_decay), _ptr(beta), _ptr(convolved))
-        if warm_state is None:
-            c.check(c._lib.tk100_gdn_prepare(*args))
-        else:
-            c.check(c._lib.tk100_gdn_prepare_warm(*args, _ptr(warm_state)))
+        c.check(c._lib.tk100_gdn_prepare(
+            c.handle, _stream(stream), batch, _ptr(input), _ptr(control_weights), _ptr(a_log),
+            _ptr(dt_bias), _ptr(projected), _ptr(convolution_weights), _ptr(state_rows),
+            _ptr(history), _ptr(log_decay), _ptr(beta), _ptr(convolved)))
 
 
 class GdnRecurrenceOp:
