@@ -21,13 +21,14 @@ __global__ void __launch_bounds__(128, 1) bench_kernel(long long* cycles, uint32
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar2;
   __shared__ uint32_t tmem_base;
   // [W 16 KB][A N*128 B][SF 8 KB]
   for (int i = threadIdx.x; i < (16384 + N * 128 + 8192) / 4; i += blockDim.x)
     reinterpret_cast<uint32_t*>(smem)[i] = 0x38383838u;  // finite codes / scales
   if (threadIdx.x == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar2, 1);
     fence_mbar_init();
   }
   fence_proxy_async_smem();
@@ -59,7 +60,7 @@ __global__ void __launch_bounds__(128, 1) bench_kernel(long long* cycles, uint32
       }
       for (int k4 = 0; k4 < 4; ++k4) {
         const uint32_t slot = sf_base + ((it + k4) % 8) * 16;
-        if (MODE == 1) {  // interleaved
+        if (MODE == 1 || MODE == 5) {  // interleaved
           tmem_cp_32x128b_warpx4(slot, umma_desc_noswizzle_rows16(sfsm + k4 * 512));
           tmem_cp_32x128b_warpx4(slot + 8, umma_desc_noswizzle_rows16(sfsm + 2048 + k4 * 512));
           if (N == 256)
@@ -78,6 +79,9 @@ __global__ void __launch_bounds__(128, 1) bench_kernel(long long* cycles, uint32
           umma_nvfp4(tmem, dw + 2 * k4, da + 2 * k4, IDESC, slot, slot + 8, 1u);
         }
       }
+      // MODE 5 / 6: a commit after every 256-deep block, as a mainloop that frees a ring stage does
+      // (it arrives on a barrier nobody waits for)
+      if (MODE == 5 || MODE == 6) umma_commit(&bar2);
     }
     umma_commit(&bar);
     mbar_wait(&bar, 0, status);
@@ -99,7 +103,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar2;
   __shared__ uint32_t tmem_base;
   const uint32_t rank = cluster_cta_rank();
   // kPairStages x ([W 16 KB][A 16 KB (128 tokens)][SF 8 KB]); PMODE >= 3 walks the stages like a
@@ -109,6 +113,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
     reinterpret_cast<uint32_t*>(smem)[i] = 0x38383838u;
   if (threadIdx.x == 0) {
     mbar_init(&bar, 1);
+    mbar_init(&bar2, 1);
     fence_mbar_init();
   }
   fence_proxy_async_smem();
@@ -134,7 +139,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
       const uint64_t da = umma_desc_sw128(base + 16384);
       const uint32_t sfsm = base + 32768;
       const uint32_t slot = sf_base + (it % 8) * 16;
-      if ((PMODE == 1 || PMODE == 4) && rank == 0) {
+      if ((PMODE == 1 || PMODE == 4 || PMODE == 5) && rank == 0) {
         tmem_cp_32x128b_warpx4_pair(slot, umma_desc_noswizzle_rows16(sfsm + k4 * 512));
         tmem_cp_32x128b_warpx4_pair(slot + 4, umma_desc_noswizzle_rows16(sfsm + 2048 + k4 * 512));
         tmem_cp_32x128b_warpx4_pair(slot + 8, umma_desc_noswizzle_rows16(sfsm + 4096 + k4 * 512));
@@ -145,6 +150,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
         tmem_cp_32x128b_warpx4(slot + 8, umma_desc_noswizzle_rows16(sfsm + 4096 + k4 * 512));
       }
       if (rank == 0) umma_nvfp4_pair(tmem, dw + 2 * k4, da + 2 * k4, IDESC, slot, slot + 4, 1u);
+      // PMODE 5 / 6: a commit (to both CTAs) after every 256-deep block
+      if ((PMODE == 5 || PMODE == 6) && rank == 0 && k4 == 3) umma_commit_pair(&bar2);
     }
     if (rank == 0) {
       umma_commit_pair(&bar);
@@ -233,5 +240,9 @@ int main() {
   run_pair<2>("pair: 3 cp.cg1 per CTA + mma.cg2", d_cycles, d_status);
   run_pair<3>("pair: mma only, ring of 4 stages", d_cycles, d_status);
   run_pair<4>("pair: 3 cp.cg2 + mma, ring", d_cycles, d_status);
+  run<128, 6>("mma only + commit per 4", d_cycles, d_status);
+  run<128, 5>("interleaved + commit per 4", d_cycles, d_status);
+  run_pair<6>("pair: mma only, ring, commit per 4", d_cycles, d_status);
+  run_pair<5>("pair: 3 cp + mma, ring, commit/4", d_cycles, d_status);
   return 0;
 }
