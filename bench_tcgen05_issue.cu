@@ -95,6 +95,8 @@ __global__ void __launch_bounds__(128, 1) bench_kernel(long long* cycles, uint32
 // CTA pairs (tcgen05 cta_group::2, M = 256, N = 256): the even CTA issues the MMAs for both.
 //   PMODE 0: MMA only.
 //   PMODE 1: per K step three cta_group::2 scale copies (SFA, two SFB tiles), then the MMA.
+//   PMODE 5 / 6: PMODE 4 / 3 plus one commit (to both CTAs) after every 256-deep block.
+//   PMODE 7: PMODE 2 on the ring, with the leader's commit per block and the odd CTA's own.
 //   PMODE 2: every CTA issues its own three copies with cta_group::1 (the odd CTA's run beside
 //            the even CTA's MMAs, unsynchronised: rate only), the even CTA the cta_group::2 MMA.
 template <int PMODE>
@@ -103,7 +105,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  __shared__ uint64_t bar, bar2;
+  __shared__ uint64_t bar, bar2, bar3;
   __shared__ uint32_t tmem_base;
   const uint32_t rank = cluster_cta_rank();
   // kPairStages x ([W 16 KB][A 16 KB (128 tokens)][SF 8 KB]); PMODE >= 3 walks the stages like a
@@ -114,6 +116,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
   if (threadIdx.x == 0) {
     mbar_init(&bar, 1);
     mbar_init(&bar2, 1);
+    mbar_init(&bar3, 1);
     fence_mbar_init();
   }
   fence_proxy_async_smem();
@@ -144,21 +147,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
         tmem_cp_32x128b_warpx4_pair(slot + 4, umma_desc_noswizzle_rows16(sfsm + 2048 + k4 * 512));
         tmem_cp_32x128b_warpx4_pair(slot + 8, umma_desc_noswizzle_rows16(sfsm + 4096 + k4 * 512));
       }
-      if (PMODE == 2) {
+      if (PMODE == 2 || PMODE == 7) {
         tmem_cp_32x128b_warpx4(slot, umma_desc_noswizzle_rows16(sfsm + k4 * 512));
         tmem_cp_32x128b_warpx4(slot + 4, umma_desc_noswizzle_rows16(sfsm + 2048 + k4 * 512));
         tmem_cp_32x128b_warpx4(slot + 8, umma_desc_noswizzle_rows16(sfsm + 4096 + k4 * 512));
       }
       if (rank == 0) umma_nvfp4_pair(tmem, dw + 2 * k4, da + 2 * k4, IDESC, slot, slot + 4, 1u);
       // PMODE 5 / 6: a commit (to both CTAs) after every 256-deep block
-      if ((PMODE == 5 || PMODE == 6) && rank == 0 && k4 == 3) umma_commit_pair(&bar2);
+      if ((PMODE == 5 || PMODE == 6 || PMODE == 7) && rank == 0 && k4 == 3) umma_commit_pair(&bar2);
+      // PMODE 7: the odd CTA reports its own copies of the block on a barrier of its own
+      if (PMODE == 7 && rank == 1 && k4 == 3) umma_commit(&bar3);
     }
     if (rank == 0) {
       umma_commit_pair(&bar);
-    } else if (PMODE == 2) {
+    } else if (PMODE == 2 || PMODE == 7) {
       umma_commit(&bar);  // the odd CTA's own copies
     }
-    if (rank == 0 || PMODE == 2) mbar_wait(&bar, 0, status);
+    if (rank == 0 || PMODE == 2 || PMODE == 7) mbar_wait(&bar, 0, status);
     else mbar_wait(&bar, 0, status);  // the even CTA's commit arrives here too
     const long long t1 = clock64();
     cycles[blockIdx.x] = t1 - t0;
@@ -244,5 +249,6 @@ int main() {
   run<128, 5>("interleaved + commit per 4", d_cycles, d_status);
   run_pair<6>("pair: mma only, ring, commit per 4", d_cycles, d_status);
   run_pair<5>("pair: 3 cp + mma, ring, commit/4", d_cycles, d_status);
+  run_pair<7>("pair: own cg1 cps, ring, commit/4", d_cycles, d_status);
   return 0;
 }
