@@ -637,3 +637,45 @@ def test_rejected_launches(tk, ctx):
                   input_global_divisor=0.0)
     assert "input scale divisor" in str(info.value)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("rows", [256, 300, 700])
+def test_wide_tile_route_matches_plain_route_bit_for_bit(tk, rows, monkeypatch):
+    """TK100_NVFP4_WIDE=2 runs prefill shapes on 256-token tiles (one CTA per SM, a second
+    activation scale tile per stage): same K order into one fp32 accumulator as the 128-token
+    tiles, so the same bits -- also with a ragged last tile whose second scale tile does not exist."""
+    from tuiskollm_b200 import synth
+
+    hidden, inter = 1024, 1536
+    xb = synth.normal_bf16(19, rows, (rows, hidden))
+    gu_codes, gu_scales, gu_div = synth.nvfp4_weights(19, 1, 2 * inter, hidden)
+    dn_codes, dn_scales, dn_div = synth.nvfp4_weights(19, 2, hidden, inter)
+    a_div, m_div = float(np.float32(448.0 * 6.0 / 5.0)), float(np.float32(448.0 * 6.0 / 8.0))
+    got = {}
+    for route, env in (("wide", "2"), ("plain", "0")):
+        monkeypatch.setenv("TK100_NVFP4_WIDE", env)
+        monkeypatch.setenv("TK100_NVFP4_WIDE_MIN_ROWS", "256")
+        c = tk.Context(device=0, hidden=hidden, intermediate=inter, max_rows=2048)
+        a_codes, a_scales = act_planes(tk, rows + 1, hidden)
+        m_codes, m_scales = act_planes(tk, rows + 1, inter)
+        mid = sentinel_plane((rows + 1, inter), torch.int16)
+        out = sentinel_plane((rows + 1, hidden), torch.int16)
+        tk.Nvfp4SwiGluOp(c).launch_quantize(None, rows, dev(xb.view(np.int16)), dev(gu_codes), dev(gu_scales),
+                                            float(gu_div), mid, activation_codes=a_codes,
+                                            activation_scales=a_scales, input_global_divisor=a_div,
+                                            output_global_divisor=m_div, output_codes=m_codes,
+                                            output_scales=m_scales)
+        r_gu = c.last_kernel
+        tk.Nvfp4DownOp(c).launch(None, rows, None, dev(dn_codes), dev(dn_scales), float(dn_div), out,
+                                 activation_codes=m_codes, activation_scales=m_scales,
+                                 input_global_divisor=m_div)
+        r_dn = c.last_kernel
+        torch.cuda.synchronize()
+        assert c.device_status() == 0, route
+        assert r_gu.startswith("nvfp4_gemm_kernel<256") == (route == "wide"), (route, r_gu)
+        assert r_dn.startswith("nvfp4_gemm_kernel<256") == (route == "wide"), (route, r_dn)
+        for pl in (mid, out):
+            assert_inactive_untouched(pl, rows)
+        got[route] = (_u16(mid)[:rows].copy(), _u16(out)[:rows].copy())
+    assert np.array_equal(got["wide"][0], got["plain"][0]), "gate/up + SwiGLU"
+    assert np.array_equal(got["wide"][1], got["plain"][1]), "down"

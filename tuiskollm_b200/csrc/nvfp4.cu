@@ -45,11 +45,14 @@ constexpr int kSfSlotCols = 16;      // columns per slot: SFA0 [0,4) SFA1 [4,8) 
 __host__ __device__ constexpr int nv_stages(int block_tok, bool gate_up) {
   // plain projection: 4 stages (98 KB) at <= 32 tokens and 3 stages (108 KB) at 128, so that
   // two CTAs share an SM (one runs its epilogue or split reduction under the other's loop)
-  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 4 : 3);
+  // 256-token tiles: 4 stages of 54 KB, one CTA per SM
+  return gate_up ? (block_tok <= 32 ? 5 : 4) : (block_tok <= 32 ? 4 : block_tok <= 128 ? 3 : 4);
 }
 
 __host__ __device__ constexpr int nv_stage_bytes(int block_tok, bool gate_up) {
-  return (gate_up ? 2 : 1) * (kWTile + kSfStage) + block_tok * kStageKBytes + kSfStage;
+  // activation scales: one 128-token scale tile per 128 tokens of the tile
+  return (gate_up ? 2 : 1) * (kWTile + kSfStage) + block_tok * kStageKBytes +
+         (block_tok > 128 ? 2 : 1) * kSfStage;
 }
 
 template <int STAGES, int BLOCK_TOK>
@@ -100,7 +103,7 @@ static __device__ __noinline__ uint32_t nvfp4_code_of_lane(uint32_t bf16_bits, f
 }
 
 template <int BLOCK_TOK, bool GATE_UP>
-__global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 2)
+__global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), (GATE_UP || BLOCK_TOK > 128) ? 1 : 2)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_a, const Nvfp4Params p) {
   constexpr int STAGES = nv_stages(BLOCK_TOK, GATE_UP);
@@ -187,10 +190,12 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
     // arrive as full boxes, zero-filled beyond the end of the row)
     const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
     const uint32_t code_bytes = NW * kWTile + BLOCK_TOK * kStageKBytes;
+    // a 256-token tile brings a second activation scale tile, when its tokens exist
+    const uint32_t sfb_tiles = (BLOCK_TOK > 128 && tok0 + kRows < p.rows) ? 2u : 1u;
     mbar_arrive_expect_tx(&ctl->full[s],
                           TK100_DBG(p, DBG_NO_ACT)
                               ? NW * (kWTile + sf_bytes)
-                              : code_bytes + (NW + 1) * sf_bytes);
+                              : code_bytes + (NW + sfb_tiles) * sf_bytes);
     tma_load_2d(stage, &tmap_w, &ctl->full[s], kbyte, w_tile * kRows, pol_w);
     bulk_load_1d(stage + OFF_SFA, sfa0 + sf_off, sf_bytes, &ctl->full[s], pol_w);
     if (GATE_UP) {
@@ -207,6 +212,11 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
     const uint32_t sf_bytes = static_cast<uint32_t>(min(4, (p.k - kb * kStageK) / 64)) * kSfChunk;
     bulk_load_1d(stage + OFF_SFB, sfb + static_cast<size_t>(kb) * kSfStage, sf_bytes,
                  &ctl->full[s], pol_a);
+    if (BLOCK_TOK > 128 && tok0 + kRows < p.rows) {
+      bulk_load_1d(stage + OFF_SFB + kSfStage,
+                   sfb + chunks_per_tile * kSfChunk + static_cast<size_t>(kb) * kSfStage, sf_bytes,
+                   &ctl->full[s], pol_a);
+    }
   };
   const int pre = nkb < STAGES ? nkb : STAGES;
 
@@ -285,6 +295,10 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
                 slot + 4, umma_desc_noswizzle_rows16(base + OFF_SFA + kSfStage + k4 * kSfChunk));
           }
           tmem_cp_32x128b_warpx4(slot + 8, umma_desc_noswizzle_rows16(base + OFF_SFB + k4 * kSfChunk));
+          if (BLOCK_TOK > 128) {  // tokens [128, 256): the next four scale columns
+            tmem_cp_32x128b_warpx4(slot + 12,
+                                   umma_desc_noswizzle_rows16(base + OFF_SFB + kSfStage + k4 * kSfChunk));
+          }
           const uint32_t acc = (i | k4) != 0;
           umma_nvfp4(tmem, desc_w0 + 2 * k4, desc_a + 2 * k4, IDESC, slot, slot + 8 + sfb_quartile, acc);
           if (GATE_UP) {
@@ -392,6 +406,8 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), GATE_UP ? 1 : 
           }
         }
       }
+    } else if (BLOCK_TOK > 128) {
+      // 256-token tiles are launched unsplit only
     } else if (clustered && pushed) {
       const uint32_t rank = cluster_cta_rank();  // = split
       cluster_wait();
@@ -760,8 +776,8 @@ cudaError_t nv_prepare() {
 }  // namespace
 
 size_t nvfp4_ring_bytes(int block_tok) {
-  return block_tok <= 32 ? static_cast<size_t>(nv_stages(32, false)) * nv_stage_bytes(32, false)
-                         : static_cast<size_t>(nv_stages(128, false)) * nv_stage_bytes(128, false);
+  const int tile = block_tok <= 32 ? 32 : block_tok <= 128 ? 128 : 256;
+  return static_cast<size_t>(nv_stages(tile, false)) * nv_stage_bytes(tile, false);
 }
 
 cudaError_t nvfp4_prepare() {
@@ -769,6 +785,7 @@ cudaError_t nvfp4_prepare() {
   if ((e = nv_prepare<32, true>()) != cudaSuccess) return e;
   if ((e = nv_prepare<128, true>()) != cudaSuccess) return e;
   if ((e = nv_prepare<32, false>()) != cudaSuccess) return e;
+  if ((e = nv_prepare<256, false>()) != cudaSuccess) return e;
   return nv_prepare<128, false>();
 }
 
@@ -783,6 +800,7 @@ cudaError_t launch_nvfp4_gemm(cudaStream_t stream, int block_tok, bool gate_up,
     return gate_up ? nv_launch<128, true>(stream, tmap_w, tmap_a, p)
                    : nv_launch<128, false>(stream, tmap_w, tmap_a, p);
   }
+  if (block_tok == 256 && !gate_up) return nv_launch<256, false>(stream, tmap_w, tmap_a, p);
   return cudaErrorInvalidValue;
 }
 

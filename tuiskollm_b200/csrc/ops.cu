@@ -40,6 +40,8 @@ Tuning Tuning::from_environment() {
   t.nvfp4_pair = env_int("TK100_PAIR", t.nvfp4_pair);
   t.nvfp4_pair_min_rows = env_int("TK100_PAIR_MIN_ROWS", t.nvfp4_pair_min_rows);
   t.swiglu_pairs = env_int("TK100_SWIGLU_PAIRS", t.swiglu_pairs);
+  t.nvfp4_wide = env_int("TK100_NVFP4_WIDE", t.nvfp4_wide);
+  t.nvfp4_wide_min_rows = env_int("TK100_NVFP4_WIDE_MIN_ROWS", t.nvfp4_wide_min_rows);
   t.nvfp4_persist = env_int("TK100_PERSIST", t.nvfp4_persist);
   t.nvfp4_persist_min_rows = env_int("TK100_PERSIST_MIN_ROWS", t.nvfp4_persist_min_rows);
   t.fused_exchange = env_int("TK100_FUSED_TAIL", t.fused_exchange);
@@ -1034,13 +1036,19 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
                          "launching the persistent NVFP4 projection"));
     return quantise_after();
   }
-  const int block_tok = rows <= 32 ? 32 : 128;
+  // 256-token tiles (one CTA per SM, a third fewer operand bytes and issue slots per MAC) for
+  // prefill shapes: the plain projection unsplit, and the gate/up pairs.
+  const bool pairs_wanted = gate_up && ctx_.tuning().swiglu_pairs != 0;
+  const bool wide = rows >= ctx_.tuning().nvfp4_wide_min_rows &&
+                    ((!gate_up && ctx_.tuning().nvfp4_wide >= 1) ||
+                     (pairs_wanted && ctx_.tuning().nvfp4_wide >= 2));
+  const int block_tok = rows <= 32 ? 32 : wide ? 256 : 128;
   const int tiles_n = out_rows / 128;
   const int tiles_m = (rows + block_tok - 1) / block_tok;
   const long long tiles = static_cast<long long>(tiles_n) * tiles_m;
   const int kb_total = (columns + 255) / 256;
   int splits = 1;
-  if (!gate_up) {
+  if (!gate_up && !wide) {
     // two CTAs share an SM at <= 32 tokens
     // Clusters cannot straddle GPCs, so a launch that fills every slot spills into a second
     // wave: aim at ~80 % of the slots (measured on 5120 x 17408, M = 8: 6 splits 13.0 us, 7 splits
@@ -1106,7 +1114,7 @@ Status Nvfp4MlpOp::launch(cudaStream_t stream, bool gate_up, int rows, int out_r
     // split K included (down, M = 1: 14.05 -> 14.6 us, so off by default).
     const size_t land = static_cast<size_t>(p.splits - 1) * (rows < block_tok ? rows : block_tok) * 128 * sizeof(float);
     const bool everywhere = ctx_.tuning().cluster == 2;
-    if ((as_pairs && (block_tok == 128 || everywhere)) ||
+    if ((as_pairs && (block_tok >= 128 || everywhere)) ||
         (everywhere && p.splits > 1 && land <= nvfp4_ring_bytes(block_tok))) {
       p.cluster = 2;
     }

@@ -40,6 +40,9 @@ struct Tuning {
   int nvfp4_pair_min_rows = 1024;
   int nvfp4_persist = 0;      // TK100_PERSIST=1: persistent CTA-pair route for NVFP4 prefill shapes
   int nvfp4_persist_min_rows = 512;  // TK100_PERSIST_MIN_ROWS
+  int nvfp4_wide = 0;         // TK100_NVFP4_WIDE: 256-token tiles (one CTA per SM) for NVFP4 prefill
+                              // shapes: 1 down, 2 the gate/up pairs too
+  int nvfp4_wide_min_rows = 512;  // TK100_NVFP4_WIDE_MIN_ROWS
   int swiglu_pairs = 1;       // TK100_SWIGLU_PAIRS=0: one CTA holds the gate and the up tile
   int fused_exchange = 1;     // TK100_FUSED_TAIL=0: argmax finalize / exchange as launches of their own
   int fused_quant = 0;        // TK100_FUSED_QUANT=1: launches of one wave and at most 4 rows quantise
