@@ -12,6 +12,7 @@ const SOURCES: &[&str] = &[
     "norm_quant.cu",
     "fp8_proj.cu",
     "fp8_pair.cu",
+    "fp8_pair_persist.cu",
     "fp8_mlp.cu",
     "gdn.cu",
     "materialize.cu",

@@ -158,7 +158,7 @@ def test_benchmarked_prefill_shapes_sampled_tiles(tk, ctx, oracle, out_rows, row
     tk.GdnInputProjectionOp(ctx, out_rows).launch(None, rows, x, planes.codes, planes.scales, w, s,
                                                   planes.out)
     torch.cuda.synchronize()
-    assert ctx.last_kernel.startswith("fp8_pair_kernel"), ctx.last_kernel
+    assert ctx.last_kernel.startswith(("fp8_pair_kernel", "fp8_pair_persist_kernel")), ctx.last_kernel
     xb = _u16(x)
     oc, os_ = oracle.quantize_e4m3(xb)
     assert np.array_equal(host(planes.codes)[:rows], oc)
@@ -356,3 +356,34 @@ def test_registered_plane_is_not_encoded_again(tk, ctx, oracle):
     assert torch.equal(out_a, out_b)
     with pytest.raises(tk.GpuError, match="register plane"):
         ctx.register_plane(wd.view(-1)[1:1 + 1024 * 64].view(1024, 64))   # not 128-byte aligned
+
+
+@pytest.mark.parametrize("out_rows,rows", [(1024, 700), (4096, 1300), (4096, 2600)])
+def test_persistent_pair_route_matches_pair_route_bit_for_bit(tk, oracle, out_rows, rows, monkeypatch):
+    """TK100_FP8_PERSIST: resident CTA pairs walk the pair tiles with two TMEM accumulators in
+    rotation.  (4096, 1300) gives some pairs a second tile, (4096, 2600) a third (the first
+    accumulator is reused, so the issuer has to wait for its epilogue).  Same K order into one fp32
+    accumulator as the one-tile-per-pair kernel: the same bits, ragged token tails included; the
+    first case is also checked against the oracle."""
+    from tuiskollm_b200 import synth
+
+    hidden = 1024
+    xb = synth.normal_bf16(47, rows, (rows, hidden))
+    wc, ws = synth.fp8_weights(47, out_rows, out_rows, hidden)
+    outs = {}
+    for route, env in (("persistent", "2"), ("pair", "0")):
+        monkeypatch.setenv("TK100_FP8_PAIR", "2")
+        monkeypatch.setenv("TK100_FP8_PERSIST", env)
+        c = tk.Context(device=0, hidden=hidden, max_rows=4096)
+        planes = Planes(rows + 2, hidden, out_rows)
+        tk.GdnInputProjectionOp(c, out_rows).launch(
+            None, rows, dev(xb.view(np.int16)), planes.codes, planes.scales, dev(wc),
+            dev(ws.view(np.int16)), planes.out)
+        torch.cuda.synchronize()
+        assert c.device_status() == 0, route
+        assert c.last_kernel.startswith("fp8_pair_persist_kernel") == (route == "persistent"), c.last_kernel
+        planes.check_inactive(rows)
+        if out_rows == 1024:
+            check_projection(oracle, xb, wc, ws, planes, rows, floor=0.25 * (hidden / 5120) ** 0.5)
+        outs[route] = _u16(planes.out)[:rows].copy()
+    assert np.array_equal(outs["persistent"], outs["pair"])

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtuisko_sm100.so")
-SOURCES = ["norm_quant.cu", "fp8_proj.cu", "fp8_pair.cu", "fp8_mlp.cu", "gdn.cu", "materialize.cu", "nvfp4.cu", "nvfp4_pair.cu", "nvfp4_persist.cu", "peer_reduce.cu", "sampler.cu", "ops.cu", "static_entry.cu"]
+SOURCES = ["norm_quant.cu", "fp8_proj.cu", "fp8_pair.cu", "fp8_pair_persist.cu", "fp8_mlp.cu", "gdn.cu", "materialize.cu", "nvfp4.cu", "nvfp4_pair.cu", "nvfp4_persist.cu", "peer_reduce.cu", "sampler.cu", "ops.cu", "static_entry.cu"]
 HEADERS = ["common.cuh", "ptx.cuh", "kernels.h", "ops.hpp", "../../include/tuisko_sm100.h"]
 
 

@@ -253,6 +253,10 @@ int fp8_projection_stages(int block_tok);
 cudaError_t fp8_projection_prepare();  // sets the dynamic shared-memory attributes once
 // fp8_pair.cu: prefill route on CTA pairs (256-row x 256-token pair tiles, BF16 output only,
 // unsplit K; out_rows must be a multiple of 256).
+// Persistent form (fp8_pair_persist.cu): `pairs` resident CTA pairs walk the pair tiles.
+cudaError_t fp8_pair_persist_prepare();
+cudaError_t launch_fp8_pair_persist(cudaStream_t stream, int pairs, const CUtensorMap& tmap_w,
+                                    const CUtensorMap& tmap_a, const Fp8ProjParams& p);
 cudaError_t fp8_pair_prepare();
 cudaError_t launch_fp8_pair(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                             const Fp8ProjParams& p);

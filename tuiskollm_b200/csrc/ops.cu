@@ -40,6 +40,7 @@ Tuning Tuning::from_environment() {
   t.nvfp4_pair = env_int("TK100_PAIR", t.nvfp4_pair);
   t.nvfp4_pair_min_rows = env_int("TK100_PAIR_MIN_ROWS", t.nvfp4_pair_min_rows);
   t.swiglu_pairs = env_int("TK100_SWIGLU_PAIRS", t.swiglu_pairs);
+  t.fp8_persist = env_int("TK100_FP8_PERSIST", t.fp8_persist);
   t.nvfp4_wide = env_int("TK100_NVFP4_WIDE", t.nvfp4_wide);
   t.nvfp4_wide_min_rows = env_int("TK100_NVFP4_WIDE_MIN_ROWS", t.nvfp4_wide_min_rows);
   t.nvfp4_persist = env_int("TK100_PERSIST", t.nvfp4_persist);
@@ -127,6 +128,11 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
   }
   if ((e = fp8_swiglu_prepare()) != cudaSuccess) {
     *error = std::string("[gpu.module] preparing the FP8 SwiGLU routes: ") + cudaGetErrorString(e);
+    delete ctx;
+    return TK100_ERR_MODULE;
+  }
+  if ((e = fp8_pair_persist_prepare()) != cudaSuccess) {
+    *error = std::string("[gpu.module] preparing the persistent FP8 pair kernel: ") + cudaGetErrorString(e);
     delete ctx;
     return TK100_ERR_MODULE;
   }
@@ -705,6 +711,16 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
       q.debug = debug_flags();
       q.stamps = debug_stamps();
       ctx_.count_launch();
+      // More pair tiles than pairs that fit the device at once: the resident pairs walk the tiles
+      // with two accumulators in rotation (TK100_FP8_PERSIST).
+      const long long pair_tiles = pair_ctas / 2;
+      if (tune.fp8_persist != 0 && ctx_.persist_pairs() > 0 &&
+          (pair_tiles > ctx_.persist_pairs() || tune.fp8_persist == 2)) {
+        const int pairs = static_cast<int>(pair_tiles < ctx_.persist_pairs() ? pair_tiles : ctx_.persist_pairs());
+        ctx_.note_route("fp8_pair_persist_kernel", 6, pairs, 1, 1);
+        return ctx_.check(launch_fp8_pair_persist(stream, pairs, map_w, map_a, q),
+                          "launching the persistent FP8 pair projection");
+      }
       ctx_.note_route("fp8_pair_kernel", q.deep_ring ? 6 : 3, 0, 1, 1);
       return ctx_.check(launch_fp8_pair(stream, map_w, map_a, q), "launching the FP8 pair projection");
     }

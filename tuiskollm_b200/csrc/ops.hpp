@@ -40,6 +40,8 @@ struct Tuning {
   int nvfp4_pair_min_rows = 1024;
   int nvfp4_persist = 0;      // TK100_PERSIST=1: persistent CTA-pair route for NVFP4 prefill shapes
   int nvfp4_persist_min_rows = 512;  // TK100_PERSIST_MIN_ROWS
+  int fp8_persist = 0;        // TK100_FP8_PERSIST=1: persistent CTA pairs with two accumulators for FP8
+                              // prefill shapes of more pair tiles than resident pairs
   int nvfp4_wide = 0;         // TK100_NVFP4_WIDE: 256-token tiles (one CTA per SM) for NVFP4 prefill
                               // shapes: 1 down, 2 the gate/up pairs too
   int nvfp4_wide_min_rows = 512;  // TK100_NVFP4_WIDE_MIN_ROWS
