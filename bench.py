@@ -1160,8 +1160,8 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local, nccl_reduce=False):
 
 def run_case(args):
     """One small side case on one GPU (for profiling): `nvfp4:M`, `fp8:N:M`, `norm:M`,
-    `exchange`, `stamps:N:M` (per-CTA time stamps, experiment build) or `issue` (the tcgen05
-    issue-rate micro-benchmark beside this file)."""
+    `gdn:B`, `sampler:B`, `exchange`, `stamps:N:M` (per-CTA time stamps, experiment build) or
+    `issue` (the tcgen05 issue-rate micro-benchmark beside this file)."""
     if args.case == "issue":
         src = os.path.join(ROOT, "bench_tcgen05_issue.cu")
         exe = os.path.join(ROOT, "bench_tcgen05_issue")
@@ -1306,6 +1306,55 @@ def run_case(args):
             norm()
         ms = time_region(torch, norm, reps) / reps
         rows = [{"op": "norm", "M": m, "us": ms * 1e3, "GB/s": (11 * m * HIDDEN + 4 * m) / ms / 1e6}]
+    elif parts[0] == "gdn":
+        # one GDN decode step (prepare, recurrence) per call, state slots rotating through > L2
+        b = int(parts[1])
+        slots = 48
+        g_x = synth.torch_normal_bf16(SEED, 400, (8, HIDDEN), "cuda")
+        g_cw = synth.torch_normal_bf16(SEED, 401, (96, HIDDEN), "cuda", std=0.02)
+        g_alog = synth.torch_normal_bf16(SEED, 402, (48,), "cuda")
+        g_dt = synth.torch_normal_bf16(SEED, 403, (48,), "cuda")
+        g_proj = synth.torch_normal_bf16(SEED, 404, (8, 16384), "cuda")
+        g_convw = synth.torch_normal_bf16(SEED, 405, (10240, 4), "cuda", std=0.5)
+        g_hist = synth.torch_normal_bf16(SEED, 406, (slots, 10240, 3), "cuda")
+        g_state = torch.zeros((slots, 48, 128, 128), dtype=torch.float32, device="cuda")
+        g_state.normal_(0.0, 0.05, generator=torch.Generator(device="cuda").manual_seed(SEED + 407))
+        g_norm = synth.torch_normal_bf16(SEED, 408, (128,), "cuda")
+        g_decay = torch.empty((8, 48), dtype=torch.float32, device="cuda")
+        g_beta = torch.empty((8, 48), dtype=torch.float32, device="cuda")
+        g_conv = torch.empty((8, 10240), dtype=torch.bfloat16, device="cuda")
+        g_out = torch.empty((8, 6144), dtype=torch.bfloat16, device="cuda")
+        groups = slots // b
+        slot_rows = [torch.arange(g * b, (g + 1) * b, dtype=torch.int32, device="cuda") for g in range(groups)]
+        prep_op, rec_op = tk.GdnPrepareOp(ctx), tk.GdnRecurrenceOp(ctx)
+        state = {"i": 0}
+
+        def gdn_step():
+            r = slot_rows[state["i"] % groups]
+            state["i"] += 1
+            prep_op.launch(None, b, g_x, g_cw, g_alog, g_dt, g_proj, g_convw, r, g_hist, g_decay, g_beta, g_conv)
+            rec_op.launch(None, b, g_conv, g_proj, g_decay, g_beta, g_norm, r, g_state, g_out)
+
+        for _ in range(3):
+            gdn_step()
+        ms = time_region(torch, gdn_step, reps) / reps
+        rows = [{"op": "gdn_step (eager launches)", "B": b, "us": ms * 1e3}]
+    elif parts[0] == "sampler":
+        b = int(parts[1])
+        vocab = 248320
+        copies = 8
+        logit_rows = [synth.torch_normal_bf16(SEED, 500 + c, (b, vocab), "cuda", std=3.0) for c in range(copies)]
+        samp = tk.Sampler(ctx, vocab, [tk.SamplingOptions(seed=i) for i in range(b)], [(1, 2)] * b)
+        state = {"i": 0}
+
+        def draw():
+            samp.sample(None, logit_rows[state["i"] % copies])
+            state["i"] += 1
+
+        for _ in range(3):
+            draw()
+        ms = time_region(torch, draw, reps) / reps
+        rows = [{"op": "device sampler (eager launches)", "B": b, "us": ms * 1e3}]
     elif parts[0] == "exchange":
         # the fused exchange kernel with world = 1: its fixed cost without NVLink or rank skew
         m = 1
