@@ -1695,10 +1695,23 @@ def run_native(args):
             "selected_tokens": [c["token0_index"] for c in checks],
         }
         if tp:
+            # per rank: its share of the slice's weight bytes (FP8 QKV + GDN-in planes, NVFP4 codes and
+            # scales of gate_up and down) against the measured copy rate, and the fp32 partial sums
+            # that cross NVLink (each rank sends and receives (world - 1) / world of them, two-shot)
+            from tuiskollm_b200 import synth as _synth
+            slice_weight_bytes = ((_synth.QKV_ROWS + _synth.GDN_ROWS) * HIDDEN
+                                  + 3 * _synth.INTERMEDIATE * HIDDEN * 9 // 16)
             line["tp_layer_slice"] = [
                 {"M": t[0], "us": t[1] * 1e3, "launch": t[2], "partial_bytes": t[0] * HIDDEN * 4,
                  "reduce": t[3],
-                 "parallelism": f"column(QKV,GDN-in,gate_up) + row(down) x{world}, fp32 partial sums"}
+                 "parallelism": f"column(QKV,GDN-in,gate_up) + row(down) x{world}, fp32 partial sums",
+                 "roofline": {"bound": "hbm" if t[0] <= 32 else "tensor",
+                              "weight_bytes_per_rank": slice_weight_bytes // world,
+                              "floor_us_at_measured_hbm": slice_weight_bytes / world / peak / 1e3,
+                              "frac": slice_weight_bytes / world / peak / 1e3 / (t[1] * 1e3),
+                              "nvlink_bytes_per_rank": t[0] * HIDDEN * 4 * (world - 1) // world,
+                              "nvlink_floor_us_at_770GBs": t[0] * HIDDEN * 4 * (world - 1) / world / 770e3,
+                              "peak_kind": peak_kind}}
                 for t in tp]
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, note, srows = cpu_lm_head(m, 3, 1, budget_s=15.0,
