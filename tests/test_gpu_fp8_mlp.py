@@ -193,3 +193,36 @@ def test_fp8_swiglu_rejected_launches(tk, ctx):
         op.launch(None, 1, x, codes, scales, w.data_ptr() + 16, ws, out)
     assert "128-byte aligned" in str(info.value)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("rows", [256, 512])
+def test_benchmarked_fp8_down_and_gdn_output_sampled_rows(tk, ctx, oracle, rows):
+    """The benchmarked batched shapes of the dense-FP8 down projection (K = 17408: at 256 tokens
+    the one-CTA kernel with K split over clusters, at 512 the CTA pairs) and of the GDN output
+    projection at full size: quantiser bit-exact, sampled output rows (first, middle and last
+    128-row tile) of every token against the f64 oracle within 1e-2."""
+    from tuiskollm_b200 import synth
+
+    for columns, stream in ((INTER, 91), (GDN_VALUE, 92)):
+        w, s = synth.torch_fp8_weights(7, stream, HIDDEN, columns, "cuda")
+        xb = synth.normal_bf16(7, stream + 10, (rows, columns))
+        planes = Planes(rows + 1, columns, HIDDEN)
+        if columns == INTER:
+            tk.Fp8DownOp(ctx).launch(None, rows, dev(xb.view(np.int16)), planes.codes, planes.scales, w, s,
+                                     planes.out)
+        else:
+            tk.GdnOutputProjectionOp(ctx, columns).launch(None, rows, dev(xb.view(np.int16)), planes.codes,
+                                                          planes.scales, w, s, planes.out)
+        route = ctx.last_kernel
+        torch.cuda.synchronize()
+        oc, os_ = oracle.quantize_e4m3(xb)
+        assert np.array_equal(host(planes.codes)[:rows], oc), route
+        assert np.array_equal(host(planes.scales)[:rows].view(np.uint32), os_.view(np.uint32)), route
+        sample = np.concatenate([np.arange(0, 16), np.arange(2560, 2576), np.arange(HIDDEN - 16, HIDDEN)])
+        wc = host(w)[sample]
+        ws = host(s.view(torch.int16)).view(np.uint16)[sample]
+        exp = oracle.fp8_projection(oc, os_, wc, ws)
+        got = _u16(planes.out)[:rows][:, sample]
+        assert max_relative_error(got, exp, 4 * float(np.abs(exp).mean())) <= 1e-2, route
+        planes.check_inactive(rows)
+    assert ctx.device_status() == 0

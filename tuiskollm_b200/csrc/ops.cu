@@ -688,8 +688,12 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     // most SMs idle: the one-CTA kernel splits K instead (TK100_FP8_PAIR=2 takes the pair route
     // anyway).  Shards of 32-48 pair CTAs were measured faster on pairs than split.
     const long long pair_ctas = 2LL * ((rows + 255) / 256) * (out_rows / 256);
+    // A long reduction on few pair tiles (the dense-FP8 down projection at 256 tokens: 40 CTAs
+    // walking K = 17408) leaves most SMs idle as well; the one-CTA kernel splits K over clusters
+    // there (measured 44.6 against 57.0 us).
+    const bool long_k_few_tiles = pair_ctas < ctx_.sm_count() / 2 && columns >= 16384;
     if (tune.fp8_pair != 0 && rows >= min_rows && out_rows % 256 == 0 &&
-        (pair_ctas >= 32 || tune.fp8_pair == 2) && output &&
+        ((pair_ctas >= 32 && !long_k_few_tiles) || tune.fp8_pair == 2) && output &&
         !logits_f32 && !argmax_scratch && ctx_.forced_block_tok() == 0 && ctx_.forced_splits() == 0) {
       CUtensorMap map_w, map_a;
       TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(out_rows),
