@@ -1720,9 +1720,19 @@ def run_native(args):
                                     "sample": note, "seconds_per_sample": dt,
                                     "sampled_vocab_rows": srows}
         if world == 1 and not args.no_extra:
+            # clocks while the configuration rows run (their cases are visited in rotating order,
+            # so one median covers them all); each row also carries time x that median, which
+            # compares runs taken at different sustained clocks
+            row_sampler = ClockSampler(local)
+            row_sampler.start()
             rows, deviation = config_rows(torch, tk, ctx, peak, peak_kind,
                                           {"m": m, "vocab": vocab, "wc": wc, "ws": ws},
                                           with_cpu=not args.no_cpu)
+            row_clocks = row_sampler.stop()
+            line["clocks_configs"] = row_clocks
+            if row_clocks.get("sm_mhz"):
+                for r in rows:
+                    r["kilocycles_at_median_sm_clock"] = r["us"]["median"] * row_clocks["sm_mhz"] / 1e3
             line["configs"] = rows
             if deviation is not None:
                 line["w4a4_vs_a16"] = deviation
