@@ -1160,7 +1160,7 @@ def tp_layer_slice(torch, tk, dist, rank, world, m, local, nccl_reduce=False):
 
 def run_case(args):
     """One small side case on one GPU (for profiling): `nvfp4:M`, `fp8:N:M`, `norm:M`,
-    `gdn:B`, `sampler:B`, `exchange`, `stamps:N:M` (per-CTA time stamps, experiment build) or
+    `fp8mlp:M`, `gdn:B`, `sampler:B`, `exchange`, `stamps:N:M` (per-CTA time stamps, experiment build) or
     `issue` (the tcgen05 issue-rate micro-benchmark beside this file)."""
     if args.case == "issue":
         src = os.path.join(ROOT, "bench_tcgen05_issue.cu")
@@ -1306,6 +1306,38 @@ def run_case(args):
             norm()
         ms = time_region(torch, norm, reps) / reps
         rows = [{"op": "norm", "M": m, "us": ms * 1e3, "GB/s": (11 * m * HIDDEN + 4 * m) / ms / 1e6}]
+    elif parts[0] == "fp8mlp":
+        # dense-FP8 gate/up + SwiGLU and down at M tokens, weight planes rotating through > L2
+        m = int(parts[1])
+        inter = synth.INTERMEDIATE
+        copies = 3 if m <= 32 else 1
+        gu_planes = [synth.torch_fp8_weights(SEED, 70 + c, 2 * inter, HIDDEN, "cuda") for c in range(copies)]
+        dn_planes = [synth.torch_fp8_weights(SEED, 75 + c, HIDDEN, inter, "cuda") for c in range(copies)]
+        x = synth.torch_normal_bf16(SEED, 9, (m, HIDDEN), "cuda")
+        xi = synth.torch_normal_bf16(SEED, 10, (m, inter), "cuda")
+        c1 = torch.empty((m, HIDDEN), dtype=torch.uint8, device="cuda")
+        c2 = torch.empty((m, inter), dtype=torch.uint8, device="cuda")
+        s1, s2 = (torch.empty((m,), dtype=torch.float32, device="cuda") for _ in range(2))
+        mid = torch.empty((m, inter), dtype=torch.bfloat16, device="cuda")
+        out = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device="cuda")
+        sw_op, dn_op = tk.Fp8SwiGluOp(ctx), tk.Fp8DownOp(ctx)
+        sw_op.launch(None, m, x, c1, s1, gu_planes[0][0], gu_planes[0][1], mid)
+        dn_op.launch(None, m, xi, c2, s2, dn_planes[0][0], dn_planes[0][1], out)
+        rows = []
+        for nm, op_, planes_, args_ in (("fp8_swiglu", sw_op, gu_planes, (c1, s1, mid)),
+                                        ("fp8_down", dn_op, dn_planes, (c2, s2, out))):
+            state = {"i": 0}
+
+            def run(op_=op_, planes_=planes_, args_=args_, state=state):
+                w, sc = planes_[state["i"] % len(planes_)]
+                state["i"] += 1
+                op_.launch(None, m, None, args_[0], args_[1], w, sc, args_[2])
+
+            for _ in range(3):
+                run()
+            kernel = ctx.last_kernel
+            ms = time_region(torch, run, reps) / reps
+            rows.append({"op": nm, "M": m, "us": ms * 1e3, "kernel": kernel})
     elif parts[0] == "gdn":
         # one GDN decode step (prepare, recurrence) per call, state slots rotating through > L2
         b = int(parts[1])
