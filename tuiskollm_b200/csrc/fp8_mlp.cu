@@ -28,23 +28,31 @@ constexpr int kWTile = kRows * kTileKBytes;
 constexpr int kEpilogueWarps = 8;  // two per TMEM lane quadrant, alternate 16-token chunks
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 
-__host__ __device__ constexpr int sw_stages(int block_tok) { return block_tok <= 32 ? 5 : 4; }
+// Ring depth.  32-token tiles: 5 stages of 36 KB.  128-token tiles: 4 stages of 48 KB when the
+// launch is one token tile deep (136 CTAs, one per SM: the deep ring carries the stream), 2 stages
+// when it has several token tiles -- then two CTAs share an SM (96 KB each, their two accumulators
+// fill the 512 TMEM columns) and one runs its ramp or its SwiGLU epilogue under the other's K loop
+// (M = 256: 57.8 -> 48.9 us, M = 512: 97.3 -> 87.0 us, M = 2048: 357.7 -> 315.0 us; a single
+// token tile on the shallow ring: 30.9 -> 42.6 us, hence both).
+__host__ __device__ constexpr int sw_stages(int block_tok, bool shallow) {
+  return block_tok <= 32 ? 5 : (shallow ? 2 : 4);
+}
 __host__ __device__ constexpr int sw_stage_bytes(int block_tok) { return 2 * kWTile + block_tok * kTileKBytes; }
 
-template <int BLOCK_TOK>
+template <int BLOCK_TOK, bool SHALLOW>
 struct SwControl {
-  uint64_t full[sw_stages(BLOCK_TOK)];
-  uint64_t empty[sw_stages(BLOCK_TOK)];
+  uint64_t full[sw_stages(BLOCK_TOK, SHALLOW)];
+  uint64_t empty[sw_stages(BLOCK_TOK, SHALLOW)];
   uint64_t tmem_full;
   float a_scale[BLOCK_TOK];
   uint32_t tmem_base;
   uint32_t pad;
 };
 
-template <int BLOCK_TOK>
+template <int BLOCK_TOK, bool SHALLOW>
 constexpr size_t sw_smem_bytes() {
-  return 1024 + static_cast<size_t>(sw_stages(BLOCK_TOK)) * sw_stage_bytes(BLOCK_TOK) +
-         sizeof(SwControl<BLOCK_TOK>);
+  return 1024 + static_cast<size_t>(sw_stages(BLOCK_TOK, SHALLOW)) * sw_stage_bytes(BLOCK_TOK) +
+         sizeof(SwControl<BLOCK_TOK, SHALLOW>);
 }
 
 __device__ __forceinline__ float silu_fp8_path(float v) {
@@ -53,15 +61,15 @@ __device__ __forceinline__ float silu_fp8_path(float v) {
   return __fdividef(v, 1.0f + ex);
 }
 
-template <int BLOCK_TOK>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BLOCK_TOK, bool SHALLOW>
+__global__ void __launch_bounds__(kThreads, SHALLOW ? 2 : 1)
     fp8_swiglu_kernel(const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_a, const Fp8SwigluParams p) {
-  constexpr int STAGES = sw_stages(BLOCK_TOK);
+  constexpr int STAGES = sw_stages(BLOCK_TOK, SHALLOW);
   constexpr int STAGE_BYTES = sw_stage_bytes(BLOCK_TOK);
   constexpr uint32_t TMEM_COLS = 2 * BLOCK_TOK;  // 64 or 256: gate accumulator, then up
   constexpr uint32_t IDESC = umma_idesc_e4m3(kRows, BLOCK_TOK);
-  using Ctl = SwControl<BLOCK_TOK>;
+  using Ctl = SwControl<BLOCK_TOK, SHALLOW>;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -207,28 +215,38 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-template <int BLOCK_TOK>
+template <int BLOCK_TOK, bool SHALLOW>
 cudaError_t sw_launch(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                       const Fp8SwigluParams& p) {
   dim3 grid((p.rows + BLOCK_TOK - 1) / BLOCK_TOK, (p.intermediate + kRows - 1) / kRows, 1);
-  return launch_kernel(fp8_swiglu_kernel<BLOCK_TOK>, grid, dim3(kThreads), sw_smem_bytes<BLOCK_TOK>(),
-                       stream, tmap_w, tmap_a, p);
+  return launch_kernel(fp8_swiglu_kernel<BLOCK_TOK, SHALLOW>, grid, dim3(kThreads),
+                       sw_smem_bytes<BLOCK_TOK, SHALLOW>(), stream, tmap_w, tmap_a, p);
+}
+
+template <int BLOCK_TOK, bool SHALLOW>
+cudaError_t sw_prepare() {
+  return cudaFuncSetAttribute(fp8_swiglu_kernel<BLOCK_TOK, SHALLOW>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(sw_smem_bytes<BLOCK_TOK, SHALLOW>()));
 }
 
 }  // namespace
 
 cudaError_t fp8_swiglu_prepare() {
-  cudaError_t e = cudaFuncSetAttribute(fp8_swiglu_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(sw_smem_bytes<32>()));
+  cudaError_t e = sw_prepare<32, false>();
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(fp8_swiglu_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(sw_smem_bytes<128>()));
+  if ((e = sw_prepare<128, false>()) != cudaSuccess) return e;
+  return sw_prepare<128, true>();
 }
 
 cudaError_t launch_fp8_swiglu(cudaStream_t stream, int block_tok, const CUtensorMap& tmap_w,
                               const CUtensorMap& tmap_a, const Fp8SwigluParams& p) {
-  if (block_tok == 32) return sw_launch<32>(stream, tmap_w, tmap_a, p);
-  if (block_tok == 128) return sw_launch<128>(stream, tmap_w, tmap_a, p);
+  if (block_tok == 32) return sw_launch<32, false>(stream, tmap_w, tmap_a, p);
+  if (block_tok == 128) {
+    // several token tiles: the shallow ring, two CTAs per SM
+    return p.rows > 128 ? sw_launch<128, true>(stream, tmap_w, tmap_a, p)
+                        : sw_launch<128, false>(stream, tmap_w, tmap_a, p);
+  }
   return cudaErrorInvalidValue;
 }
 

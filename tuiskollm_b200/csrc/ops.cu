@@ -892,7 +892,7 @@ Status Fp8SwiGluOp::launch(cudaStream_t stream, int rows, const uint16_t* input,
   p.out = output;
   p.status = ctx_.status_word();
   ctx_.count_launch();
-  ctx_.note_route("fp8_swiglu_kernel", block_tok, 0, 1, 0);
+  ctx_.note_route("fp8_swiglu_kernel", block_tok, block_tok == 128 && rows > 128 ? 1 : 0, 1, 0);
   return ctx_.check(launch_fp8_swiglu(stream, block_tok, map_w, map_a, p), "launching the FP8 SwiGLU");
 }
 
