@@ -208,6 +208,12 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   return p;
 }
 
+// fp32 store with an L2 cache policy (e.g. evict_last: the line stays in L2 instead of being
+// written back to DRAM in the middle of a read stream).
+__device__ __forceinline__ void st_global_f32_policy(float* p, float v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(policy) : "memory");
+}
+
 // 2-D tiled load, completion counted in bytes on `bar`.  c0 is the innermost
 // coordinate; c0 * element size must be a multiple of 16 bytes.
 // Asks L2 to fetch one box of a tiled tensor; nothing lands in shared memory and nothing is
