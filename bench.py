@@ -1320,12 +1320,19 @@ def run_case(args):
         s1, s2 = (torch.empty((m,), dtype=torch.float32, device="cuda") for _ in range(2))
         mid = torch.empty((m, inter), dtype=torch.bfloat16, device="cuda")
         out = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device="cuda")
-        sw_op, dn_op = tk.Fp8SwiGluOp(ctx), tk.Fp8DownOp(ctx)
+        go_planes = [synth.torch_fp8_weights(SEED, 80 + c, HIDDEN, 6144, "cuda") for c in range(4 if m <= 32 else 1)]
+        xg = synth.torch_normal_bf16(SEED, 11, (m, 6144), "cuda")
+        c3 = torch.empty((m, 6144), dtype=torch.uint8, device="cuda")
+        s3 = torch.empty((m,), dtype=torch.float32, device="cuda")
+        out_g = torch.empty((m, HIDDEN), dtype=torch.bfloat16, device="cuda")
+        sw_op, dn_op, go_op = tk.Fp8SwiGluOp(ctx), tk.Fp8DownOp(ctx), tk.GdnOutputProjectionOp(ctx, 6144)
         sw_op.launch(None, m, x, c1, s1, gu_planes[0][0], gu_planes[0][1], mid)
         dn_op.launch(None, m, xi, c2, s2, dn_planes[0][0], dn_planes[0][1], out)
+        go_op.launch(None, m, xg, c3, s3, go_planes[0][0], go_planes[0][1], out_g)
         rows = []
         for nm, op_, planes_, args_ in (("fp8_swiglu", sw_op, gu_planes, (c1, s1, mid)),
-                                        ("fp8_down", dn_op, dn_planes, (c2, s2, out))):
+                                        ("fp8_down", dn_op, dn_planes, (c2, s2, out)),
+                                        ("fp8_gdn_output", go_op, go_planes, (c3, s3, out_g))):
             state = {"i": 0}
 
             def run(op_=op_, planes_=planes_, args_=args_, state=state):
