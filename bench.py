@@ -842,7 +842,7 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
         case = f"fp8_lm_head_argmax:M{m}"
         proto.add(case, graph.replay, 1)
         meta[case] = {"config": 3, "op": "fp8_lm_head_argmax", "M": m, "N": lm["vocab"], "K": HIDDEN,
-                      "kernel": ctx.last_kernel + " + argmax_finalize_kernel", "kind": "hbm",
+                      "kernel": ctx.last_kernel + " (finalize in its last CTA)", "kind": "hbm",
                       "bytes": algorithmic_bytes(m, lm["vocab"], HIDDEN, 4),
                       "cpu": ("fp8", m, lm["vocab"], HIDDEN, 4)}
         keep.append((graph, x, codes, scales, logits, scratch, pairs))

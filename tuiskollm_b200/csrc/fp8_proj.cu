@@ -55,7 +55,7 @@ struct Control {
   uint64_t tmem_full;
   uint64_t go;    // split-K on a leader: the leader's ring is free, peers may store into it
   uint64_t done;  // split-K on a leader: every peer's partial tile has landed (leader only)
-  unsigned long long red[BLOCK_TOK];  // per-token argmax keys of this CTA
+  uint32_t red[BLOCK_TOK];  // per-token argmax keys of this CTA (local_key)
   float a_scale[BLOCK_TOK];
   float q_amax[4][kFusedQuantRows];  // fused quantiser: per-warp maxima of the epilogue warps
   uint32_t tmem_base;
@@ -86,6 +86,24 @@ __device__ __forceinline__ ArgmaxPair unpack_key(unsigned long long packed) {
   o.value = __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xffffffffu));
   o.index = packed == 0ull ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(packed));
   return o;
+}
+
+// Inside one CTA (128 consecutive weight rows) a candidate travels as 32 bits: the 16 significant
+// bits of the BF16 logit's order key above 128 - row in tile (1..128, so a lower row wins a tie and
+// 0 means "no candidate").  32-bit shuffles and native shared-memory maxima instead of 64-bit ones;
+// global_key() widens the CTA's winner to the packed (order key, ~index) word the merge works on.
+__device__ __forceinline__ uint32_t local_key(uint32_t bf16_bits, int row_in_tile) {
+  return (total_order_key(bf16_bits << 16) & 0xffff0000u) | static_cast<uint32_t>(128 - row_in_tile);
+}
+
+__device__ __forceinline__ unsigned long long global_key(uint32_t local, uint32_t first_index) {
+  const uint32_t high = local & 0xffff0000u;
+  // low half of the order key of a value whose low 16 bits are zero: ones for a negative value
+  // (top key bit clear), zeros otherwise
+  const uint32_t order = high | ((high & 0x80000000u) ? 0u : 0xffffu);
+  const uint32_t index = first_index + (128u - (local & 0xffffu));
+  return (static_cast<unsigned long long>(order) << 32) |
+         static_cast<unsigned long long>(0xffffffffu - index);
 }
 
 // Vocabulary-sharded greedy selection without a collective library call.  The calling threads
@@ -164,6 +182,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
   constexpr int STAGE_BYTES = kWStageBytes + A_STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = BLOCK_TOK < 32 ? 32 : BLOCK_TOK;
   constexpr uint32_t IDESC = umma_idesc_e4m3(kTileRows, BLOCK_TOK);
+  constexpr bool BATCHED16 = BLOCK_TOK == 16;  // 16-token tiles with more than three tokens: batched epilogue
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -347,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
             if (tile_n == 0 && split == 0 && p.scales_out) p.scales_out[tok0 + et] = scale;
           }
           ctl->a_scale[et] = scale;
-          ctl->red[et] = 0ull;
+          ctl->red[et] = 0u;
         }
         epilogue_barrier();
         // ---- each stage's code tile: epilogue warp w makes the k-blocks i = w, w + 4, ...; a lane
@@ -403,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     if (!fused_quant) {
       for (int j = et; j < BLOCK_TOK; j += kEpilogueThreads) {
         ctl->a_scale[j] = (j < valid_tok) ? p.act_scales[tok0 + j] : 0.0f;
-        ctl->red[j] = 0ull;
+        ctl->red[j] = 0u;
       }
     }
     const float w_scale = row_ok ? bf16_bits_to_f32(p.w_scales[n]) : 0.0f;
@@ -424,18 +443,13 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         if (p.logits_f32) p.logits_f32[o] = v;
       }
       if (want_argmax) {
-        unsigned long long packed = 0ull;
+        uint32_t packed = 0u;
         if (row_ok) {
           if ((b & 0x7f80u) == 0x7f80u) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
-          packed = (static_cast<unsigned long long>(total_order_key(b << 16)) << 32) |
-                   static_cast<unsigned long long>(0xffffffffu -
-                                                   static_cast<uint32_t>(p.vocab_offset + n));
+          packed = local_key(b, row_in_tile);
         }
 #pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) {
-          const unsigned long long other = __shfl_xor_sync(0xffffffffu, packed, o2);
-          packed = other > packed ? other : packed;
-        }
+        for (int o2 = 16; o2 > 0; o2 >>= 1) packed = max(packed, __shfl_xor_sync(0xffffffffu, packed, o2));
         if (lane == 0) atomicMax(&ctl->red[j], packed);
       }
     };
@@ -449,10 +463,10 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
         tmem_ld_wait();
-        if constexpr (BLOCK_TOK >= 32) {
-          // Many tokens per tile: the 16 tokens of a chunk go through scaling, rounding, stores
+        if (BLOCK_TOK >= 32 || (BATCHED16 && valid_tok > 3)) {
+          // Several tokens per tile: the 16 tokens of a chunk go through scaling, rounding, stores
           // and the warp maxima side by side (one dependent chain per token would leave the few
-          // epilogue warps waiting on latencies).  Same values, same order of comparisons.
+          // epilogue warps waiting on latencies).  Same values; maxima commute.
           uint32_t b[16];
           float v[16];
 #pragma unroll
@@ -473,42 +487,51 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
               // CTA, the tokens' rows a megabyte apart) is stored with the evict_last policy, so
               // the lines wait in L2 for the end of the weight stream instead of interrupting it
               // with scattered DRAM writes (LM head, M = 32: 242 -> 232 us).
-              const uint64_t logits_policy = l2_policy_evict_last();
+              if constexpr (BLOCK_TOK >= 32) {
+                const uint64_t logits_policy = l2_policy_evict_last();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (c0 + j < valid_tok) {
-                  st_global_f32_policy(p.logits_f32 + o0 + static_cast<size_t>(j) * p.out_rows, v[j], logits_policy);
+                for (int j = 0; j < 16; ++j) {
+                  if (c0 + j < valid_tok) {
+                    st_global_f32_policy(p.logits_f32 + o0 + static_cast<size_t>(j) * p.out_rows, v[j], logits_policy);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (c0 + j < valid_tok) p.logits_f32[o0 + static_cast<size_t>(j) * p.out_rows] = v[j];
                 }
               }
             }
           }
           if (want_argmax) {
-            unsigned long long pk[16];
+            uint32_t pk[16];
             uint32_t nonfinite = 0;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const bool live = row_ok && c0 + j < valid_tok;
               nonfinite |= (live && (b[j] & 0x7f80u) == 0x7f80u) ? 1u : 0u;
-              pk[j] = live ? ((static_cast<unsigned long long>(total_order_key(b[j] << 16)) << 32) |
-                              static_cast<unsigned long long>(0xffffffffu -
-                                                              static_cast<uint32_t>(p.vocab_offset + n)))
-                           : 0ull;
+              pk[j] = live ? local_key(b[j], row_in_tile) : 0u;
             }
             if (nonfinite) atomicOr(p.status, STATUS_NONFINITE_LOGIT);
+            // 16 tokens x 32 rows -> 16 maxima in 16 exchanges instead of 80: at each step a lane
+            // hands half of its tokens to the partner and keeps the maximum of the other half, so
+            // after offsets 16, 8, 4, 2 lane l holds token l >> 1 over 16 rows, and the exchange at
+            // offset 1 completes it.  Integer maxima: any order gives the same key.
 #pragma unroll
-            for (int o2 = 16; o2 > 0; o2 >>= 1) {
+            for (int o2 = 16, count = 8; o2 > 1; o2 >>= 1, count >>= 1) {
+              const bool upper = (lane & o2) != 0;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const unsigned long long other = __shfl_xor_sync(0xffffffffu, pk[j], o2);
-                pk[j] = other > pk[j] ? other : pk[j];
+              for (int j = 0; j < 8; ++j) {
+                if (j < count) {
+                  const uint32_t give = upper ? pk[j] : pk[j + count];
+                  const uint32_t keep = upper ? pk[j + count] : pk[j];
+                  pk[j] = max(keep, __shfl_xor_sync(0xffffffffu, give, o2));
+                }
               }
             }
-            if (lane == 0) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (c0 + j < valid_tok) atomicMax(&ctl->red[c0 + j], pk[j]);
-              }
-            }
+            pk[0] = max(pk[0], __shfl_xor_sync(0xffffffffu, pk[0], 1));
+            const int token = c0 + (lane >> 1);
+            if ((lane & 1) == 0 && token < valid_tok && pk[0] != 0u) atomicMax(&ctl->red[token], pk[0]);
           }
         } else {
 #pragma unroll
@@ -689,17 +712,24 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       cluster_wait();
     }
 
+    const bool spread = p.spread_keys != nullptr;
+    const int group = tile_n % kArgmaxGroups;
     if (want_argmax && !TK100_DBG(p, DBG_NO_EPILOGUE) &&
         (p.splits == 1 || (clustered && !on_leader) || (on_leader && split == 0) || ctl->is_last)) {
       epilogue_barrier();
       for (int j = et; j < valid_tok; j += kEpilogueThreads) {
-        const unsigned long long best = ctl->red[j];
-        if (best != 0ull) {
+        const uint32_t local = ctl->red[j];
+        if (local != 0u) {
+          const unsigned long long best =
+              global_key(local, static_cast<uint32_t>(p.vocab_offset + tile_n * kTileRows));
           // The value the atomic returns is stored to shared memory: the thread cannot pass the
           // barrier below before the atomic has been performed at L2, which orders it before the
           // ticket (no device-wide fence, which would also wait for this thread's logit stores).
-          const unsigned long long before = atomicMax(p.argmax_keys + tok0 + j, best);
-          if (p.tail_ticket != nullptr) ctl->red[j] = before;
+          unsigned long long* key =
+              spread ? p.spread_keys + (static_cast<size_t>(group) * kArgmaxSpreadRows + tok0 + j) * 16
+                     : p.argmax_keys + tok0 + j;
+          const unsigned long long before = atomicMax(key, best);
+          if (p.tail_ticket != nullptr) ctl->red[j] = static_cast<uint32_t>(before >> 32);
         }
       }
     }
@@ -708,9 +738,22 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       // draws the last one finalises (one GPU) or exchanges with the peers and merges.
       epilogue_barrier();
       if (et == 0) {
-        const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
-        const unsigned int ticket = atomicAdd(p.tail_ticket, 1u);
-        const bool last = ticket == total - 1;
+        bool last;
+        if (spread) {
+          // the group's ticket first; the last CTA of a group draws for the group
+          const unsigned int groups = gridDim.x < kArgmaxGroups ? gridDim.x : kArgmaxGroups;
+          const unsigned int members =
+              (gridDim.x - group + kArgmaxGroups - 1) / kArgmaxGroups * gridDim.y * gridDim.z;
+          unsigned int* group_ticket = p.spread_tickets + group * 32;
+          last = atomicAdd(group_ticket, 1u) == members - 1;
+          if (last) {
+            *group_ticket = 0u;
+            last = atomicAdd(p.tail_ticket, 1u) == groups - 1;
+          }
+        } else {
+          const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+          last = atomicAdd(p.tail_ticket, 1u) == total - 1;
+        }
         unsigned int step = 0;
         if (last) {
           *p.tail_ticket = 0u;  // re-armed for the next launch
@@ -725,10 +768,31 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
       }
       epilogue_barrier();
       if (ctl->tail_last) {
+        if (spread) {
+          // fold the groups: all loads of a token first, then the maximum (any order: integer max)
+          for (int t = et; t < p.rows; t += kEpilogueThreads) {
+            unsigned long long k[kArgmaxGroups];
+#pragma unroll
+            for (int g = 0; g < kArgmaxGroups; ++g) {
+              k[g] = __ldcg(p.spread_keys + (static_cast<size_t>(g) * kArgmaxSpreadRows + t) * 16);
+            }
+            unsigned long long best = 0ull;
+#pragma unroll
+            for (int g = 0; g < kArgmaxGroups; ++g) {
+              if (k[g] != 0ull) p.spread_keys[(static_cast<size_t>(g) * kArgmaxSpreadRows + t) * 16] = 0ull;
+              best = k[g] > best ? k[g] : best;
+            }
+            if (p.world > 1) {
+              __stcg(p.argmax_keys + t, best);  // read back below by this same thread
+            } else {
+              p.pairs_out[t] = unpack_key(best);
+            }
+          }
+        }
         if (p.world > 1) {
           exchange_and_merge(et, kEpilogueThreads, p.rows, p.world, p.rank, p.argmax_keys, p.peers,
                              ctl->tail_step, p.pairs_out, p.status);
-        } else {
+        } else if (!spread) {
           for (int t = et; t < p.rows; t += kEpilogueThreads) {
             const unsigned long long packed = __ldcg(p.argmax_keys + t);
             p.argmax_keys[t] = 0ull;

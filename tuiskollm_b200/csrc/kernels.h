@@ -203,6 +203,11 @@ struct ExchangePeers {
 // Largest row count whose activation quantiser the projection kernel runs itself.
 constexpr int kFusedQuantRows = 4;
 
+constexpr int kArgmaxGroups = 8;
+constexpr int kArgmaxSpreadRows = 32;
+constexpr size_t kArgmaxSpreadBytes =
+    static_cast<size_t>(kArgmaxGroups) * (kArgmaxSpreadRows + 1) * 128;  // keys, then the tickets
+
 struct Fp8ProjParams {
   int rows;       // active tokens M
   int out_rows;   // weight rows N (this shard)
@@ -240,6 +245,16 @@ struct Fp8ProjParams {
   // and clears argmax_keys.  Null ticket = no fused tail.
   unsigned int* tail_ticket;
   ArgmaxPair* pairs_out;        // [rows]
+  // Spread maxima (fused tail, rows <= kArgmaxSpreadRows): the CTAs of one wave finish together,
+  // and their atomics on one token's key -- and on the keys of the other tokens in the same
+  // 128-byte line -- queue behind one another at one L2 slice while the CTAs hold their SM slots.
+  // With spread_keys set, CTA tile_n works on group tile_n % kArgmaxGroups: key (group, token)
+  // sits in a line of its own ([group][kArgmaxSpreadRows] lines of 16 words, word 0 used), and
+  // tickets are drawn per group (spread_tickets, one line each) with only the last CTA of a group
+  // drawing from tail_ticket.  The CTA that draws the last one folds the groups, clears them and
+  // leaves argmax_keys untouched (world == 1) or holding the folded keys for the exchange.
+  unsigned long long* spread_keys;  // library-owned, zero between launches; null = direct keys
+  unsigned int* spread_tickets;     // [kArgmaxGroups] lines of 32 words, word 0 used
   int world, rank;
   unsigned int* step_counter;   // device step number of the exchange
   ExchangePeers peers;

@@ -46,6 +46,7 @@ Tuning Tuning::from_environment() {
   t.nvfp4_persist = env_int("TK100_PERSIST", t.nvfp4_persist);
   t.nvfp4_persist_min_rows = env_int("TK100_PERSIST_MIN_ROWS", t.nvfp4_persist_min_rows);
   t.fused_exchange = env_int("TK100_FUSED_TAIL", t.fused_exchange);
+  t.argmax_spread = env_int("TK100_ARGMAX_SPREAD", t.argmax_spread);
   t.fused_quant = env_int("TK100_FUSED_QUANT", t.fused_quant);
   return t;
 }
@@ -166,6 +167,8 @@ Status Context::create(const tk100_config& in, Context** out, std::string* error
             cudaMalloc(&ctx->status_, sizeof(uint32_t)) == cudaSuccess &&
             cudaMalloc(&ctx->exchange_step_, 2 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->exchange_step_, 0, 2 * sizeof(unsigned int)) == cudaSuccess &&
+            cudaMalloc(&ctx->argmax_spread_, kArgmaxSpreadBytes) == cudaSuccess &&
+            cudaMemset(ctx->argmax_spread_, 0, kArgmaxSpreadBytes) == cudaSuccess &&
             cudaMalloc(&ctx->peer_sum_state_, 4 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->peer_sum_state_, 0, 4 * sizeof(unsigned int)) == cudaSuccess &&
             cudaMemset(ctx->counters_, 0, ctx->counter_count_ * sizeof(unsigned int)) ==
@@ -187,6 +190,7 @@ Context::~Context() {
   if (counters_) cudaFree(counters_);
   if (status_) cudaFree(status_);
   if (exchange_step_) cudaFree(exchange_step_);
+  if (argmax_spread_) cudaFree(argmax_spread_);
   if (peer_sum_state_) cudaFree(peer_sum_state_);
 }
 
@@ -829,6 +833,10 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     p.rank = tail ? tail->rank : 0;
     p.step_counter = ctx_.exchange_step();
     p.peers = peers;
+    if (rows <= kArgmaxSpreadRows && ctx_.tuning().argmax_spread != 0) {
+      p.spread_keys = ctx_.argmax_spread_keys();
+      p.spread_tickets = ctx_.argmax_spread_tickets();
+    }
   }
   ctx_.count_launch();
   {

@@ -47,6 +47,7 @@ struct Tuning {
   int nvfp4_wide_min_rows = 512;  // TK100_NVFP4_WIDE_MIN_ROWS
   int swiglu_pairs = 1;       // TK100_SWIGLU_PAIRS=0: one CTA holds the gate and the up tile
   int fused_exchange = 1;     // TK100_FUSED_TAIL=0: argmax finalize / exchange as launches of their own
+  int argmax_spread = 1;      // TK100_ARGMAX_SPREAD=0: every CTA's maxima go straight to the caller's keys
   int fused_quant = 0;        // TK100_FUSED_QUANT=1: launches of one wave and at most 4 rows quantise
                               // inside the projection kernel, 2: at every size (measured slower
                               // than the quantiser launch in front, so off by default)
@@ -83,6 +84,13 @@ class Context {
   uint32_t* status_word() const { return status_; }
   unsigned int* exchange_step() const { return exchange_step_; }
   unsigned int* tail_ticket() const { return exchange_step_ + 1; }
+  unsigned long long* argmax_spread_keys() const {
+    return reinterpret_cast<unsigned long long*>(argmax_spread_);
+  }
+  unsigned int* argmax_spread_tickets() const {
+    return reinterpret_cast<unsigned int*>(argmax_spread_ +
+                                           static_cast<size_t>(kArgmaxGroups) * kArgmaxSpreadRows * 128);
+  }
   unsigned int* peer_sum_state() const { return peer_sum_state_; }
   const Tuning& tuning() const { return tuning_; }
   int forced_splits() const { return tuning_.splits; }
@@ -108,6 +116,7 @@ class Context {
   uint32_t* status_ = nullptr;
   unsigned int* exchange_step_ = nullptr;  // [0] device step counter of the peer argmax exchange,
                                            // [1] ticket of the LM head's fused tail
+  uint8_t* argmax_spread_ = nullptr;  // LM head: per-group maxima and tickets (kArgmaxSpreadBytes)
   unsigned int* peer_sum_state_ = nullptr;  // peer sum: [0] step counter, [1..3] phase tickets
   Tuning tuning_;
   uint64_t launches_ = 0;
