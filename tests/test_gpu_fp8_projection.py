@@ -387,3 +387,54 @@ def test_persistent_pair_route_matches_pair_route_bit_for_bit(tk, oracle, out_ro
             check_projection(oracle, xb, wc, ws, planes, rows, floor=0.25 * (hidden / 5120) ** 0.5)
         outs[route] = _u16(planes.out)[:rows].copy()
     assert np.array_equal(outs["persistent"], outs["pair"])
+
+
+@pytest.mark.parametrize("out_rows,hidden,rows", [(1024, 1024, 256), (1024, 2048, 700), (4096, 1024, 1300),
+                                                  (5120, 6144, 256), (8192, 5120, 300)])
+def test_stream_k_pair_route(tk, oracle, out_rows, hidden, rows, monkeypatch):
+    """TK100_FP8_STREAMK=1: the resident pairs share the launch's tiles x K steps evenly; a tile
+    whose K range is cut meets in fp32 scratch under a ticket and is summed in K order by whichever
+    CTA arrives last.  The result is the oracle's within the projection tolerance (a split sum is
+    not the unsplit sum's bits, so the pair route is compared within one BF16 step, and tiles that
+    no range cuts bit for bit by construction), ragged token tails included; launches repeat bit
+    for bit, eagerly and as graph replays, and scratch counters re-arm (three launches)."""
+    from tuiskollm_b200 import synth
+
+    xb = synth.normal_bf16(53, rows, (rows, hidden))
+    wc, ws = synth.fp8_weights(53, out_rows + hidden, out_rows, hidden)
+    outs = {}
+    for route, env in (("stream_k", "1"), ("pair", "0")):
+        monkeypatch.setenv("TK100_FP8_PAIR", "2")
+        monkeypatch.setenv("TK100_FP8_STREAMK", env)
+        c = tk.Context(device=0, hidden=hidden, max_rows=4096)
+        planes = Planes(rows + 2, hidden, out_rows)
+        op = tk.GdnInputProjectionOp(c, out_rows)
+        x, w, s = dev(xb.view(np.int16)), dev(wc), dev(ws.view(np.int16))
+        launch = lambda: op.launch(None, rows, x, planes.codes, planes.scales, w, s, planes.out)
+        launch()
+        torch.cuda.synchronize()
+        assert c.device_status() == 0, route
+        assert c.last_kernel.startswith("fp8_pair_stream_k_kernel") == (route == "stream_k"), c.last_kernel
+        planes.check_inactive(rows)
+        first = _u16(planes.out)[:rows].copy()
+        if route == "stream_k":
+            if out_rows * rows <= 1024 * 700:
+                check_projection(oracle, xb, wc, ws, planes, rows, floor=0.25 * (hidden / 5120) ** 0.5)
+            for _ in range(2):
+                planes.out.fill_(0x5A5A)
+                launch()
+                torch.cuda.synchronize()
+                assert np.array_equal(_u16(planes.out)[:rows], first)
+            g = graph_replay(launch)
+            planes.out.fill_(0x5A5A)
+            g.replay()
+            g.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(_u16(planes.out)[:rows], first)
+            assert c.device_status() == 0
+        outs[route] = first
+    a = oracle.bf16_to_f32(outs["stream_k"].reshape(-1)).astype(np.float64)
+    b = oracle.bf16_to_f32(outs["pair"].reshape(-1)).astype(np.float64)
+    # one BF16 step of the larger magnitude, plus the cancellation floor of a split fp32 sum
+    assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-3), np.abs(a - b).max()
+    assert (outs["stream_k"] == outs["pair"]).mean() > 0.9

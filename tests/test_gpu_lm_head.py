@@ -140,6 +140,44 @@ def test_fused_quantiser_and_tail_equal_the_separate_launches(tk, oracle, rows, 
         assert np.array_equal(planes["fused"]["scales"][: 4 * rows].view(np.uint32), os_.view(np.uint32))
 
 
+@pytest.mark.parametrize("vocab", [112, 640, 1040, 4096 + 64])
+def test_spread_maxima_equal_direct_keys(tk, oracle, vocab, monkeypatch):
+    """Up to 32 tokens the CTAs collect their maxima in per-group keys and draw per-group tickets
+    (TK100_ARGMAX_SPREAD=0: straight into the caller's keys).  Same pairs and planes on both
+    routes, launch after launch on one context (keys and tickets re-arm themselves), for fewer
+    tiles than groups (112 and 640 rows), split K (1040) and uneven groups (4160), at token counts
+    that take the per-token and the batched maxima of 16- and 32-token tiles; 33 tokens are past
+    the spread plane and use the direct keys on both."""
+    from tuiskollm_b200 import synth
+
+    hidden = 5120
+    wc, ws = synth.fp8_weights(81, 300 + vocab, vocab, hidden)
+    w, s = dev(wc), dev(ws.view(np.int16))
+    results = {}
+    for spread in ("1", "0"):
+        monkeypatch.setenv("TK100_ARGMAX_SPREAD", spread)
+        c = tk.Context(device=0)
+        for rows in (1, 3, 4, 16, 17, 32, 33, 2):
+            xb = synth.normal_bf16(81, rows, (rows, hidden))
+            x = dev(xb.view(np.int16))
+            op, p, scratch, launch = lm_head(tk, c, x, w, s, rows, vocab, 0, rows + 1, hidden)
+            launch()
+            launch()
+            torch.cuda.synchronize()
+            assert c.device_status() == 0
+            assert int(scratch.abs().sum()) == 0, "argmax scratch must be left zero"
+            got = pairs_of(p["pairs"], rows)
+            logits = _u16(p["out"])[:rows]
+            for t in range(rows):
+                assert got["index"][t] == oracle.greedy_index(logits[t]), (spread, rows, t)
+            assert_inactive_untouched(p["pairs"], rows)
+            results[(spread, rows)] = {k: host(v.view(torch.uint8)).copy() for k, v in p.items()}
+    for (spread, rows), planes in results.items():
+        if spread == "1":
+            for k, v in planes.items():
+                assert np.array_equal(v, results[("0", rows)][k]), (rows, k)
+
+
 def test_sharded_entry_on_one_rank_equals_the_plain_entry(tk, ctx, oracle):
     """tk100_fp8_lm_head_sharded with world = 1 (its own buffer list empty) gives the pairs of
     tk100_fp8_lm_head, step after step, and leaves the scratch zero."""

@@ -16,6 +16,19 @@
 //
 // Same arithmetic as the other FP8 kernels: fp32 accumulation over K in order, times the token's
 // fp32 scale, times the row's BF16 scale, rounded to BF16 once -- bit-identical to them.
+//
+// STREAM_K: the launch's work is the sequence of all (tile, K step) pairs, cut into one contiguous
+// range per resident pair, so every pair streams the same number of K steps whatever the tile
+// count (32 pair tiles of a 256-token QKV launch keep 74 pairs busy instead of 32).  A range
+// covers the tail of one tile, whole tiles, and the head of another.  A CTA that holds only part
+// of a tile's K range writes its fp32 accumulator ([token][row], its own slot of the context's
+// scratch) and takes a ticket on the tile's counter; the CTA that draws the last ticket adds the
+// slots in K order (fixed, so launches repeat bit for bit; a split sum is not the unsplit sum's
+// bits) and finishes the tile.  Nobody waits for anybody: no spin, and the counters re-arm.
+// Measured, it does not pay on this part and stays a switch: with the exchange compiled out the
+// even schedule alone is within 6 % of the one-tile-per-pair kernel at 256 tokens (8192 x 5120:
+// 19.5 against 20.7 us) and slower at 2048 (92 against 67 us: pairs on consecutive tiles no longer
+// read the same weight tile at the same time), and the exchange costs 20-30 us on top.
 #include "common.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -44,9 +57,56 @@ struct PersistControl {
   uint64_t tmem_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
-  uint32_t pad;
+  uint32_t is_last;
   float a_scale[2][kTok];
 };
+
+// One piece of a pair's work: K steps [k0, k1) of pair tile `tile`.
+struct Segment {
+  int tile, k0, k1;
+};
+
+// The segments of pair `pair` of `pairs`: whole tiles pair, pair + pairs, ... or, STREAM_K, the
+// pieces of its contiguous range of the launch's tiles x nkb steps.
+template <bool STREAM_K>
+struct Walk {
+  long long g, g_end;
+  int nkb, stride;
+  __device__ Walk(int pair, int pairs, int tiles, int nkb_) : nkb(nkb_), stride(pairs) {
+    if (STREAM_K) {
+      const long long steps = static_cast<long long>(tiles) * nkb;
+      g = steps * pair / pairs;
+      g_end = steps * (pair + 1) / pairs;
+    } else {
+      g = pair;
+      g_end = tiles;
+    }
+  }
+  __device__ bool next(Segment& s) {
+    if (g >= g_end) return false;
+    if (STREAM_K) {
+      s.tile = static_cast<int>(g / nkb);
+      s.k0 = static_cast<int>(g - static_cast<long long>(s.tile) * nkb);
+      const long long left = g_end - g;
+      s.k1 = (nkb - s.k0 <= left) ? nkb : s.k0 + static_cast<int>(left);
+      g += s.k1 - s.k0;
+    } else {
+      s.tile = static_cast<int>(g);
+      s.k0 = 0;
+      s.k1 = nkb;
+      g += stride;
+    }
+    return true;
+  }
+};
+
+// The pair whose range holds step `step`: the p with steps * p / pairs <= step < steps * (p + 1) / pairs.
+__device__ __forceinline__ int pair_of_step(long long step, long long steps, int pairs) {
+  int q = static_cast<int>(step * pairs / steps);
+  while (q + 1 < pairs && steps * (q + 1) / pairs <= step) ++q;
+  while (q > 0 && steps * q / pairs > step) --q;
+  return q;
+}
 
 constexpr size_t persist_smem_bytes() {
   return 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(PersistControl);
@@ -56,6 +116,7 @@ __device__ __forceinline__ void epilogue_barrier() {
   asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 }
 
+template <bool STREAM_K>
 __global__ void __launch_bounds__(kThreads, 1)
     fp8_pair_persist_kernel(const __grid_constant__ CUtensorMap tmap_w,
                             const __grid_constant__ CUtensorMap tmap_a, const Fp8ProjParams p) {
@@ -108,11 +169,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       pdl_wait();
       int it = 0;  // stages issued so far, across tiles
-      for (int t = pair; t < tiles && ok; t += pairs) {
-        const int unit = t / tiles_m;
-        const int tok0 = (t - unit * tiles_m) * kTok;
+      Walk<STREAM_K> walk(pair, pairs, tiles, nkb);
+      Segment seg;
+      while (ok && walk.next(seg)) {
+        const int unit = seg.tile / tiles_m;
+        const int tok0 = (seg.tile - unit * tiles_m) * kTok;
         const int row0 = (2 * unit + static_cast<int>(rank)) * kRows;
-        for (int i = 0; i < nkb && ok; ++i, ++it) {
+        for (int i = seg.k0; i < seg.k1 && ok; ++i, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1;
           ok = mbar_wait(&ctl->empty[s], phase ^ 1, p.status);
@@ -135,16 +198,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0 && rank == 0) {
       bool ok = true;
       int it = 0, round = 0;
-      for (int t = pair; t < tiles && ok; t += pairs, ++round) {
+      Walk<STREAM_K> walk(pair, pairs, tiles, nkb);
+      Segment seg;
+      for (; ok && walk.next(seg); ++round) {
         const int b = round & 1;
         if (round >= 2) {
-          // the epilogue warps of both CTAs have read tile (round - 2) out of this accumulator
+          // the epilogue warps of both CTAs have read segment (round - 2) out of this accumulator
           ok = mbar_wait_cluster(&ctl->acc_empty[b], ((round >> 1) - 1) & 1, p.status);
           if (!ok) break;
           tc_fence_after_sync();
         }
         const uint32_t acc = tmem + static_cast<uint32_t>(b) * kAccCols;
-        for (int i = 0; i < nkb && ok; ++i, ++it) {
+        for (int i = seg.k0; i < seg.k1 && ok; ++i, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1;
           ok = mbar_wait(&ctl->full[s], phase, p.status);
@@ -155,7 +220,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint64_t desc_a = umma_desc_sw128(base + kWTile);
 #pragma unroll
           for (int k4 = 0; k4 < kTileKBytes / 32; ++k4) {
-            umma_f8f6f4_pair(acc, desc_w + 2 * k4, desc_a + 2 * k4, IDESC, (i | k4) != 0);
+            umma_f8f6f4_pair(acc, desc_w + 2 * k4, desc_a + 2 * k4, IDESC, i != seg.k0 || k4 != 0);
           }
           umma_commit_pair(&ctl->empty[s]);
         }
@@ -173,12 +238,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     pdl_wait();  // activation scales and the output plane belong to the predecessor until now
     int round = 0;
-    for (int t = pair; t < tiles; t += pairs, ++round) {
+    Walk<STREAM_K> walk(pair, pairs, tiles, nkb);
+    Segment seg;
+    const long long steps = static_cast<long long>(tiles) * nkb;
+    for (; walk.next(seg); ++round) {
       const int b = round & 1;
+      const int t = seg.tile;
       const int unit = t / tiles_m;
       const int tok0 = (t - unit * tiles_m) * kTok;
-      const int n = (2 * unit + static_cast<int>(rank)) * kRows + quad * 32 + lane;
+      const int row = quad * 32 + lane;
+      const int n = (2 * unit + static_cast<int>(rank)) * kRows + row;
       const bool row_ok = n < p.out_rows;
+      const bool whole = !STREAM_K || (seg.k0 == 0 && seg.k1 == nkb);
       {
         const int tok = tok0 + et;
         ctl->a_scale[b][et] = tok < p.rows ? p.act_scales[tok] : 0.0f;
@@ -189,6 +260,27 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool got = mbar_wait(&ctl->tmem_full[b], (round >> 1) & 1, p.status);
       tc_fence_after_sync();
       const uint32_t taddr = tmem + static_cast<uint32_t>(b) * kAccCols + (static_cast<uint32_t>(quad * 32) << 16);
+      // Scales, rounds and stores 16 tokens of this thread's row.
+      auto finish = [&](int c0, const float (&acc)[16]) {
+        uint32_t bits[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          bits[j] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(acc[j], ctl->a_scale[b][c0 + j]), w_scale));
+        }
+        if (row_ok) {
+          uint16_t* dst = p.out + static_cast<size_t>(tok0 + c0) * p.out_rows + n;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (tok0 + c0 + j < p.rows) dst[static_cast<size_t>(j) * p.out_rows] = static_cast<uint16_t>(bits[j]);
+          }
+        }
+      };
+      // this pair's slot for the piece: 0 for the first segment of its range, 1 for the last
+      float* mine = nullptr;
+      if (STREAM_K && !whole) {
+        mine = p.partials +
+               ((static_cast<size_t>(pair) * 2 + (round == 0 ? 0 : 1)) * 2 + rank) * (kRows * kTok) + row * 16;
+      }
       if (got) {
 #pragma unroll 1
         for (int c0 = part * 16; c0 < kTok; c0 += 32) {
@@ -196,17 +288,18 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint32_t r[16];
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
-          uint32_t bits[16];
+          if (whole) {
+            float acc[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            bits[j] = f32_to_bf16_bits(
-                __fmul_rn(__fmul_rn(__uint_as_float(r[j]), ctl->a_scale[b][c0 + j]), w_scale));
-          }
-          if (row_ok) {
-            uint16_t* dst = p.out + static_cast<size_t>(tok0 + c0) * p.out_rows + n;
+            for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(r[j]);
+            finish(c0, acc);
+          } else {
+            // slot layout [16-token chunk][row][16 tokens]: 64 contiguous bytes per thread
+            float4* dst = reinterpret_cast<float4*>(mine + static_cast<size_t>(c0 / 16) * (kRows * 16));
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (tok0 + c0 + j < p.rows) dst[static_cast<size_t>(j) * p.out_rows] = static_cast<uint16_t>(bits[j]);
+            for (int j = 0; j < 4; ++j) {
+              __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
             }
           }
         }
@@ -216,7 +309,62 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(acc_empty0 + static_cast<uint32_t>(b * sizeof(uint64_t)));
       // After a wait that ran out the loop goes on (every later wait gives up at its first look):
-      // leaving here would strand the other epilogue warps at the named barrier above.
+      // leaving here would strand the other epilogue warps at the named barriers.
+      if (STREAM_K && !whole) {
+        // The pieces of this CTA's half of the tile: one per pair whose range meets the tile.
+        const long long tile_step0 = static_cast<long long>(t) * nkb;
+        const int first = pair_of_step(tile_step0, steps, pairs);
+        const int last = pair_of_step(tile_step0 + nkb - 1, steps, pairs);
+        __threadfence();
+        epilogue_barrier();
+        if (et == 0) {
+          unsigned int* counter = p.counters + 2 * t + rank;
+          const unsigned int ticket = atomicAdd(counter, 1u);
+          const bool closes = ticket == static_cast<unsigned int>(last - first);
+          if (closes) *counter = 0u;  // re-armed for the next launch
+          ctl->is_last = closes ? 1u : 0u;
+        }
+        epilogue_barrier();
+        const bool closes = ctl->is_last != 0u;
+        if (closes) {
+          __threadfence();
+          // 16 tokens at a time, up to four pieces side by side: 16 loads of 16 bytes in flight
+#pragma unroll 1
+          for (int c0 = part * 16; c0 < kTok; c0 += 32) {
+            if (tok0 + c0 >= p.rows) break;
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+#pragma unroll 1
+            for (int q0 = first; q0 <= last; q0 += 4) {  // K order
+              float4 v[4][4];
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const int q = q0 + w <= last ? q0 + w : last;  // a missing piece: read again, not added
+                const bool heads_here = static_cast<int>((steps * q / pairs) / nkb) == t;
+                const float4* src = reinterpret_cast<const float4*>(
+                    p.partials + ((static_cast<size_t>(q) * 2 + (heads_here ? 0 : 1)) * 2 + rank) * (kRows * kTok) +
+                    static_cast<size_t>(c0 / 16) * (kRows * 16) + row * 16);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[w][j] = __ldcg(src + j);
+              }
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                if (q0 + w <= last) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    acc[4 * j] = __fadd_rn(acc[4 * j], v[w][j].x);
+                    acc[4 * j + 1] = __fadd_rn(acc[4 * j + 1], v[w][j].y);
+                    acc[4 * j + 2] = __fadd_rn(acc[4 * j + 2], v[w][j].z);
+                    acc[4 * j + 3] = __fadd_rn(acc[4 * j + 3], v[w][j].w);
+                  }
+                }
+              }
+            }
+            finish(c0, acc);
+          }
+        }
+      }
     }
   }
 
@@ -234,14 +382,24 @@ __global__ void __launch_bounds__(kThreads, 1)
 }  // namespace
 
 cudaError_t fp8_pair_persist_prepare() {
-  return cudaFuncSetAttribute(fp8_pair_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(fp8_pair_persist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(persist_smem_bytes()));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(fp8_pair_persist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(persist_smem_bytes()));
 }
 
+size_t fp8_pair_stream_k_scratch_bytes(int pairs) {
+  // two slots per pair (head and tail piece of its range), two CTAs, 128 rows x 256 tokens fp32
+  return static_cast<size_t>(pairs) * 2 * 2 * kRows * kTok * sizeof(float);
+}
+
 cudaError_t launch_fp8_pair_persist(cudaStream_t stream, int pairs, const CUtensorMap& tmap_w,
-                                    const CUtensorMap& tmap_a, const Fp8ProjParams& p) {
-  return launch_kernel_cluster(fp8_pair_persist_kernel, dim3(2 * pairs, 1, 1), dim3(kThreads),
-                               persist_smem_bytes(), stream, dim3(2, 1, 1), tmap_w, tmap_a, p);
+                                    const CUtensorMap& tmap_a, const Fp8ProjParams& p, bool stream_k) {
+  return stream_k ? launch_kernel_cluster(fp8_pair_persist_kernel<true>, dim3(2 * pairs, 1, 1), dim3(kThreads),
+                                          persist_smem_bytes(), stream, dim3(2, 1, 1), tmap_w, tmap_a, p)
+                  : launch_kernel_cluster(fp8_pair_persist_kernel<false>, dim3(2 * pairs, 1, 1), dim3(kThreads),
+                                          persist_smem_bytes(), stream, dim3(2, 1, 1), tmap_w, tmap_a, p);
 }
 
 }  // namespace tk100

@@ -270,8 +270,11 @@ cudaError_t fp8_projection_prepare();  // sets the dynamic shared-memory attribu
 // unsplit K; out_rows must be a multiple of 256).
 // Persistent form (fp8_pair_persist.cu): `pairs` resident CTA pairs walk the pair tiles.
 cudaError_t fp8_pair_persist_prepare();
+// stream_k: the pairs share the launch's tiles x K steps evenly; pieces of a tile meet in
+// p.partials (fp8_pair_stream_k_scratch_bytes) under tickets in p.counters (two per pair tile).
 cudaError_t launch_fp8_pair_persist(cudaStream_t stream, int pairs, const CUtensorMap& tmap_w,
-                                    const CUtensorMap& tmap_a, const Fp8ProjParams& p);
+                                    const CUtensorMap& tmap_a, const Fp8ProjParams& p, bool stream_k);
+size_t fp8_pair_stream_k_scratch_bytes(int pairs);
 cudaError_t fp8_pair_prepare();
 cudaError_t launch_fp8_pair(cudaStream_t stream, const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                             const Fp8ProjParams& p);

@@ -41,6 +41,7 @@ Tuning Tuning::from_environment() {
   t.nvfp4_pair_min_rows = env_int("TK100_PAIR_MIN_ROWS", t.nvfp4_pair_min_rows);
   t.swiglu_pairs = env_int("TK100_SWIGLU_PAIRS", t.swiglu_pairs);
   t.fp8_persist = env_int("TK100_FP8_PERSIST", t.fp8_persist);
+  t.fp8_stream_k = env_int("TK100_FP8_STREAMK", t.fp8_stream_k);
   t.nvfp4_wide = env_int("TK100_NVFP4_WIDE", t.nvfp4_wide);
   t.nvfp4_wide_min_rows = env_int("TK100_NVFP4_WIDE_MIN_ROWS", t.nvfp4_wide_min_rows);
   t.nvfp4_persist = env_int("TK100_PERSIST", t.nvfp4_persist);
@@ -696,8 +697,23 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
     // walking K = 17408) leaves most SMs idle as well; the one-CTA kernel splits K over clusters
     // there (measured 44.6 against 57.0 us).
     const bool long_k_few_tiles = pair_ctas < ctx_.sm_count() / 2 && columns >= 16384;
+    // Stream-K on resident pairs (TK100_FP8_STREAMK=1, an experiment switch: measured slower than
+    // the routes below at every benchmarked shape): every pair streams the same share of the
+    // launch's tiles x K steps.
+    const long long pair_tile_count = pair_ctas / 2;
+    const int k_steps = columns / 128;
+    bool stream_k = false;
+    int stream_pairs = 0;
+    if (tune.fp8_stream_k != 0 && ctx_.persist_pairs() > 0) {
+      const long long steps = pair_tile_count * k_steps;
+      stream_pairs = static_cast<int>(steps < ctx_.persist_pairs() ? steps : ctx_.persist_pairs());
+      const bool fits = stream_pairs > 0 &&
+                        fp8_pair_stream_k_scratch_bytes(stream_pairs) <= ctx_.partial_bytes() &&
+                        static_cast<size_t>(2 * pair_tile_count) <= ctx_.counter_count();
+      stream_k = fits;
+    }
     if (tune.fp8_pair != 0 && rows >= min_rows && out_rows % 256 == 0 &&
-        ((pair_ctas >= 32 && !long_k_few_tiles) || tune.fp8_pair == 2) && output &&
+        ((pair_ctas >= 32 && !long_k_few_tiles) || tune.fp8_pair == 2 || stream_k) && output &&
         !logits_f32 && !argmax_scratch && ctx_.forced_block_tok() == 0 && ctx_.forced_splits() == 0) {
       CUtensorMap map_w, map_a;
       TK100_TRY(ctx_.tensor_map(weight_codes, static_cast<uint64_t>(out_rows),
@@ -719,6 +735,13 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
       q.debug = debug_flags();
       q.stamps = debug_stamps();
       ctx_.count_launch();
+      if (stream_k) {
+        q.partials = ctx_.partials();
+        q.counters = ctx_.counters();
+        ctx_.note_route("fp8_pair_stream_k_kernel", 6, stream_pairs, 1, 1);
+        return ctx_.check(launch_fp8_pair_persist(stream, stream_pairs, map_w, map_a, q, true),
+                          "launching the stream-K FP8 pair projection");
+      }
       // More pair tiles than pairs that fit the device at once: the resident pairs walk the tiles
       // with two accumulators in rotation (TK100_FP8_PERSIST).
       const long long pair_tiles = pair_ctas / 2;
@@ -726,7 +749,7 @@ Status Fp8ProjectionOp::launch(cudaStream_t stream, int rows, int out_rows, int 
           (pair_tiles > ctx_.persist_pairs() || tune.fp8_persist == 2)) {
         const int pairs = static_cast<int>(pair_tiles < ctx_.persist_pairs() ? pair_tiles : ctx_.persist_pairs());
         ctx_.note_route("fp8_pair_persist_kernel", 6, pairs, 1, 1);
-        return ctx_.check(launch_fp8_pair_persist(stream, pairs, map_w, map_a, q),
+        return ctx_.check(launch_fp8_pair_persist(stream, pairs, map_w, map_a, q, false),
                           "launching the persistent FP8 pair projection");
       }
       ctx_.note_route("fp8_pair_kernel", q.deep_ring ? 6 : 3, 0, 1, 1);

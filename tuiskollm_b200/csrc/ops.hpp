@@ -40,6 +40,7 @@ struct Tuning {
   int nvfp4_pair_min_rows = 1024;
   int nvfp4_persist = 0;      // TK100_PERSIST=1: persistent CTA-pair route for NVFP4 prefill shapes
   int nvfp4_persist_min_rows = 512;  // TK100_PERSIST_MIN_ROWS
+  int fp8_stream_k = 0;       // TK100_FP8_STREAMK=1: stream-K on resident pairs wherever pairs can run (measured slower)
   int fp8_persist = 0;        // TK100_FP8_PERSIST=1: persistent CTA pairs with two accumulators for FP8
                               // prefill shapes of more pair tiles than resident pairs
   int nvfp4_wide = 0;         // TK100_NVFP4_WIDE: 256-token tiles (one CTA per SM) for NVFP4 prefill
