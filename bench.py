@@ -437,13 +437,20 @@ class Protocol:
     :1228-1239): every case is a CUDA graph of `ops` operations; each of the 40 samples times
     every case once with CUDA events, visiting the cases in an order that reverses on odd samples
     and rotates by the sample number; a case reports median / p10 / p90 microseconds per
-    operation."""
+    operation.  Between the two events the graph is launched as often as it takes to reach
+    OPS_PER_SAMPLE operations (the reference launches its graph 256 times per sample, :39,
+    :1028-1031): the device idles for one host-side graph launch (a few microseconds) after the
+    start event, and that idle time belongs to no operation."""
+
+    OPS_PER_SAMPLE = 32
 
     def __init__(self, torch):
         self.torch = torch
         self.cases = []  # (name, replay, ops, replays per sample)
 
-    def add(self, name, replay, ops, inner=1):
+    def add(self, name, replay, ops, inner=None):
+        if inner is None:
+            inner = max(1, -(-self.OPS_PER_SAMPLE // ops))
         self.cases.append((name, replay, ops, inner))
 
     @staticmethod
@@ -476,6 +483,8 @@ class Protocol:
             v.sort()
             out[name] = {"median": statistics.median(v), "p10": percentile(v, 0.1),
                          "p90": percentile(v, 0.9), "samples": len(v)}
+        for name, _replay, ops, inner in self.cases:
+            out[name]["operations_per_sample"] = ops * inner
         return out
 
 
@@ -973,7 +982,8 @@ def config_rows(torch, tk, ctx, peak_gbs, peak_kind, lm, with_cpu=True):
         md = meta[case]
         us = r["median"]
         row = {"config": md["config"], "op": md["op"], "M": md["M"],
-               "us": {"median": us, "p10": r["p10"], "p90": r["p90"], "samples": r["samples"]}}
+               "us": {"median": us, "p10": r["p10"], "p90": r["p90"], "samples": r["samples"],
+                      "operations_per_sample": r["operations_per_sample"]}}
         for key in ("N", "K", "weight_copies"):
             if key in md:
                 row[key] = md[key]
