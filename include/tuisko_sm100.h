@@ -288,7 +288,11 @@ TK100_API tk100_status tk100_gdn_recurrence(tk100_ctx* ctx, tk100_stream stream,
  * plane; logits_f32 and pairs are optional (NULL to skip; with pairs == NULL and
  * argmax_scratch != NULL the packed maxima are left in argmax_scratch).  argmax_scratch is a
  * caller-owned array of `rows` 64-bit words that must be zero before the first launch;
- * every launch leaves it zero again.  pairs[i].index is a global vocabulary index. */
+ * every launch leaves it zero again (with pairs != NULL and up to 32 rows the CTAs collect their
+ * maxima in keys owned by the context, one cache line per token and group of CTAs, and the
+ * caller's array is not written at all).  Launches on one context that write pairs must be
+ * ordered on one stream: they share those keys and the ticket that elects the finishing CTA.
+ * pairs[i].index is a global vocabulary index. */
 TK100_API tk100_status tk100_fp8_lm_head(tk100_ctx* ctx, tk100_stream stream, int rows, int vocab_rows,
                                int vocab_offset, const uint16_t* input, uint8_t* activation_codes,
                                float* activation_scales, const uint8_t* weight_codes,
