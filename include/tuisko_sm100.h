@@ -90,7 +90,10 @@ TK100_API tk100_status tk100_create(const tk100_config* config, tk100_ctx** out)
 TK100_API void tk100_destroy(tk100_ctx* ctx);
 /* Message of the last failure on this context (or of tk100_create when ctx is NULL). */
 TK100_API const char* tk100_last_error(const tk100_ctx* ctx);
-/* Reads and clears the device status word; synchronises `stream`. */
+/* Reads and clears the device status word; synchronises `stream`.  When the word reports a wait
+ * that ran out, the tickets and keys a kernel that gave up may have left behind (split-K tile
+ * tickets, the LM head's tail ticket and per-group maxima) are zeroed as well, so the context can
+ * be used again; the results of the launches before the call are invalid. */
 TK100_API tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* word);
 /* Number of kernels this context has launched (for launch accounting). */
 TK100_API uint64_t tk100_launch_count(const tk100_ctx* ctx);

@@ -361,5 +361,12 @@ def test_peer_exchange_single_rank_and_bounded_wait(tk, ctx, oracle):
     op.exchange(None, rows, 2, 0, scratch, [buf2[0].data_ptr(), buf2[1].data_ptr()], merged)
     assert ctx.device_status() & _lib.DEVICE_WAIT_TIMEOUT
     assert ctx.device_status() == 0
+    # the context is usable again: reading a timed-out status word re-arms tickets and keys
+    scratch.zero_()
+    launch()
+    torch.cuda.synchronize()
+    again = pairs_of(p["pairs"], rows)
+    assert np.array_equal(again["index"], expect["index"]) and np.array_equal(again["value"], expect["value"])
+    assert ctx.device_status() == 0
     with pytest.raises(tk.GpuError):
         op.exchange(None, rows, 9, 0, scratch, [buf.data_ptr()] * 9, merged)

@@ -1233,9 +1233,14 @@ tk100_status tk100_device_status(tk100_ctx* ctx, tk100_stream stream, uint32_t* 
   if (e == cudaSuccess) e = cudaMemsetAsync(ctx->impl->status_word(), 0, sizeof(uint32_t), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e == cudaSuccess && (*word & tk100::STATUS_WAIT_TIMEOUT)) {
-    // CTAs that gave up may have left split-K tickets behind: re-arm them.
+    // CTAs that gave up may have left split-K tickets, the LM head's tail ticket or its spread
+    // maxima behind: re-arm them (the exchange's step number keeps counting).
     e = cudaMemsetAsync(ctx->impl->counters(), 0,
                         ctx->impl->counter_count() * sizeof(unsigned int), s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->impl->tail_ticket(), 0, sizeof(unsigned int), s);
+    if (e == cudaSuccess) {
+      e = cudaMemsetAsync(ctx->impl->argmax_spread_keys(), 0, tk100::kArgmaxSpreadBytes, s);
+    }
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   }
   return ctx->impl->check(e, "reading the device status word");
