@@ -371,8 +371,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Neither CTA may release shared memory or TMEM while the pair still works on it.
   tc_fence_before_sync();
   __syncthreads();
-  cluster_arrive();
-  cluster_wait();
+  cluster_arrive_relaxed();  // execution order only: nothing here waits for the epilogue's global stores
+  cluster_wait_relaxed();
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc_pair(tmem, kTmemCols);

@@ -708,8 +708,8 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
           }
         }
       }
-      cluster_arrive();  // nobody's shared memory may go away while a peer still reads it
-      cluster_wait();
+      cluster_arrive_relaxed();  // nobody's shared memory may go away while a peer still reads it
+      cluster_wait_relaxed();
     }
 
     const bool spread = p.spread_keys != nullptr;
@@ -809,8 +809,8 @@ __global__ void __launch_bounds__(kThreads, BLOCK_TOK <= 32 ? (DEEP == 1 ? 2 : (
     // the TMA and UMMA warps take part in the two cluster barriers of the reduction
     cluster_arrive();
     cluster_wait();
-    cluster_arrive();
-    cluster_wait();
+    cluster_arrive_relaxed();
+    cluster_wait_relaxed();
   }
 
   tc_fence_before_sync();

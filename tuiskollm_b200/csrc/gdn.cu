@@ -282,7 +282,11 @@ __global__ void __cluster_dims__(SPLIT, 1, 1) __launch_bounds__(kRecThreads)
     s.y = fmaf(old_state[i].y, decay, k.y * update);
     s.z = fmaf(old_state[i].z, decay, k.z * update);
     s.w = fmaf(old_state[i].w, decay, k.w * update);
-    *reinterpret_cast<float4*>(state + i * kHeadDim + lane * 4) = s;
+    // Four-CTA clusters (batches up to 4) keep the new rows and store them behind the push below;
+    // with two-CTA clusters the registers that takes cost the sixth resident CTA per SM, and the
+    // 768 CTAs of batch 8 would no longer run as one wave.
+    if constexpr (kRecSplit == 4) old_state[i] = s;
+    else *reinterpret_cast<float4*>(state + i * kHeadDim + lane * 4) = s;
     rec[i] = dot4(s, q);
   }
 #pragma unroll
@@ -302,11 +306,18 @@ __global__ void __cluster_dims__(SPLIT, 1, 1) __launch_bounds__(kRecThreads)
     for (int i = 1; i < kRowsPerWarp; ++i) mine = lane == i ? rec[i] : mine;
     recurrent[warp * kRowsPerWarp + lane] = mine;
   }
-  // Lane r pushes this warp's sum of squares into CTA r of the cluster.
+  // Lane r pushes this warp's sum of squares into CTA r of the cluster.  Four-CTA clusters store
+  // the new state rows between the two halves of the barrier: its release half would otherwise
+  // wait for those global stores before it lets the peers see the sums (batch 1: 4.9 -> 4.6 us).
   cluster_wait();
   if (lane < kRecSplit)
     st_dsmem_f32(mapa_u32(smem_u32(&squares[rank * kRecWarps + warp]), lane), square);
   cluster_arrive();
+  if constexpr (kRecSplit == 4) {
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i)
+      *reinterpret_cast<float4*>(state + i * kHeadDim + lane * 4) = old_state[i];
+  }
   cluster_wait();
 
   if (tid < kRowsPerCta) {

@@ -636,8 +636,8 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), (GATE_UP || BL
     if (pushed) {
       if (warp < 2) cluster_wait();  // completes the barrier every thread arrived on after set-up
     } else {
-      cluster_arrive();  // both CTAs keep their shared memory until the partner has read it
-      cluster_wait();
+      cluster_arrive_relaxed();  // both CTAs keep their shared memory until the partner has read it
+      cluster_wait_relaxed();
     }
   }
 
@@ -677,8 +677,8 @@ __global__ void __launch_bounds__(nv_threads(BLOCK_TOK, GATE_UP), (GATE_UP || BL
         }
       }
     }
-    cluster_arrive();  // no CTA's shared memory may go away while a peer still reads it
-    cluster_wait();
+    cluster_arrive_relaxed();  // no CTA's shared memory may go away while a peer still reads it
+    cluster_wait_relaxed();
   }
 
   tc_fence_before_sync();

@@ -344,10 +344,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 #endif
 
-  // Neither CTA may release shared memory or TMEM while the pair still works on it.
+  // Neither CTA may release shared memory or TMEM while the pair still works on it (execution
+  // order only: nothing here waits for the epilogue's global stores).
   tc_fence_before_sync();
-  cluster_arrive();
-  cluster_wait();
+  cluster_arrive_relaxed();
+  cluster_wait_relaxed();
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc_pair(tmem, kTmemCols);

@@ -68,6 +68,14 @@ __device__ __forceinline__ void cluster_arrive() {
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
+// The same barrier without memory ordering: for "nobody leaves before everybody is done reading",
+// where the reads have already returned their values.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_relaxed() {
+  asm volatile("barrier.cluster.wait;" ::: "memory");
+}
 
 // shared::cluster address of the byte at local shared-memory address `local_smem_addr` in CTA
 // `rank` of this cluster.
